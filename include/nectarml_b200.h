@@ -1,0 +1,195 @@
+/*
+ * nectarml_b200 -- C ABI of the B200 (sm_100a) dense-contraction path:
+ * Conv2d / ConvTranspose2d / Linear in forward, input-gradient and weight-gradient.
+ *
+ * Two layers of entry points:
+ *
+ *  (1) nml_conv_* / nml_linear_*  -- descriptor based, caller-owned outputs and workspace,
+ *      explicit stream, no allocation, no synchronisation, int status return.
+ *  (2) nml_ref_*                  -- the flat signatures of the reference's host ops
+ *      (device pointers as integers + shape ints in, freshly cudaMalloc'ed result out), so a
+ *      binding of the reference's `_nectarml.tensor.conv.*` / `_nectarml.tensor.matmul`
+ *      names can forward to them one to one.
+ *
+ * All pointers are device pointers unless stated.  Nothing here takes or returns a torch type.
+ */
+#ifndef NECTARML_B200_H
+#define NECTARML_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes (0 = success).  nml_status_string() names them. */
+enum {
+    NML_OK = 0,
+    NML_ERR_INVALID = 1,     /* bad descriptor / argument                                   */
+    NML_ERR_WORKSPACE = 2,   /* workspace missing or too small                              */
+    NML_ERR_CUDA = 3,        /* a CUDA runtime / driver call failed                         */
+    NML_ERR_UNSUPPORTED = 4, /* valid request the kernels do not cover (e.g. groups != 1)   */
+    NML_ERR_DEVICE = 5       /* a kernel gave up on a bounded wait (see nml_device_status)  */
+};
+
+/* Element types; the values equal the reference's DType enum
+ * (nectarml/csrc/include/common/dtype.h:15-21: Float32 = 0, Float16 = 1). */
+enum { NML_F32 = 0, NML_F16 = 1 };
+
+/* Activation layouts. The reference only knows NCHW (nectarml/csrc/ops/tensor/conv/conv2d.cpp:71-134);
+ * NHWC is this library's native layout and needs no conversion pass. */
+enum { NML_NCHW = 0, NML_NHWC = 1 };
+
+/* Arithmetic of the contraction.
+ *  NML_MATH_F16    operands rounded to fp16, fp32 accumulation (replaces cublasHgemm,
+ *                  conv2d.cpp:111-118, with a wider accumulator)
+ *  NML_MATH_3XTF32 fp32 operands split into tf32 hi + lo, three tensor-core products, fp32
+ *                  accumulation (replaces cublasSgemm, conv2d.cpp:100-109)
+ *  NML_MATH_TF32   single tf32 product (not used by the reference-compatible entry points) */
+enum { NML_MATH_F16 = 0, NML_MATH_3XTF32 = 1, NML_MATH_TF32 = 2 };
+
+/* Geometry of one Conv2d (transposed = 0) or ConvTranspose2d (transposed = 1) layer plus the
+ * storage formats of the tensors of one call.  batch/c_in/h/w describe the layer's INPUT;
+ * the layer's output has c_out channels and the usual output size
+ *   conv : (h + 2p - d(k-1) - 1)/s + 1            (nectarml/nn/functional/conv.py:406-407)
+ *   convT: (h-1)s - 2p + d(k-1) + 1 + outpad      (nectarml/nn/functional/conv.py:479-482)
+ * Weights are [c_out, c_in, kh, kw] for conv and [c_in, c_out, kh, kw] for convT
+ * (nectarml/nn/conv.py:287-289), always dense (groups == 1).
+ *   in_dtype / in_layout   : the activation tensors read by the call (x, or dy and x)
+ *   out_dtype / out_layout : the activation tensor written (y or dx); dw and db are fp32
+ *   w_dtype                : weights and bias as stored                                  */
+typedef struct nml_conv_desc {
+    int batch, c_in, h, w;
+    int c_out, kh, kw;
+    int stride_h, stride_w;
+    int pad_h, pad_w;
+    int dil_h, dil_w;
+    int outpad_h, outpad_w; /* ConvTranspose2d only */
+    int transposed;
+    int in_dtype, in_layout;
+    int out_dtype, out_layout;
+    int w_dtype;
+    int math;
+    int round_out_f16;      /* forward only: round the result through fp16 before the store,
+                               as the reference's autocast forward does (conv2d.cpp:415-435)  */
+} nml_conv_desc;
+
+/* y = x * W^T + b with W [out_features, in_features] (nectarml/nn/linear.py:44-47). */
+typedef struct nml_linear_desc {
+    int rows, in_features, out_features;
+    int in_dtype, out_dtype, w_dtype;
+    int math;
+    int round_out_f16;
+} nml_linear_desc;
+
+enum { NML_PASS_FORWARD = 0, NML_PASS_BACKWARD_DATA = 1, NML_PASS_BACKWARD_WEIGHT = 2 };
+
+const char* nml_status_string(int status);
+
+/* Output size of the layer described by d (height, width). Returns a status. */
+int nml_conv_output_size(const nml_conv_desc* d, int* h_out, int* w_out);
+
+/* Bytes of workspace the given pass needs (0 is possible). Returns a status. */
+int nml_conv_workspace_size(const nml_conv_desc* d, int pass, size_t* bytes);
+int nml_linear_workspace_size(const nml_linear_desc* d, int pass, size_t* bytes);
+
+/* Forward.  Replaces run_conv2d / run_conv_transpose2d and their im2col, bias, transposition
+ * and cast kernels (nectarml/csrc/ops/tensor/conv/conv2d.cpp:71-134, 136-211, 401-497).
+ * bias may be NULL. */
+int nml_conv_forward(const nml_conv_desc* d, const void* x, const void* w, const void* bias, void* y,
+                     void* workspace, size_t workspace_bytes, void* stream);
+
+/* Input gradient: dx from dy.  Replaces run_conv2d_backward_input + col2im
+ * (conv2d.cpp:213-274, 499-518) and conv_transpose2d_backward_input (conv2d.cpp:520-542). */
+int nml_conv_backward_data(const nml_conv_desc* d, const void* dy, const void* w, void* dx,
+                           void* workspace, size_t workspace_bytes, void* stream);
+
+/* Weight gradient (overwrites dw, fp32, weight-shaped) and, when db != NULL, the bias gradient
+ * db[c] = sum over batch and pixels of dy (fp32).  Replaces run_conv2d_backward_weight /
+ * run_conv_transpose2d_backward_weight (conv2d.cpp:276-335, 337-395) and the three chained
+ * reductions of `out_grad.sum(dim=(0,2,3))` (nectarml/cuda/tensor/conv.py:175-176). */
+int nml_conv_backward_weight(const nml_conv_desc* d, const void* x, const void* dy, float* dw,
+                             float* db, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Linear.  Replaces the permute + cast + cublas + broadcast-add chain behind
+ * `x @ W.transpose(1,0) + b` (nectarml/nn/linear.py:44-47,
+ * nectarml/core/_tensor/numerical.py:864-907) and its backward (numerical.py:896-904, 662-666):
+ *   forward          y [rows,out] = x [rows,in] * W[out,in]^T + b
+ *   backward_data    dx[rows,in]  = dy[rows,out] * W[out,in]
+ *   backward_weight  dw[out,in]   = dy^T * x,  db[out] = column sums of dy            */
+int nml_linear_forward(const nml_linear_desc* d, const void* x, const void* w, const void* bias,
+                       void* y, void* workspace, size_t workspace_bytes, void* stream);
+int nml_linear_backward_data(const nml_linear_desc* d, const void* dy, const void* w, void* dx,
+                             void* workspace, size_t workspace_bytes, void* stream);
+int nml_linear_backward_weight(const nml_linear_desc* d, const void* x, const void* dy, float* dw,
+                               float* db, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Synchronises the current device and returns NML_OK, or NML_ERR_DEVICE with *code set to the
+ * wait that timed out inside a kernel since the last call (and clears it).  The asynchronous
+ * entry points above never block, so this is how a caller learns of a device-side give-up. */
+int nml_device_status(int* code);
+
+/* Number of contraction-kernel launches this process has made (for launch accounting). */
+long long nml_launch_count(void);
+
+/* ---- reference-shaped entry points ------------------------------------------------------
+ * Same argument lists as the reference's host ops, which its pybind module registers as
+ * `_nectarml.tensor.conv.*` and `_nectarml.tensor.matmul`
+ * (nectarml/csrc/python/ops/tensor/conv.h:71-150, matmul.h:10-16, bindings.cpp:41-51).
+ * Pointers travel as integers; *result receives a device pointer obtained from cudaMalloc that
+ * the caller releases with cudaFree (the reference's `free_cuda` path ends in cudaFree,
+ * nectarml/csrc/pool/allocator_pool.cpp:75-96).  dtype uses the NML_F32 / NML_F16 values.
+ * Like the reference these run on the legacy default stream and are ordered by it.
+ * With half_precision != 0 the tensors are fp32 in memory, the contraction runs on fp16
+ * operands and the fp32 result holds fp16-rounded values (conv2d.cpp:415-435); otherwise fp32
+ * tensors use the 3xTF32 split and fp16 tensors the fp16 path.  The backward entry points take
+ * the dtype of the tensors they are handed and always produce fp32 gradients. */
+int nml_ref_conv2d(uintptr_t input_ptr, size_t input_size, uintptr_t weight_ptr, size_t weight_size,
+                   uintptr_t bias_ptr, size_t bias_size, size_t output_size, int B, int C_in, int H,
+                   int W, int C_out, int KH, int KW, int stride_h, int stride_w, int padding_h,
+                   int padding_w, int dilation_h, int dilation_w, int groups, int dtype,
+                   int half_precision, uintptr_t* result);
+int nml_ref_conv_transpose2d(uintptr_t input_ptr, size_t input_size, uintptr_t weight_ptr,
+                             size_t weight_size, uintptr_t bias_ptr, size_t bias_size,
+                             size_t output_size, int B, int C_in, int H, int W, int C_out, int KH,
+                             int KW, int stride_h, int stride_w, int padding_h, int padding_w,
+                             int dilation_h, int dilation_w, int output_padding_h,
+                             int output_padding_w, int groups, int dtype, int half_precision,
+                             uintptr_t* result);
+int nml_ref_conv2d_backward_input(uintptr_t out_grad_ptr, uintptr_t weight_ptr, int B, int C_in, int H,
+                                  int W, int C_out, int KH, int KW, int H_out, int W_out,
+                                  int stride_h, int stride_w, int padding_h, int padding_w,
+                                  int dilation_h, int dilation_w, int groups, int dtype,
+                                  uintptr_t* result);
+int nml_ref_conv_transpose2d_backward_input(uintptr_t out_grad_ptr, uintptr_t weight_ptr, int B,
+                                            int C_in, int H, int W, int C_out, int KH, int KW,
+                                            int H_out, int W_out, int stride_h, int stride_w,
+                                            int padding_h, int padding_w, int dilation_h,
+                                            int dilation_w, int groups, int dtype, uintptr_t* result);
+int nml_ref_conv2d_backward_weight(uintptr_t out_grad_ptr, uintptr_t input_ptr, int B, int C_in, int H,
+                                   int W, int C_out, int KH, int KW, int H_out, int W_out,
+                                   int stride_h, int stride_w, int padding_h, int padding_w,
+                                   int dilation_h, int dilation_w, int dtype, uintptr_t* result);
+int nml_ref_conv_transpose2d_backward_weight(uintptr_t out_grad_ptr, uintptr_t input_ptr, int B,
+                                             int C_in, int H, int W, int C_out, int KH, int KW,
+                                             int H_out, int W_out, int stride_h, int stride_w,
+                                             int padding_h, int padding_w, int dilation_h,
+                                             int dilation_w, int dtype, uintptr_t* result);
+/* C[..., M, N] = A[..., M, K] * B[K, N] (or batched B), row-major
+ * (nectarml/csrc/ops/tensor/matmul.cpp:8-48).  a_shape / b_shape are host arrays. */
+int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_rank,
+                   const int* b_shape, int b_rank, int dtype, uintptr_t* result);
+
+/* ---- test support ----------------------------------------------------------------------
+ * Copies one TMA box of a row-major host-described 4-D tensor (dims fastest first) into a
+ * linear device buffer without swizzle, so tests can pin the coordinate, element-stride and
+ * zero-fill behaviour the implicit-GEMM address math relies on.  elem_bytes is 2 or 4. */
+int nml_debug_tma_box(const void* tensor, int elem_bytes, const int dims[4], const int box[4],
+                      const int elem_strides[4], const int coords[4], void* out, size_t out_bytes,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NECTARML_B200_H */

@@ -1,0 +1,996 @@
+// Host side of the C ABI declared in include/nectarml_b200.h: turns a layer description into
+// conversion passes, TMA tensor maps, a tile/phase/tap table and one launch of the
+// contraction kernel.  No allocation, no synchronisation in the descriptor-based entry
+// points; the reference-shaped entry points allocate their result as the reference does.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <string.h>
+
+#include <algorithm>
+#include <mutex>
+#include <vector>
+
+#include "../../include/nectarml_b200.h"
+#include "nml_prepass.cuh"
+#include "nml_umma.cuh"
+
+namespace nml {
+
+// ------------------------------------------------------------------ utilities --
+#define NML_CUDA(expr)                                   \
+    do {                                                 \
+        cudaError_t e_ = (expr);                         \
+        if (e_ != cudaSuccess) {                         \
+            set_last_cuda_error(e_, #expr);              \
+            return NML_ERR_CUDA;                         \
+        }                                                \
+    } while (0)
+
+static thread_local char g_last_error[256] = {0};
+static void set_last_cuda_error(cudaError_t e, const char* what) {
+    snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
+}
+
+static inline size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+// Bump allocator over the caller's workspace; in dry mode it only measures.
+struct Bump {
+    uint8_t* base;
+    size_t off, cap;
+    bool dry;
+    void* take(size_t bytes) {
+        off = round_up(off, 256);
+        void* p = dry ? nullptr : base + off;
+        off += bytes;
+        return p;
+    }
+    bool fits() const { return dry || off <= cap; }
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// Tensor map over a dense tensor given fastest-first dims; strides are the dense ones.
+static int encode_map(CUtensorMap* tm, const void* ptr, int elem_bytes, int rank, const uint64_t* dims,
+                      const uint32_t* box, const uint32_t* estr, bool swizzle128) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (!fn) {
+        snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled not available");
+        return NML_ERR_CUDA;
+    }
+    cuuint64_t gdim[5], gstr[5];
+    cuuint32_t b[5], es[5];
+    uint64_t pitch = elem_bytes;
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        b[i] = box[i];
+        es[i] = estr[i];
+        pitch *= dims[i];
+        if (i + 1 < rank) gstr[i] = pitch;  // stride of dim i+1
+    }
+    CUresult r = fn(tm, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
+                    rank, const_cast<void*>(ptr), gdim, gstr, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        snprintf(g_last_error, sizeof(g_last_error),
+                 "cuTensorMapEncodeTiled failed (%d): rank %d dims %llu %llu %llu %llu box %u %u %u %u",
+                 (int)r, rank, (unsigned long long)dims[0], (unsigned long long)(rank > 1 ? dims[1] : 0),
+                 (unsigned long long)(rank > 2 ? dims[2] : 0), (unsigned long long)(rank > 3 ? dims[3] : 0),
+                 box[0], rank > 1 ? box[1] : 0, rank > 2 ? box[2] : 0, rank > 3 ? box[3] : 0);
+        return NML_ERR_CUDA;
+    }
+    return NML_OK;
+}
+
+// Per-device state: status word the kernels report into, SM count.
+struct DeviceState {
+    int* err = nullptr;
+    int sms = 0;
+    bool attr_set = false;
+};
+static DeviceState g_dev[64];
+static std::mutex g_dev_mutex;
+static long long g_launches = 0;
+
+static int device_state(DeviceState** out) {
+    int dev = 0;
+    NML_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return NML_ERR_INVALID;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    DeviceState& s = g_dev[dev];
+    if (!s.err) {
+        NML_CUDA(cudaMalloc(&s.err, sizeof(int)));
+        NML_CUDA(cudaMemset(s.err, 0, sizeof(int)));
+        NML_CUDA(cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev));
+    }
+    if (!s.attr_set) {
+        NML_CUDA(cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+        s.attr_set = true;
+    }
+    *out = &s;
+    return NML_OK;
+}
+
+struct MathInfo {
+    int es, kb, enc, planes, kind;
+};
+static bool math_info(int math, MathInfo* m) {
+    switch (math) {
+        case NML_MATH_F16: *m = {2, 64, ENC_F16, 1, KIND_F16}; return true;
+        case NML_MATH_3XTF32: *m = {4, 32, ENC_TF32_PAIR, 2, KIND_TF32}; return true;
+        case NML_MATH_TF32: *m = {4, 32, ENC_TF32_HI, 1, KIND_TF32}; return true;
+    }
+    return false;
+}
+
+// Converts an activation tensor into the NHWC operand encoding of `mi` unless it already is one.
+// planes[0..1] receive the operand pointers, *cp the padded channel count.
+static int prepare_activation(const void* src, int dtype, int layout, int batch, int c, int h, int w,
+                              const MathInfo& mi, Bump& ws, cudaStream_t st, const void* planes[2], int* cp,
+                              float* colsum) {
+    const int align = 16 / mi.es;
+    const bool direct = (mi.enc == ENC_F16) && dtype == NML_F16 && (c % align == 0) &&
+                        (layout == NML_NHWC || (h == 1 && w == 1) || c == 1);
+    const size_t pixels = static_cast<size_t>(batch) * h * w;
+    if (direct) {
+        planes[0] = src;
+        planes[1] = nullptr;
+        *cp = c;
+        if (colsum && !ws.dry) {
+            int rows_per_block = 256;
+            dim3 grid(ceil_div(c, 256), static_cast<unsigned>((pixels + rows_per_block - 1) / rows_per_block));
+            colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
+                                                             rows_per_block);
+        }
+        return NML_OK;
+    }
+    const int Cp = static_cast<int>(round_up(c, align));
+    *cp = Cp;
+    void* p0 = ws.take(pixels * Cp * mi.es);
+    void* p1 = (mi.planes == 2) ? ws.take(pixels * Cp * mi.es) : nullptr;
+    planes[0] = p0;
+    planes[1] = p1;
+    if (ws.dry) return NML_OK;
+    if (!ws.fits()) return NML_ERR_WORKSPACE;
+    if (layout == NML_NCHW && !(h == 1 && w == 1)) {
+        dim3 grid(ceil_div(h * w, 64), ceil_div(Cp, 64), batch);
+        if (dtype == NML_F32)
+            nchw_to_nhwc_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), p0, p1, mi.enc, c, Cp,
+                                                            h * w, colsum);
+        else
+            nchw_to_nhwc_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), p0, p1, mi.enc, c,
+                                                             Cp, h * w, colsum);
+    } else {
+        size_t total = pixels * Cp;
+        int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 16));
+        if (dtype == NML_F32)
+            convert_rows_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(src), p0, p1, mi.enc, pixels,
+                                                              c, Cp);
+        else
+            convert_rows_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(src), p0, p1, mi.enc,
+                                                               pixels, c, Cp);
+        if (colsum) {
+            int rows_per_block = 256;
+            dim3 grid(ceil_div(c, 256), static_cast<unsigned>((pixels + rows_per_block - 1) / rows_per_block));
+            if (dtype == NML_F32)
+                colsum_rows_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), colsum, pixels, c,
+                                                                rows_per_block);
+            else
+                colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
+                                                                 rows_per_block);
+        }
+    }
+    NML_CUDA(cudaGetLastError());
+    return NML_OK;
+}
+
+// Picks a power-of-two pixel box (w, h, n) with 2^bits pixels that covers the grid with the
+// fewest boxes; ties go to the wider box.  box extents times the element stride stay <= 256.
+static void choose_box(int bits, int gw, int gh, int gn, int s_w, int s_h, int* wl, int* hl, int* nl) {
+    long long best = -1;
+    for (int a = bits; a >= 0; --a) {
+        if ((1 << a) * s_w > 256) continue;
+        for (int b = bits - a; b >= 0; --b) {
+            if ((1 << b) * s_h > 256) continue;
+            int c = bits - a - b;
+            if ((1 << c) > 256) continue;
+            long long tiles = 1ll * ceil_div(gw, 1 << a) * ceil_div(gh, 1 << b) * ceil_div(gn, 1 << c);
+            if (best < 0 || tiles < best) {
+                best = tiles;
+                *wl = a;
+                *hl = b;
+                *nl = c;
+            }
+        }
+    }
+}
+
+static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
+    const int stage_bytes = kStageABytes + P.bn * 128;
+    int stages = std::min(8, (232448 - 1024 - 256) / stage_bytes);
+    P.stages = stages;
+    size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024 + 256;
+    smem = std::max<size_t>(smem, 120 * 1024);  // one CTA per SM: each allocates its own TMEM
+    P.err = ds->err;
+    int grid = std::min(P.num_tiles, ds->sms);
+    if (grid <= 0) return NML_OK;
+    umma_conv_kernel<<<grid, kThreads, smem, st>>>(P);
+    NML_CUDA(cudaGetLastError());
+    ++g_launches;
+    return NML_OK;
+}
+
+// ------------------------------------------------------- fprop-like problems --
+struct FpropLike {
+    const void* a;
+    int a_dtype, a_layout, batch, a_c, a_h, a_w;
+    const void* w;
+    int w_dtype, d0, d1, kh, kw, k_is_dim0, w_direct;
+    int gather;  // 0: output pixel o reads input o*s - p + k*d; 1: output pixel o gathers from (o + p - k*d)/s
+    int s_h, s_w, p_h, p_w, d_h, d_w;
+    void* out;
+    int out_dtype, out_layout, out_c, out_h, out_w;
+    const void* bias;
+    int bias_dtype;
+    int math, round_f16;
+};
+
+static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
+    MathInfo mi;
+    if (!math_info(f.math, &mi)) return NML_ERR_INVALID;
+    const int T = f.kh * f.kw;
+    const int K = f.k_is_dim0 ? f.d0 : f.d1;
+    const int N = f.k_is_dim0 ? f.d1 : f.d0;
+    if (K != f.a_c || N != f.out_c) return NML_ERR_INVALID;
+    if (T > kMaxTaps || f.s_h * f.s_w > kMaxPhases) return NML_ERR_UNSUPPORTED;
+    if (f.batch <= 0 || f.a_c <= 0 || f.a_h <= 0 || f.a_w <= 0 || f.out_c <= 0 || f.out_h <= 0 || f.out_w <= 0)
+        return NML_ERR_INVALID;
+
+    DeviceState* ds = nullptr;
+    if (!ws.dry) {
+        int rc = device_state(&ds);
+        if (rc) return rc;
+    }
+    // activation operand
+    const void* a_planes[2];
+    int Cp = 0;
+    int rc = prepare_activation(f.a, f.a_dtype, f.a_layout, f.batch, f.a_c, f.a_h, f.a_w, mi, ws, st, a_planes, &Cp,
+                                nullptr);
+    if (rc) return rc;
+    // weight operand
+    const int c_blocks = ceil_div(K, mi.kb);
+    const int kp = c_blocks * mi.kb;
+    const int align = 16 / mi.es;
+    bool direct_w = f.w_direct && T == 1 && mi.enc == ENC_F16 && f.w_dtype == NML_F16 &&
+                    ((f.k_is_dim0 ? N : K) % align == 0);
+    const void* w_planes[2] = {f.w, nullptr};
+    int b_mn_major = 0;
+    if (direct_w) {
+        b_mn_major = f.k_is_dim0 ? 1 : 0;
+    } else {
+        size_t bytes = static_cast<size_t>(N) * T * kp * mi.es;
+        void* p0 = ws.take(bytes);
+        void* p1 = (mi.planes == 2) ? ws.take(bytes) : nullptr;
+        w_planes[0] = p0;
+        w_planes[1] = p1;
+        if (!ws.dry) {
+            if (!ws.fits()) return NML_ERR_WORKSPACE;
+            size_t total = static_cast<size_t>(N) * T * kp;
+            int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 8));
+            if (f.w_dtype == NML_F32)
+                repack_weight_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(f.w), p0, p1, mi.enc,
+                                                                   f.d0, f.d1, T, f.k_is_dim0, kp);
+            else
+                repack_weight_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(f.w), p0, p1, mi.enc,
+                                                                    f.d0, f.d1, T, f.k_is_dim0, kp);
+            NML_CUDA(cudaGetLastError());
+        }
+    }
+    // bias as fp32
+    const float* bias32 = static_cast<const float*>(f.bias);
+    if (f.bias && f.bias_dtype == NML_F16) {
+        float* b = static_cast<float*>(ws.take(sizeof(float) * N));
+        bias32 = b;
+        if (!ws.dry) {
+            if (!ws.fits()) return NML_ERR_WORKSPACE;
+            to_float_kernel<__half><<<ceil_div(N, 256), 256, 0, st>>>(static_cast<const __half*>(f.bias), b, N);
+        }
+    }
+    if (ws.dry) return NML_OK;
+    if (!ws.fits()) return NML_ERR_WORKSPACE;
+
+    KParams P;
+    memset(&P, 0, sizeof(P));
+    P.mode = MODE_FPROP;
+    P.out_mode = (f.out_layout == NML_NCHW && !(f.out_h == 1 && f.out_w == 1)) ? OUT_NCHW : OUT_NHWC;
+    P.kind = mi.kind;
+    P.passes = (mi.planes == 2) ? 3 : 1;
+    P.kb = mi.kb;
+    P.c_blocks = c_blocks;
+    P.a_mn_major = 0;
+    P.b_mn_major = b_mn_major;
+    P.batch = f.batch;
+    P.n_tiles = ceil_div(N, 256);
+    P.bn = static_cast<int>(round_up(ceil_div(N, P.n_tiles), b_mn_major ? 64 : 32));
+    P.out = f.out;
+    P.bias = bias32;
+    P.out_f16 = (f.out_dtype == NML_F16);
+    P.round_f16 = f.round_f16;
+    P.c_out = N;
+    P.out_h = f.out_h;
+    P.out_w = f.out_w;
+    P.ld_out = N;
+
+    // phases and taps
+    int n_taps = 0, n_phases = 0;
+    if (!f.gather) {
+        Phase& ph = P.phases[0];
+        ph.ph = ph.pw = 0;
+        ph.hq = f.out_h;
+        ph.wq = f.out_w;
+        ph.tap_begin = 0;
+        for (int kh = 0; kh < f.kh; ++kh)
+            for (int kw = 0; kw < f.kw; ++kw) {
+                Tap& t = P.taps[n_taps++];
+                t.dh = static_cast<short>(kh * f.d_h - f.p_h);
+                t.dw = static_cast<short>(kw * f.d_w - f.p_w);
+                t.wk = direct_w ? 0 : (kh * f.kw + kw) * kp;
+            }
+        ph.tap_count = static_cast<short>(n_taps);
+        n_phases = 1;
+        P.a_stride_h = f.s_h;
+        P.a_stride_w = f.s_w;
+        P.out_stride_h = P.out_stride_w = 1;
+    } else {
+        for (int ph_ = 0; ph_ < f.s_h; ++ph_)
+            for (int pw_ = 0; pw_ < f.s_w; ++pw_) {
+                if (ph_ >= f.out_h || pw_ >= f.out_w) continue;
+                Phase& ph = P.phases[n_phases++];
+                ph.ph = static_cast<short>(ph_);
+                ph.pw = static_cast<short>(pw_);
+                ph.hq = ceil_div(f.out_h - ph_, f.s_h);
+                ph.wq = ceil_div(f.out_w - pw_, f.s_w);
+                ph.tap_begin = static_cast<short>(n_taps);
+                for (int kh = 0; kh < f.kh; ++kh) {
+                    int nh = ph_ + f.p_h - kh * f.d_h;
+                    if (((nh % f.s_h) + f.s_h) % f.s_h != 0) continue;
+                    for (int kw = 0; kw < f.kw; ++kw) {
+                        int nw = pw_ + f.p_w - kw * f.d_w;
+                        if (((nw % f.s_w) + f.s_w) % f.s_w != 0) continue;
+                        Tap& t = P.taps[n_taps++];
+                        t.dh = static_cast<short>(nh / f.s_h);
+                        t.dw = static_cast<short>(nw / f.s_w);
+                        t.wk = direct_w ? 0 : (kh * f.kw + kw) * kp;
+                    }
+                }
+                ph.tap_count = static_cast<short>(n_taps - ph.tap_begin);
+            }
+        P.a_stride_h = P.a_stride_w = 1;
+        P.out_stride_h = f.s_h;
+        P.out_stride_w = f.s_w;
+    }
+    P.n_phases = n_phases;
+    // M-tile box from the largest phase grid
+    const int esw = f.gather ? 1 : f.s_w, esh = f.gather ? 1 : f.s_h;
+    choose_box(7, P.phases[0].wq, P.phases[0].hq, f.batch, esw, esh, &P.wb_log2, &P.hb_log2, &P.nb_log2);
+    int tiles = 0;
+    for (int p = 0; p < n_phases; ++p) {
+        Phase& ph = P.phases[p];
+        ph.tiles_w = ceil_div(ph.wq, 1 << P.wb_log2);
+        ph.tiles_h = ceil_div(ph.hq, 1 << P.hb_log2);
+        ph.tile_begin = tiles;
+        tiles += ph.tiles_w * ph.tiles_h * ceil_div(f.batch, 1 << P.nb_log2) * P.n_tiles;
+    }
+    P.num_tiles = tiles;
+
+    // tensor maps
+    for (int pl = 0; pl < mi.planes; ++pl) {
+        uint64_t adims[4] = {static_cast<uint64_t>(Cp), static_cast<uint64_t>(f.a_w), static_cast<uint64_t>(f.a_h),
+                             static_cast<uint64_t>(f.batch)};
+        uint32_t abox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>((1 << P.wb_log2) * esw),
+                            static_cast<uint32_t>((1 << P.hb_log2) * esh), static_cast<uint32_t>(1 << P.nb_log2)};
+        uint32_t aes[4] = {1, static_cast<uint32_t>(esw), static_cast<uint32_t>(esh), 1};
+        rc = encode_map(&P.tmA[pl], a_planes[pl], mi.es, 4, adims, abox, aes, true);
+        if (rc) return rc;
+        uint32_t one[2] = {1, 1};
+        if (!b_mn_major) {
+            uint64_t bdims[2] = {static_cast<uint64_t>(direct_w ? K : T * kp), static_cast<uint64_t>(N)};
+            uint32_t bbox[2] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(P.bn)};
+            rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 2, bdims, bbox, one, true);
+        } else {
+            uint64_t bdims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
+            uint32_t bbox[2] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(mi.kb)};
+            rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 2, bdims, bbox, one, true);
+        }
+        if (rc) return rc;
+    }
+    return launch_kernel(P, ds, st);
+}
+
+// ------------------------------------------------------- wgrad-like problems --
+struct WgradLike {
+    const void* patch;  // tensor the (tap-shifted, strided) patches are cut from
+    int patch_c, patch_h, patch_w;
+    const void* plain;  // tensor indexed by the pixel itself
+    int plain_c, plain_h, plain_w;
+    int dtype, layout, batch;
+    int kh, kw, s_h, s_w, p_h, p_w, d_h, d_w;
+    float* dw;  // [plain_c][patch_c][kh*kw]
+    float* colsum;
+    int colsum_of_patch;
+    int math;
+};
+
+static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
+    MathInfo mi;
+    if (!math_info(g.math, &mi)) return NML_ERR_INVALID;
+    const int T = g.kh * g.kw;
+    if (T > kMaxTaps) return NML_ERR_UNSUPPORTED;
+    if (g.batch <= 0 || g.patch_c <= 0 || g.plain_c <= 0 || g.patch_h <= 0 || g.patch_w <= 0 || g.plain_h <= 0 ||
+        g.plain_w <= 0)
+        return NML_ERR_INVALID;
+    DeviceState* ds = nullptr;
+    if (!ws.dry) {
+        int rc = device_state(&ds);
+        if (rc) return rc;
+        if (g.colsum) {
+            int nsum = g.colsum_of_patch ? g.patch_c : g.plain_c;
+            NML_CUDA(cudaMemsetAsync(g.colsum, 0, sizeof(float) * nsum, st));
+        }
+        NML_CUDA(cudaMemsetAsync(g.dw, 0, sizeof(float) * static_cast<size_t>(g.plain_c) * g.patch_c * T, st));
+    }
+    const void* pa[2];
+    const void* pb[2];
+    int cpa = 0, cpb = 0;
+    int rc = prepare_activation(g.patch, g.dtype, g.layout, g.batch, g.patch_c, g.patch_h, g.patch_w, mi, ws, st, pa,
+                                &cpa, g.colsum_of_patch ? g.colsum : nullptr);
+    if (rc) return rc;
+    rc = prepare_activation(g.plain, g.dtype, g.layout, g.batch, g.plain_c, g.plain_h, g.plain_w, mi, ws, st, pb, &cpb,
+                            g.colsum_of_patch ? nullptr : g.colsum);
+    if (rc) return rc;
+    if (ws.dry) return NML_OK;
+    if (!ws.fits()) return NML_ERR_WORKSPACE;
+
+    KParams P;
+    memset(&P, 0, sizeof(P));
+    P.mode = MODE_WGRAD;
+    P.kind = mi.kind;
+    P.passes = (mi.planes == 2) ? 3 : 1;
+    P.kb = mi.kb;
+    P.a_mn_major = 1;
+    P.b_mn_major = 1;
+    P.batch = g.batch;
+    P.c_blocks = ceil_div(g.patch_c, mi.kb);
+    P.groups_total = T * P.c_blocks;
+    P.c_patch = g.patch_c;
+    P.c_plain = g.plain_c;
+    P.n_taps = T;
+    P.n_tiles = ceil_div(g.plain_c, 256);
+    P.bn = static_cast<int>(round_up(ceil_div(g.plain_c, P.n_tiles), 64));
+    P.c_out = g.plain_c;
+    P.out = g.dw;
+    P.a_stride_h = g.s_h;
+    P.a_stride_w = g.s_w;
+    P.out_stride_h = P.out_stride_w = 1;
+    for (int kh = 0; kh < g.kh; ++kh)
+        for (int kw = 0; kw < g.kw; ++kw) {
+            Tap& t = P.taps[kh * g.kw + kw];
+            t.dh = static_cast<short>(kh * g.d_h - g.p_h);
+            t.dw = static_cast<short>(kw * g.d_w - g.p_w);
+            t.wk = kh * g.kw + kw;
+        }
+    const int bits = (mi.kb == 64) ? 6 : 5;
+    choose_box(bits, g.plain_w, g.plain_h, g.batch, g.s_w, g.s_h, &P.wb_log2, &P.hb_log2, &P.nb_log2);
+    P.ktiles_w = ceil_div(g.plain_w, 1 << P.wb_log2);
+    P.ktiles_h = ceil_div(g.plain_h, 1 << P.hb_log2);
+    P.kblocks_total = P.ktiles_w * P.ktiles_h * ceil_div(g.batch, 1 << P.nb_log2);
+    const int m_tiles = ceil_div(P.groups_total * mi.kb, kTileM);
+    const int mn_tiles = m_tiles * P.n_tiles;
+    int split = std::max(1, ds->sms / mn_tiles);
+    split = std::min(split, P.kblocks_total);
+    // every slice gets at least one K block
+    int per = ceil_div(P.kblocks_total, split);
+    split = ceil_div(P.kblocks_total, per);
+    P.split_k = split;
+    P.num_tiles = mn_tiles * split;
+
+    for (int pl = 0; pl < mi.planes; ++pl) {
+        uint64_t adims[4] = {static_cast<uint64_t>(cpa), static_cast<uint64_t>(g.patch_w),
+                             static_cast<uint64_t>(g.patch_h), static_cast<uint64_t>(g.batch)};
+        uint32_t abox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>((1 << P.wb_log2) * g.s_w),
+                            static_cast<uint32_t>((1 << P.hb_log2) * g.s_h), static_cast<uint32_t>(1 << P.nb_log2)};
+        uint32_t aes[4] = {1, static_cast<uint32_t>(g.s_w), static_cast<uint32_t>(g.s_h), 1};
+        rc = encode_map(&P.tmA[pl], pa[pl], mi.es, 4, adims, abox, aes, true);
+        if (rc) return rc;
+        uint64_t bdims[4] = {static_cast<uint64_t>(cpb), static_cast<uint64_t>(g.plain_w),
+                             static_cast<uint64_t>(g.plain_h), static_cast<uint64_t>(g.batch)};
+        uint32_t bbox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(1 << P.wb_log2),
+                            static_cast<uint32_t>(1 << P.hb_log2), static_cast<uint32_t>(1 << P.nb_log2)};
+        uint32_t bes[4] = {1, 1, 1, 1};
+        rc = encode_map(&P.tmB[pl], pb[pl], mi.es, 4, bdims, bbox, bes, true);
+        if (rc) return rc;
+    }
+    return launch_kernel(P, ds, st);
+}
+
+// --------------------------------------------------------- layer -> problems --
+static bool conv_out_size(const nml_conv_desc* d, int* ho, int* wo) {
+    if (!d || d->stride_h <= 0 || d->stride_w <= 0 || d->dil_h <= 0 || d->dil_w <= 0 || d->kh <= 0 || d->kw <= 0 ||
+        d->pad_h < 0 || d->pad_w < 0)
+        return false;
+    if (!d->transposed) {
+        int nh = d->h + 2 * d->pad_h - d->dil_h * (d->kh - 1) - 1;
+        int nw = d->w + 2 * d->pad_w - d->dil_w * (d->kw - 1) - 1;
+        if (nh < 0 || nw < 0) return false;
+        *ho = nh / d->stride_h + 1;
+        *wo = nw / d->stride_w + 1;
+    } else {
+        *ho = (d->h - 1) * d->stride_h - 2 * d->pad_h + d->dil_h * (d->kh - 1) + 1 + d->outpad_h;
+        *wo = (d->w - 1) * d->stride_w - 2 * d->pad_w + d->dil_w * (d->kw - 1) + 1 + d->outpad_w;
+    }
+    return *ho > 0 && *wo > 0;
+}
+
+static int conv_pass(const nml_conv_desc* d, int pass, const void* in0, const void* in1, const void* bias, void* out,
+                     float* db, Bump& ws, cudaStream_t st) {
+    int ho, wo;
+    if (!conv_out_size(d, &ho, &wo)) return NML_ERR_INVALID;
+    const bool tr = d->transposed != 0;
+    if (pass == NML_PASS_BACKWARD_WEIGHT) {
+        // in0 = x, in1 = dy
+        WgradLike g;
+        memset(&g, 0, sizeof(g));
+        if (!tr) {
+            g.patch = in0; g.patch_c = d->c_in; g.patch_h = d->h; g.patch_w = d->w;
+            g.plain = in1; g.plain_c = d->c_out; g.plain_h = ho; g.plain_w = wo;
+            g.colsum_of_patch = 0;
+        } else {
+            g.patch = in1; g.patch_c = d->c_out; g.patch_h = ho; g.patch_w = wo;
+            g.plain = in0; g.plain_c = d->c_in; g.plain_h = d->h; g.plain_w = d->w;
+            g.colsum_of_patch = 1;
+        }
+        g.dtype = d->in_dtype; g.layout = d->in_layout; g.batch = d->batch;
+        g.kh = d->kh; g.kw = d->kw; g.s_h = d->stride_h; g.s_w = d->stride_w;
+        g.p_h = d->pad_h; g.p_w = d->pad_w; g.d_h = d->dil_h; g.d_w = d->dil_w;
+        g.dw = static_cast<float*>(out);
+        g.colsum = db;
+        g.math = d->math;
+        return run_wgrad_like(g, ws, st);
+    }
+    FpropLike f;
+    memset(&f, 0, sizeof(f));
+    // conv forward and convT backward-data are strided reads; conv backward-data and convT forward gather.
+    const bool forward = (pass == NML_PASS_FORWARD);
+    const bool reads_layer_input = forward;  // A is the layer input for forward, the output gradient otherwise
+    f.a = in0;
+    f.a_dtype = d->in_dtype; f.a_layout = d->in_layout; f.batch = d->batch;
+    if (reads_layer_input) { f.a_c = d->c_in; f.a_h = d->h; f.a_w = d->w; f.out_c = d->c_out; f.out_h = ho; f.out_w = wo; }
+    else                   { f.a_c = d->c_out; f.a_h = ho; f.a_w = wo; f.out_c = d->c_in; f.out_h = d->h; f.out_w = d->w; }
+    f.w = in1; f.w_dtype = d->w_dtype;
+    // weight source dims: conv [c_out][c_in][T], convT [c_in][c_out][T]
+    f.d0 = tr ? d->c_in : d->c_out;
+    f.d1 = tr ? d->c_out : d->c_in;
+    f.kh = d->kh; f.kw = d->kw;
+    // contraction channel is a_c: it is dim0 exactly when a_c names d0
+    f.k_is_dim0 = (forward == tr) ? 1 : 0;  // conv fwd: k=c_in=d1; conv bwd: k=c_out=d0; convT fwd: k=c_in=d0; convT bwd: k=c_out=d1
+    f.w_direct = 0;
+    f.gather = (forward == tr) ? 1 : 0;     // conv fwd 0, conv bwd 1, convT fwd 1, convT bwd 0
+    f.s_h = d->stride_h; f.s_w = d->stride_w; f.p_h = d->pad_h; f.p_w = d->pad_w; f.d_h = d->dil_h; f.d_w = d->dil_w;
+    f.out = out; f.out_dtype = d->out_dtype; f.out_layout = d->out_layout;
+    f.bias = forward ? bias : nullptr; f.bias_dtype = d->w_dtype;
+    f.math = d->math;
+    f.round_f16 = forward ? d->round_out_f16 : 0;
+    return run_fprop_like(f, ws, st);
+}
+
+static int linear_pass(const nml_linear_desc* d, int pass, const void* in0, const void* in1, const void* bias,
+                       void* out, float* db, Bump& ws, cudaStream_t st) {
+    if (!d || d->rows <= 0 || d->in_features <= 0 || d->out_features <= 0) return NML_ERR_INVALID;
+    if (pass == NML_PASS_BACKWARD_WEIGHT) {
+        WgradLike g;
+        memset(&g, 0, sizeof(g));
+        g.patch = in0; g.patch_c = d->in_features; g.patch_h = 1; g.patch_w = d->rows;
+        g.plain = in1; g.plain_c = d->out_features; g.plain_h = 1; g.plain_w = d->rows;
+        g.dtype = d->in_dtype; g.layout = NML_NHWC; g.batch = 1;
+        g.kh = g.kw = 1; g.s_h = g.s_w = 1; g.d_h = g.d_w = 1;
+        g.dw = static_cast<float*>(out);
+        g.colsum = db; g.colsum_of_patch = 0;
+        g.math = d->math;
+        return run_wgrad_like(g, ws, st);
+    }
+    FpropLike f;
+    memset(&f, 0, sizeof(f));
+    const bool forward = (pass == NML_PASS_FORWARD);
+    f.a = in0; f.a_dtype = d->in_dtype; f.a_layout = NML_NHWC; f.batch = 1; f.a_h = 1; f.a_w = d->rows;
+    f.a_c = forward ? d->in_features : d->out_features;
+    f.w = in1; f.w_dtype = d->w_dtype; f.d0 = d->out_features; f.d1 = d->in_features; f.kh = f.kw = 1;
+    f.k_is_dim0 = forward ? 0 : 1;
+    f.w_direct = 1;
+    f.gather = 0;
+    f.s_h = f.s_w = 1; f.d_h = f.d_w = 1;
+    f.out = out; f.out_dtype = d->out_dtype; f.out_layout = NML_NHWC;
+    f.out_c = forward ? d->out_features : d->in_features; f.out_h = 1; f.out_w = d->rows;
+    f.bias = forward ? bias : nullptr; f.bias_dtype = d->w_dtype;
+    f.math = d->math;
+    f.round_f16 = forward ? d->round_out_f16 : 0;
+    return run_fprop_like(f, ws, st);
+}
+
+// Grow-only per-device workspace for the reference-shaped entry points.
+struct RefWorkspace {
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+static RefWorkspace g_ref_ws[64];
+
+static int ref_workspace(size_t need, void** out) {
+    int dev = 0;
+    NML_CUDA(cudaGetDevice(&dev));
+    RefWorkspace& w = g_ref_ws[dev];
+    if (need > w.bytes) {
+        if (w.ptr) {
+            NML_CUDA(cudaDeviceSynchronize());
+            NML_CUDA(cudaFree(w.ptr));
+            w.ptr = nullptr;
+            w.bytes = 0;
+        }
+        size_t grow = round_up(need + need / 4, 1 << 20);
+        NML_CUDA(cudaMalloc(&w.ptr, grow));
+        w.bytes = grow;
+    }
+    *out = w.ptr;
+    return NML_OK;
+}
+
+__global__ void tma_box_probe_kernel(const __grid_constant__ CUtensorMap tm, int c0, int c1, int c2, int c3,
+                                     uint32_t bytes, uint8_t* out, int* err) {
+    extern __shared__ __align__(1024) uint8_t box_smem[];
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        fence_mbar_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        mbar_arrive_expect_tx(smem_u32(&bar), bytes);
+        tma_load_4d(smem_u32(box_smem), &tm, smem_u32(&bar), c0, c1, c2, c3);
+    }
+    bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, err, ERR_WAIT_FULL);
+    if (ok)
+        for (uint32_t i = threadIdx.x; i < bytes; i += blockDim.x) out[i] = box_smem[i];
+}
+
+}  // namespace nml
+
+using namespace nml;
+
+// ---------------------------------------------------------------- C ABI -------
+extern "C" {
+
+const char* nml_status_string(int status) {
+    switch (status) {
+        case NML_OK: return "ok";
+        case NML_ERR_INVALID: return "invalid argument";
+        case NML_ERR_WORKSPACE: return "workspace too small";
+        case NML_ERR_CUDA: return g_last_error[0] ? g_last_error : "CUDA error";
+        case NML_ERR_UNSUPPORTED: return "unsupported configuration";
+        case NML_ERR_DEVICE: return "a kernel abandoned a bounded wait";
+    }
+    return "unknown status";
+}
+
+int nml_conv_output_size(const nml_conv_desc* d, int* h_out, int* w_out) {
+    if (!d || !h_out || !w_out) return NML_ERR_INVALID;
+    return conv_out_size(d, h_out, w_out) ? NML_OK : NML_ERR_INVALID;
+}
+
+int nml_conv_workspace_size(const nml_conv_desc* d, int pass, size_t* bytes) {
+    if (!d || !bytes) return NML_ERR_INVALID;
+    Bump ws{nullptr, 0, 0, true};
+    int rc = conv_pass(d, pass, nullptr, nullptr, d, nullptr, nullptr, ws, nullptr);
+    *bytes = round_up(ws.off, 256);
+    return rc;
+}
+
+int nml_linear_workspace_size(const nml_linear_desc* d, int pass, size_t* bytes) {
+    if (!d || !bytes) return NML_ERR_INVALID;
+    Bump ws{nullptr, 0, 0, true};
+    int rc = linear_pass(d, pass, nullptr, nullptr, d, nullptr, nullptr, ws, nullptr);
+    *bytes = round_up(ws.off, 256);
+    return rc;
+}
+
+int nml_conv_forward(const nml_conv_desc* d, const void* x, const void* w, const void* bias, void* y,
+                     void* workspace, size_t workspace_bytes, void* stream) {
+    if (!d || !x || !w || !y) return NML_ERR_INVALID;
+    Bump ws{static_cast<uint8_t*>(workspace), 0, workspace ? workspace_bytes : 0, false};
+    return conv_pass(d, NML_PASS_FORWARD, x, w, bias, y, nullptr, ws, static_cast<cudaStream_t>(stream));
+}
+
+int nml_conv_backward_data(const nml_conv_desc* d, const void* dy, const void* w, void* dx, void* workspace,
+                           size_t workspace_bytes, void* stream) {
+    if (!d || !dy || !w || !dx) return NML_ERR_INVALID;
+    Bump ws{static_cast<uint8_t*>(workspace), 0, workspace ? workspace_bytes : 0, false};
+    return conv_pass(d, NML_PASS_BACKWARD_DATA, dy, w, nullptr, dx, nullptr, ws, static_cast<cudaStream_t>(stream));
+}
+
+int nml_conv_backward_weight(const nml_conv_desc* d, const void* x, const void* dy, float* dw, float* db,
+                             void* workspace, size_t workspace_bytes, void* stream) {
+    if (!d || !x || !dy || !dw) return NML_ERR_INVALID;
+    Bump ws{static_cast<uint8_t*>(workspace), 0, workspace ? workspace_bytes : 0, false};
+    return conv_pass(d, NML_PASS_BACKWARD_WEIGHT, x, dy, nullptr, dw, db, ws, static_cast<cudaStream_t>(stream));
+}
+
+int nml_linear_forward(const nml_linear_desc* d, const void* x, const void* w, const void* bias, void* y,
+                       void* workspace, size_t workspace_bytes, void* stream) {
+    if (!d || !x || !w || !y) return NML_ERR_INVALID;
+    Bump ws{static_cast<uint8_t*>(workspace), 0, workspace ? workspace_bytes : 0, false};
+    return linear_pass(d, NML_PASS_FORWARD, x, w, bias, y, nullptr, ws, static_cast<cudaStream_t>(stream));
+}
+
+int nml_linear_backward_data(const nml_linear_desc* d, const void* dy, const void* w, void* dx, void* workspace,
+                             size_t workspace_bytes, void* stream) {
+    if (!d || !dy || !w || !dx) return NML_ERR_INVALID;
+    Bump ws{static_cast<uint8_t*>(workspace), 0, workspace ? workspace_bytes : 0, false};
+    return linear_pass(d, NML_PASS_BACKWARD_DATA, dy, w, nullptr, dx, nullptr, ws,
+                       static_cast<cudaStream_t>(stream));
+}
+
+int nml_linear_backward_weight(const nml_linear_desc* d, const void* x, const void* dy, float* dw, float* db,
+                               void* workspace, size_t workspace_bytes, void* stream) {
+    if (!d || !x || !dy || !dw) return NML_ERR_INVALID;
+    Bump ws{static_cast<uint8_t*>(workspace), 0, workspace ? workspace_bytes : 0, false};
+    return linear_pass(d, NML_PASS_BACKWARD_WEIGHT, x, dy, nullptr, dw, db, ws, static_cast<cudaStream_t>(stream));
+}
+
+int nml_device_status(int* code) {
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    NML_CUDA(cudaDeviceSynchronize());
+    int v = 0;
+    NML_CUDA(cudaMemcpy(&v, ds->err, sizeof(int), cudaMemcpyDeviceToHost));
+    if (code) *code = v;
+    if (v != 0) {
+        NML_CUDA(cudaMemset(ds->err, 0, sizeof(int)));
+        return NML_ERR_DEVICE;
+    }
+    return NML_OK;
+}
+
+long long nml_launch_count(void) { return g_launches; }
+
+// ---- reference-shaped entry points ----
+static void fill_conv_desc(nml_conv_desc* d, int transposed, int B, int C_in, int H, int W, int C_out, int KH,
+                           int KW, int sh, int sw, int ph, int pw, int dh, int dw, int oph, int opw) {
+    memset(d, 0, sizeof(*d));
+    d->batch = B; d->c_in = C_in; d->h = H; d->w = W; d->c_out = C_out; d->kh = KH; d->kw = KW;
+    d->stride_h = sh; d->stride_w = sw; d->pad_h = ph; d->pad_w = pw; d->dil_h = dh; d->dil_w = dw;
+    d->outpad_h = oph; d->outpad_w = opw; d->transposed = transposed;
+    d->in_layout = d->out_layout = NML_NCHW;
+}
+
+static int ref_run_conv(nml_conv_desc* d, int pass, const void* in0, const void* in1, const void* bias,
+                        size_t out_bytes, uintptr_t* result) {
+    if (!result) return NML_ERR_INVALID;
+    size_t need = 0;
+    int rc = nml_conv_workspace_size(d, pass, &need);
+    if (rc) return rc;
+    void* ws = nullptr;
+    rc = ref_workspace(need, &ws);
+    if (rc) return rc;
+    void* out = nullptr;
+    NML_CUDA(cudaMalloc(&out, out_bytes ? out_bytes : 1));
+    Bump b{static_cast<uint8_t*>(ws), 0, need, false};
+    rc = conv_pass(d, pass, in0, in1, bias, out, nullptr, b, nullptr);
+    if (rc) {
+        cudaFree(out);
+        return rc;
+    }
+    *result = reinterpret_cast<uintptr_t>(out);
+    return NML_OK;
+}
+
+static int ref_forward(int transposed, uintptr_t input_ptr, uintptr_t weight_ptr, uintptr_t bias_ptr,
+                       size_t output_size, int B, int C_in, int H, int W, int C_out, int KH, int KW, int sh, int sw,
+                       int ph, int pw, int dh, int dw, int oph, int opw, int groups, int dtype, int half_precision,
+                       uintptr_t* result) {
+    if (groups != 1) return NML_ERR_UNSUPPORTED;
+    if (dtype != NML_F32 && dtype != NML_F16) return NML_ERR_INVALID;
+    nml_conv_desc d;
+    fill_conv_desc(&d, transposed, B, C_in, H, W, C_out, KH, KW, sh, sw, ph, pw, dh, dw, oph, opw);
+    d.in_dtype = d.out_dtype = d.w_dtype = dtype;
+    d.math = (half_precision || dtype == NML_F16) ? NML_MATH_F16 : NML_MATH_3XTF32;
+    d.round_out_f16 = half_precision ? 1 : 0;
+    int ho, wo;
+    if (!conv_out_size(&d, &ho, &wo)) return NML_ERR_INVALID;
+    size_t elems = static_cast<size_t>(B) * C_out * ho * wo;
+    if (output_size != 0 && output_size != elems) return NML_ERR_INVALID;
+    return ref_run_conv(&d, NML_PASS_FORWARD, reinterpret_cast<const void*>(input_ptr),
+                        reinterpret_cast<const void*>(weight_ptr), reinterpret_cast<const void*>(bias_ptr),
+                        elems * (dtype == NML_F16 ? 2 : 4), result);
+}
+
+int nml_ref_conv2d(uintptr_t input_ptr, size_t input_size, uintptr_t weight_ptr, size_t weight_size,
+                   uintptr_t bias_ptr, size_t bias_size, size_t output_size, int B, int C_in, int H, int W, int C_out,
+                   int KH, int KW, int stride_h, int stride_w, int padding_h, int padding_w, int dilation_h,
+                   int dilation_w, int groups, int dtype, int half_precision, uintptr_t* result) {
+    (void)input_size; (void)weight_size; (void)bias_size;
+    return ref_forward(0, input_ptr, weight_ptr, bias_ptr, output_size, B, C_in, H, W, C_out, KH, KW, stride_h,
+                       stride_w, padding_h, padding_w, dilation_h, dilation_w, 0, 0, groups, dtype, half_precision,
+                       result);
+}
+
+int nml_ref_conv_transpose2d(uintptr_t input_ptr, size_t input_size, uintptr_t weight_ptr, size_t weight_size,
+                             uintptr_t bias_ptr, size_t bias_size, size_t output_size, int B, int C_in, int H, int W,
+                             int C_out, int KH, int KW, int stride_h, int stride_w, int padding_h, int padding_w,
+                             int dilation_h, int dilation_w, int output_padding_h, int output_padding_w, int groups,
+                             int dtype, int half_precision, uintptr_t* result) {
+    (void)input_size; (void)weight_size; (void)bias_size;
+    return ref_forward(1, input_ptr, weight_ptr, bias_ptr, output_size, B, C_in, H, W, C_out, KH, KW, stride_h,
+                       stride_w, padding_h, padding_w, dilation_h, dilation_w, output_padding_h, output_padding_w,
+                       groups, dtype, half_precision, result);
+}
+
+// The backward entry points receive H_out/W_out explicitly; for ConvTranspose2d they determine
+// the output padding, which the reference's signature does not pass.
+static int ref_backward(int transposed, int pass, uintptr_t p0, uintptr_t p1, int B, int C_in, int H, int W,
+                        int C_out, int KH, int KW, int H_out, int W_out, int sh, int sw, int ph, int pw, int dh,
+                        int dw, int dtype, uintptr_t* result) {
+    if (dtype != NML_F32 && dtype != NML_F16) return NML_ERR_INVALID;
+    nml_conv_desc d;
+    fill_conv_desc(&d, transposed, B, C_in, H, W, C_out, KH, KW, sh, sw, ph, pw, dh, dw, 0, 0);
+    int ho, wo;
+    if (!conv_out_size(&d, &ho, &wo)) return NML_ERR_INVALID;
+    if (transposed) {
+        d.outpad_h = H_out - ho;
+        d.outpad_w = W_out - wo;
+        if (d.outpad_h < 0 || d.outpad_w < 0 || d.outpad_h >= sh + dh || d.outpad_w >= sw + dw) return NML_ERR_INVALID;
+    } else if (ho != H_out || wo != W_out) {
+        return NML_ERR_INVALID;
+    }
+    d.in_dtype = d.w_dtype = dtype;
+    d.out_dtype = NML_F32;
+    d.math = (dtype == NML_F16) ? NML_MATH_F16 : NML_MATH_3XTF32;
+    size_t elems;
+    const void *in0, *in1;
+    if (pass == NML_PASS_BACKWARD_DATA) {
+        elems = static_cast<size_t>(B) * C_in * H * W;
+        in0 = reinterpret_cast<const void*>(p0);  // out_grad
+        in1 = reinterpret_cast<const void*>(p1);  // weight
+    } else {
+        elems = static_cast<size_t>(C_out) * C_in * KH * KW;
+        in0 = reinterpret_cast<const void*>(p1);  // input
+        in1 = reinterpret_cast<const void*>(p0);  // out_grad
+    }
+    return ref_run_conv(&d, pass, in0, in1, nullptr, elems * 4, result);
+}
+
+int nml_ref_conv2d_backward_input(uintptr_t out_grad_ptr, uintptr_t weight_ptr, int B, int C_in, int H, int W,
+                                  int C_out, int KH, int KW, int H_out, int W_out, int stride_h, int stride_w,
+                                  int padding_h, int padding_w, int dilation_h, int dilation_w, int groups, int dtype,
+                                  uintptr_t* result) {
+    if (groups != 1) return NML_ERR_UNSUPPORTED;
+    return ref_backward(0, NML_PASS_BACKWARD_DATA, out_grad_ptr, weight_ptr, B, C_in, H, W, C_out, KH, KW, H_out,
+                        W_out, stride_h, stride_w, padding_h, padding_w, dilation_h, dilation_w, dtype, result);
+}
+
+int nml_ref_conv_transpose2d_backward_input(uintptr_t out_grad_ptr, uintptr_t weight_ptr, int B, int C_in, int H,
+                                            int W, int C_out, int KH, int KW, int H_out, int W_out, int stride_h,
+                                            int stride_w, int padding_h, int padding_w, int dilation_h,
+                                            int dilation_w, int groups, int dtype, uintptr_t* result) {
+    if (groups != 1) return NML_ERR_UNSUPPORTED;
+    return ref_backward(1, NML_PASS_BACKWARD_DATA, out_grad_ptr, weight_ptr, B, C_in, H, W, C_out, KH, KW, H_out,
+                        W_out, stride_h, stride_w, padding_h, padding_w, dilation_h, dilation_w, dtype, result);
+}
+
+int nml_ref_conv2d_backward_weight(uintptr_t out_grad_ptr, uintptr_t input_ptr, int B, int C_in, int H, int W,
+                                   int C_out, int KH, int KW, int H_out, int W_out, int stride_h, int stride_w,
+                                   int padding_h, int padding_w, int dilation_h, int dilation_w, int dtype,
+                                   uintptr_t* result) {
+    return ref_backward(0, NML_PASS_BACKWARD_WEIGHT, out_grad_ptr, input_ptr, B, C_in, H, W, C_out, KH, KW, H_out,
+                        W_out, stride_h, stride_w, padding_h, padding_w, dilation_h, dilation_w, dtype, result);
+}
+
+int nml_ref_conv_transpose2d_backward_weight(uintptr_t out_grad_ptr, uintptr_t input_ptr, int B, int C_in, int H,
+                                             int W, int C_out, int KH, int KW, int H_out, int W_out, int stride_h,
+                                             int stride_w, int padding_h, int padding_w, int dilation_h,
+                                             int dilation_w, int dtype, uintptr_t* result) {
+    return ref_backward(1, NML_PASS_BACKWARD_WEIGHT, out_grad_ptr, input_ptr, B, C_in, H, W, C_out, KH, KW, H_out,
+                        W_out, stride_h, stride_w, padding_h, padding_w, dilation_h, dilation_w, dtype, result);
+}
+
+int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_rank, const int* b_shape, int b_rank,
+                   int dtype, uintptr_t* result) {
+    if (!a_shape || !b_shape || a_rank < 2 || b_rank < 2 || !result) return NML_ERR_INVALID;
+    if (dtype != NML_F32 && dtype != NML_F16) return NML_ERR_INVALID;
+    const int M = a_shape[a_rank - 2], K = a_shape[a_rank - 1], N = b_shape[b_rank - 1];
+    if (b_shape[b_rank - 2] != K) return NML_ERR_INVALID;
+    size_t batch = 1;
+    for (int i = 0; i < a_rank - 2; ++i) batch *= a_shape[i];
+    size_t b_batch = 1;
+    for (int i = 0; i < b_rank - 2; ++i) b_batch *= b_shape[i];
+    // A 2-D right operand is shared by every batch entry; a batched one must match.
+    if (b_batch != 1 && b_batch != batch) return NML_ERR_INVALID;
+    const int es = (dtype == NML_F16) ? 2 : 4;
+    // C = A * B with B [K][N]: the backward-data form of a Linear layer whose weight is B.
+    nml_linear_desc d;
+    memset(&d, 0, sizeof(d));
+    d.rows = M; d.out_features = K; d.in_features = N;
+    d.in_dtype = d.out_dtype = d.w_dtype = dtype;
+    d.math = (dtype == NML_F16) ? NML_MATH_F16 : NML_MATH_3XTF32;
+    size_t need = 0;
+    int rc = nml_linear_workspace_size(&d, NML_PASS_BACKWARD_DATA, &need);
+    if (rc) return rc;
+    void* ws = nullptr;
+    rc = ref_workspace(need, &ws);
+    if (rc) return rc;
+    void* out = nullptr;
+    NML_CUDA(cudaMalloc(&out, batch * M * N * es));
+    for (size_t b = 0; b < batch; ++b) {
+        const uint8_t* A = reinterpret_cast<const uint8_t*>(a_ptr) + b * M * K * es;
+        const uint8_t* Bm = reinterpret_cast<const uint8_t*>(b_ptr) + (b_batch == 1 ? 0 : b) * K * N * es;
+        uint8_t* C = static_cast<uint8_t*>(out) + b * M * N * es;
+        Bump bump{static_cast<uint8_t*>(ws), 0, need, false};
+        rc = linear_pass(&d, NML_PASS_BACKWARD_DATA, A, Bm, nullptr, C, nullptr, bump, nullptr);
+        if (rc) {
+            cudaFree(out);
+            return rc;
+        }
+    }
+    *result = reinterpret_cast<uintptr_t>(out);
+    return NML_OK;
+}
+
+int nml_debug_tma_box(const void* tensor, int elem_bytes, const int dims[4], const int box[4],
+                      const int elem_strides[4], const int coords[4], void* out, size_t out_bytes, void* stream) {
+    if (!tensor || !out || (elem_bytes != 2 && elem_bytes != 4)) return NML_ERR_INVALID;
+    DeviceState* ds = nullptr;
+    int rc = device_state(&ds);
+    if (rc) return rc;
+    uint64_t gd[4];
+    uint32_t bx[4], es[4];
+    size_t bytes = elem_bytes;
+    for (int i = 0; i < 4; ++i) {
+        gd[i] = dims[i];
+        bx[i] = box[i];
+        es[i] = elem_strides[i];
+        bytes *= (box[i] + elem_strides[i] - 1) / elem_strides[i];
+    }
+    if (bytes > 96 * 1024 || bytes > out_bytes || bytes % 16) return NML_ERR_INVALID;
+    CUtensorMap tm;
+    rc = encode_map(&tm, tensor, elem_bytes, 4, gd, bx, es, false);
+    if (rc) return rc;
+    static bool attr = false;
+    if (!attr) {
+        NML_CUDA(cudaFuncSetAttribute(tma_box_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+        attr = true;
+    }
+    tma_box_probe_kernel<<<1, 128, bytes + 1024, static_cast<cudaStream_t>(stream)>>>(
+        tm, coords[0], coords[1], coords[2], coords[3], static_cast<uint32_t>(bytes), static_cast<uint8_t*>(out),
+        ds->err);
+    NML_CUDA(cudaGetLastError());
+    return NML_OK;
+}
+
+}  // extern "C"

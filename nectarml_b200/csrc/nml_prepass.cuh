@@ -1,0 +1,128 @@
+// Memory-bound helper kernels around the contraction kernel: layout / precision
+// conversion of activations (NCHW -> NHWC, fp32 -> fp16 or the tf32 hi/lo pair of the
+// 3xTF32 split, with the bias-gradient column sum folded into the same pass over dY),
+// weight repacking into the K-major [n][tap][k] operand, and small utilities.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace nml {
+
+__device__ __forceinline__ float to_tf32_rna(float x) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+__device__ __forceinline__ float load_as_float(const float* p, size_t i) { return p[i]; }
+__device__ __forceinline__ float load_as_float(const __half* p, size_t i) { return __half2float(p[i]); }
+
+// Output encodings of the conversion kernels.
+enum { ENC_F16 = 0, ENC_TF32_PAIR = 1, ENC_TF32_HI = 2 };
+
+__device__ __forceinline__ void store_enc(int enc, void* out0, void* out1, size_t i, float v) {
+    if (enc == ENC_F16) {
+        reinterpret_cast<__half*>(out0)[i] = __float2half_rn(v);
+    } else {
+        float hi = to_tf32_rna(v);
+        reinterpret_cast<float*>(out0)[i] = hi;
+        if (enc == ENC_TF32_PAIR) reinterpret_cast<float*>(out1)[i] = to_tf32_rna(v - hi);
+    }
+}
+
+// in  [N][C][HW] (NCHW)  ->  out [N][HW][Cp] (NHWC, channels zero-padded to Cp).
+// Tile of 64 channels x 64 pixels through shared memory; loads coalesce along pixels,
+// stores along channels.  When `colsum` is given, the per-channel sum over all pixels
+// (the bias gradient) is accumulated with one atomic per channel per tile.
+template <typename TIn>
+__global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict__ in, void* out0,
+                                                           void* out1, int enc, int C, int Cp, int HW,
+                                                           float* colsum) {
+    __shared__ float tile[64][65];
+    const int n = blockIdx.z;
+    const int c0 = blockIdx.y * 64;
+    const int p0 = blockIdx.x * 64;
+    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;  // 64 x 4
+    const TIn* src = in + static_cast<size_t>(n) * C * HW;
+    for (int c = ty; c < 64; c += 4) {
+        float v = 0.f;
+        if (c0 + c < C && p0 + tx < HW) v = load_as_float(src, static_cast<size_t>(c0 + c) * HW + p0 + tx);
+        tile[c][tx] = v;
+    }
+    __syncthreads();
+    if (colsum != nullptr && threadIdx.x < 64 && c0 + threadIdx.x < C) {
+        float s = 0.f;
+        for (int p = 0; p < 64; ++p) s += tile[threadIdx.x][(p + threadIdx.x) & 63];
+        atomicAdd(colsum + c0 + threadIdx.x, s);
+    }
+    // store: channel index fastest
+    for (int p = ty; p < 64; p += 4) {
+        int c = c0 + tx;
+        if (p0 + p < HW && c < Cp) {
+            size_t o = (static_cast<size_t>(n) * HW + p0 + p) * Cp + c;
+            store_enc(enc, out0, out1, o, tile[tx][p]);
+        }
+    }
+}
+
+// Row-major [R][C] -> [R][Cp] with encoding change (fp32/fp16 -> fp16 / tf32 pair), zero pad.
+template <typename TIn>
+__global__ void __launch_bounds__(256) convert_rows_kernel(const TIn* __restrict__ in, void* out0,
+                                                           void* out1, int enc, size_t R, int C, int Cp) {
+    size_t total = R * static_cast<size_t>(Cp);
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t r = i / Cp;
+        int c = static_cast<int>(i - r * Cp);
+        float v = (c < C) ? load_as_float(in, r * C + c) : 0.f;
+        store_enc(enc, out0, out1, i, v);
+    }
+}
+
+// Column sums of a row-major [R][C] matrix (bias gradient of Linear, or of an NHWC dY).
+template <typename TIn>
+__global__ void __launch_bounds__(256) colsum_rows_kernel(const TIn* __restrict__ in, float* colsum,
+                                                          size_t R, int C, int rows_per_block) {
+    size_t r0 = static_cast<size_t>(blockIdx.y) * rows_per_block;
+    size_t r1 = r0 + rows_per_block < R ? r0 + rows_per_block : R;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < C; c += gridDim.x * blockDim.x) {
+        float s = 0.f;
+        for (size_t r = r0; r < r1; ++r) s += load_as_float(in, r * C + c);
+        atomicAdd(colsum + c, s);
+    }
+}
+
+// Weights [D0][D1][T] -> K-major operand dst[n][t][kp]:
+//   k_is_dim0 == 0 : n = D0 index, k = D1 index   (Conv2d forward, ConvTranspose2d dgrad)
+//   k_is_dim0 == 1 : n = D1 index, k = D0 index   (Conv2d dgrad, ConvTranspose2d forward)
+// k is zero-padded to kp per tap so that no K block straddles two taps.
+template <typename TIn>
+__global__ void __launch_bounds__(256) repack_weight_kernel(const TIn* __restrict__ w, void* out0,
+                                                            void* out1, int enc, int D0, int D1, int T,
+                                                            int k_is_dim0, int kp) {
+    const int NN = k_is_dim0 ? D1 : D0;
+    const int KK = k_is_dim0 ? D0 : D1;
+    size_t total = static_cast<size_t>(NN) * T * kp;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        int k = static_cast<int>(i % kp);
+        size_t r = i / kp;
+        int t = static_cast<int>(r % T);
+        int n = static_cast<int>(r / T);
+        float v = 0.f;
+        if (k < KK) {
+            size_t d0 = k_is_dim0 ? k : n, d1 = k_is_dim0 ? n : k;
+            v = load_as_float(w, (d0 * D1 + d1) * T + t);
+        }
+        store_enc(enc, out0, out1, i, v);
+    }
+}
+
+template <typename TIn>
+__global__ void __launch_bounds__(256) to_float_kernel(const TIn* __restrict__ in, float* out, int n) {
+    int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out[i] = load_as_float(in, i);
+}
+
+}  // namespace nml

@@ -1,0 +1,508 @@
+// The one contraction kernel of this library: a persistent, warp-specialised
+// implicit-GEMM for sm_100a.  One CTA per SM walks a static list of output tiles.
+//
+//   warp 0      TMA producer   : tiled cp.async.bulk.tensor loads (never multicast) into a
+//                                ring of 128-byte-swizzled shared-memory stages
+//   warp 1      MMA issuer     : one thread issues tcgen05.mma, accumulators live in TMEM,
+//                                two TMEM buffers so the epilogue of tile i overlaps tile i+1
+//   warps 2..5  epilogue       : tcgen05.ld -> bias / rounding / cast -> global stores
+//
+// Two tile walks share the pipeline:
+//   MODE_FPROP  rows of the tile are output pixels (n, h, w) taken as one TMA box of the
+//               NHWC activation; the K loop runs over (tap, channel block) with stride,
+//               padding and dilation folded into the box coordinates (out-of-range reads are
+//               zero-filled by TMA).  Covers Conv2d forward, Conv2d input-gradient and
+//               ConvTranspose2d forward (one sub-problem per output phase, no col2im),
+//               ConvTranspose2d input-gradient, and plain GEMMs (Linear forward / dgrad)
+//               seen as a 1x1 convolution over an image of height 1.
+//   MODE_WGRAD  rows of the tile are (tap, patch channel), columns are the other tensor's
+//               channels, the K loop runs over pixels; both operands are MN-major boxes of the
+//               NHWC tensors.  Partial sums of the split-K slices are added with fp32 atomics.
+//               Covers Conv2d / ConvTranspose2d weight-gradient and Linear weight-gradient.
+#pragma once
+#include "nml_ptx.cuh"
+
+namespace nml {
+
+enum { MODE_FPROP = 0, MODE_WGRAD = 1 };
+enum { OUT_NHWC = 0, OUT_NCHW = 1 };
+enum { KIND_F16 = 0, KIND_TF32 = 2 };
+
+// Error codes written to the status word by a kernel that gave up on a wait.
+enum {
+    ERR_WAIT_EMPTY = 101,
+    ERR_WAIT_FULL = 102,
+    ERR_WAIT_TMEM_EMPTY = 103,
+    ERR_WAIT_TMEM_FULL = 104,
+    ERR_WAIT_DRAIN = 105
+};
+
+constexpr int kMaxPhases = 16;
+constexpr int kMaxTaps = 128;
+constexpr int kTileM = 128;
+constexpr int kStageABytes = kTileM * 128;
+constexpr int kThreads = 192;
+
+struct Tap {
+    short dh, dw;  // offset of this tap's box from the tile origin, in input pixels
+    int wk;        // first K index (fprop) / tap index (wgrad) of this tap in the weight operand
+};
+
+struct Phase {
+    short ph, pw;        // first output row / column of the phase
+    short tap_begin, tap_count;
+    int hq, wq;          // extent of the phase grid
+    int tiles_h, tiles_w;
+    int tile_begin;      // first tile id of this phase
+};
+
+struct KParams {
+    CUtensorMap tmA[2];  // fprop: activation (plane 0 = value or tf32 "hi", plane 1 = tf32 "lo")
+                         // wgrad: the tensor patches are cut from
+    CUtensorMap tmB[2];  // fprop: weights; wgrad: the plainly indexed tensor
+    int mode, out_mode;
+    int num_tiles, n_tiles;
+    int bn;              // UMMA N of one tile
+    int stages;
+    int a_mn_major, b_mn_major;
+    int kind;            // KIND_F16 / KIND_TF32
+    int passes;          // 1, or 3 for the 3xTF32 split (hi*hi, hi*lo, lo*hi)
+    int kb;              // elements per 128-byte row (64 fp16, 32 tf32)
+    int c_blocks;        // channel blocks of kb per tap (fprop) / per patch tensor (wgrad)
+    int wb_log2, hb_log2, nb_log2;  // fprop: M-tile box; wgrad: K-block pixel box
+    int batch;
+    int a_stride_h, a_stride_w;      // multiplier of the tile origin in A coordinates (conv stride)
+    int out_stride_h, out_stride_w;  // distance between neighbouring outputs of one phase
+    int n_phases;
+    // wgrad
+    int groups_total;    // taps * c_blocks column groups of kb patch channels
+    int split_k, kblocks_total, ktiles_h, ktiles_w;
+    int c_patch, c_plain, n_taps;
+    // epilogue
+    void* out;
+    const float* bias;
+    int out_f16, round_f16;
+    int c_out;           // valid columns
+    int out_h, out_w;    // output image
+    int ld_out;          // NHWC: elements between consecutive pixels
+    int* err;
+    Phase phases[kMaxPhases];
+    Tap taps[kMaxTaps];
+};
+
+__device__ __forceinline__ float round_through_f16(float v) {
+    return __half2float(__float2half_rn(v));
+}
+
+// Stores 32 (or fewer) consecutive output columns of one accumulator row.
+__device__ __forceinline__ void store_row_chunk(const KParams& P, const float (&v)[32], size_t row_off,
+                                                size_t col_stride, int cg, int ncols) {
+    if (P.out_mode == OUT_NHWC) {
+        if (P.out_f16) {
+            __half* o = reinterpret_cast<__half*>(P.out) + row_off + cg;
+            if (ncols == 32 && (P.ld_out & 7) == 0) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    uint4 pk;
+                    __half2 h0 = __floats2half2_rn(v[8 * q + 0], v[8 * q + 1]);
+                    __half2 h1 = __floats2half2_rn(v[8 * q + 2], v[8 * q + 3]);
+                    __half2 h2 = __floats2half2_rn(v[8 * q + 4], v[8 * q + 5]);
+                    __half2 h3 = __floats2half2_rn(v[8 * q + 6], v[8 * q + 7]);
+                    pk.x = *reinterpret_cast<uint32_t*>(&h0);
+                    pk.y = *reinterpret_cast<uint32_t*>(&h1);
+                    pk.z = *reinterpret_cast<uint32_t*>(&h2);
+                    pk.w = *reinterpret_cast<uint32_t*>(&h3);
+                    reinterpret_cast<uint4*>(o)[q] = pk;
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < ncols) o[j] = __float2half_rn(v[j]);
+            }
+        } else {
+            float* o = reinterpret_cast<float*>(P.out) + row_off + cg;
+            if (ncols == 32 && (P.ld_out & 3) == 0) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q)
+                    reinterpret_cast<float4*>(o)[q] =
+                        make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 32; ++j)
+                    if (j < ncols) o[j] = v[j];
+            }
+        }
+    } else {  // OUT_NCHW: lanes are consecutive pixels, so each column store coalesces
+        if (P.out_f16) {
+            __half* o = reinterpret_cast<__half*>(P.out) + row_off + static_cast<size_t>(cg) * col_stride;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols) o[j * col_stride] = __float2half_rn(v[j]);
+        } else {
+            float* o = reinterpret_cast<float*>(P.out) + row_off + static_cast<size_t>(cg) * col_stride;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+                if (j < ncols) o[j * col_stride] = v[j];
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_constant__ KParams P) {
+    extern __shared__ uint8_t smem_raw[];
+    // stages need 1024-byte alignment for the 128-byte swizzle pattern
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                               ~static_cast<uintptr_t>(1023));
+    const int stage_b_bytes = P.bn * 128;
+    const int stage_bytes = kStageABytes + stage_b_bytes;
+    uint8_t* ctrl = smem + P.stages * stage_bytes;
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);          // [stages]
+    uint64_t* empty_bar = full_bar + 8;                               // [stages]
+    uint64_t* tfull_bar = empty_bar + 8;                              // [2]
+    uint64_t* tempty_bar = tfull_bar + 2;                             // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t tmem_cols = (2 * P.bn <= 32) ? 32 : (2 * P.bn <= 64) ? 64 : (2 * P.bn <= 128) ? 128
+                               : (2 * P.bn <= 256) ? 256 : 512;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < P.stages; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&tfull_bar[b]), 1);
+            mbar_init(smem_u32(&tempty_bar[b]), 4);
+        }
+        *abort_flag = 0;
+        fence_mbar_init();
+        tma_prefetch_desc(&P.tmA[0]);
+        tma_prefetch_desc(&P.tmB[0]);
+        if (P.passes > 1) {
+            tma_prefetch_desc(&P.tmA[1]);
+            tma_prefetch_desc(&P.tmB[1]);
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), tmem_cols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int box_bytes = P.kb * 128;  // one MN-major box: kb k-rows of 128 bytes
+    const int wb = 1 << P.wb_log2, hb = 1 << P.hb_log2;
+
+    // ------------------------------------------------------------ producer --
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t parity = 0;
+            bool ok = true;
+            int issued = 0;
+            const uint32_t a_bytes = kStageABytes;
+            const uint32_t tx_bytes = a_bytes + stage_b_bytes;
+            for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x) {
+                if (P.mode == MODE_FPROP) {
+                    int p = 0;
+                    while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
+                    const Phase& ph = P.phases[p];
+                    int local = tile - ph.tile_begin;
+                    int ntile = local % P.n_tiles;
+                    int m = local / P.n_tiles;
+                    int tw = m % ph.tiles_w;
+                    int th = (m / ph.tiles_w) % ph.tiles_h;
+                    int tn = m / (ph.tiles_w * ph.tiles_h);
+                    int w0 = (tw << P.wb_log2) * P.a_stride_w;
+                    int h0 = (th << P.hb_log2) * P.a_stride_h;
+                    int n0 = tn << P.nb_log2;
+                    int per_pass = ph.tap_count * P.c_blocks;
+                    int k_iters = P.passes * per_pass;
+                    for (int it = 0; it < k_iters; ++it) {
+                        int pass = it / per_pass;
+                        int rem = it - pass * per_pass;
+                        int t = rem / P.c_blocks;
+                        int cb = rem - t * P.c_blocks;
+                        const Tap& tap = P.taps[ph.tap_begin + t];
+                        const CUtensorMap* ta = &P.tmA[pass == 2 ? 1 : 0];
+                        const CUtensorMap* tb = &P.tmB[pass == 1 ? 1 : 0];
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err,
+                                       ERR_WAIT_EMPTY)) {
+                            ok = false;
+                            break;
+                        }
+                        uint32_t fb = smem_u32(&full_bar[stage]);
+                        uint32_t sa = smem_u32(smem + stage * stage_bytes);
+                        uint32_t sb = sa + kStageABytes;
+                        mbar_arrive_expect_tx(fb, tx_bytes);
+                        tma_load_4d(sa, ta, fb, cb * P.kb, w0 + tap.dw, h0 + tap.dh, n0);
+                        if (!P.b_mn_major) {
+                            tma_load_2d(sb, tb, fb, tap.wk + cb * P.kb, ntile * P.bn);
+                        } else {
+                            int nb = P.bn / P.kb;
+                            for (int j = 0; j < nb; ++j)
+                                tma_load_2d(sb + j * box_bytes, tb, fb, ntile * P.bn + j * P.kb,
+                                            tap.wk + cb * P.kb);
+                        }
+                        ++issued;
+                        if (++stage == P.stages) {
+                            stage = 0;
+                            parity ^= 1;
+                        }
+                    }
+                } else {  // MODE_WGRAD
+                    int ntile = tile % P.n_tiles;
+                    int rest = tile / P.n_tiles;
+                    int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
+                    int mt = rest % m_tiles;
+                    int z = rest / m_tiles;
+                    int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
+                    int kb_begin = z * per;
+                    int kb_end = min(kb_begin + per, P.kblocks_total);
+                    int g_per_tile = kTileM / P.kb;
+                    int na = g_per_tile, nb = P.bn / P.kb;
+                    for (int pass = 0; ok && pass < P.passes; ++pass) {
+                        const CUtensorMap* ta = &P.tmA[pass == 2 ? 1 : 0];
+                        const CUtensorMap* tb = &P.tmB[pass == 1 ? 1 : 0];
+                        for (int kbi = kb_begin; kbi < kb_end; ++kbi) {
+                            int tw = kbi % P.ktiles_w;
+                            int th = (kbi / P.ktiles_w) % P.ktiles_h;
+                            int tn = kbi / (P.ktiles_w * P.ktiles_h);
+                            int w0 = tw << P.wb_log2, h0 = th << P.hb_log2, n0 = tn << P.nb_log2;
+                            if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag,
+                                           P.err, ERR_WAIT_EMPTY)) {
+                                ok = false;
+                                break;
+                            }
+                            uint32_t fb = smem_u32(&full_bar[stage]);
+                            uint32_t sa = smem_u32(smem + stage * stage_bytes);
+                            uint32_t sb = sa + kStageABytes;
+                            mbar_arrive_expect_tx(fb, tx_bytes);
+                            for (int g = 0; g < na; ++g) {
+                                int gi = min(mt * g_per_tile + g, P.groups_total - 1);
+                                int t = gi / P.c_blocks;
+                                int cib = gi - t * P.c_blocks;
+                                const Tap& tap = P.taps[t];
+                                tma_load_4d(sa + g * box_bytes, ta, fb, cib * P.kb,
+                                            w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0);
+                            }
+                            for (int j = 0; j < nb; ++j)
+                                tma_load_4d(sb + j * box_bytes, tb, fb, ntile * P.bn + j * P.kb, w0,
+                                            h0, n0);
+                            ++issued;
+                            if (++stage == P.stages) {
+                                stage = 0;
+                                parity ^= 1;
+                            }
+                        }
+                    }
+                }
+            }
+            if (!ok) {
+                // Unwinding: give copies already issued a bounded chance to land before the
+                // CTA's shared memory goes away.
+                int back = issued < P.stages ? issued : P.stages;
+                int s = stage;
+                uint32_t par = parity;
+                for (int i = 0; i < back; ++i) {
+                    if (--s < 0) {
+                        s = P.stages - 1;
+                        par ^= 1;
+                    }
+                    uint64_t t0 = globaltimer_ns();
+                    while (!mbar_try_wait(smem_u32(&full_bar[s]), par)) {
+                        if (globaltimer_ns() - t0 > 2000000ull) {
+                            atomicCAS(P.err, 0, ERR_WAIT_DRAIN);
+                            break;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    // ---------------------------------------------------------- MMA issuer --
+    else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = make_instr_desc(P.kind, P.a_mn_major, P.b_mn_major, kTileM, P.bn);
+            const uint32_t lbo_a = P.a_mn_major ? box_bytes : 16;
+            const uint32_t lbo_b = P.b_mn_major ? box_bytes : 16;
+            const int umma_k = (P.kind == KIND_F16) ? 16 : 8;
+            // descriptor start-address advance per UMMA, in 16-byte units
+            const uint32_t adv_a = P.a_mn_major ? (umma_k * 128) >> 4 : 2;
+            const uint32_t adv_b = P.b_mn_major ? (umma_k * 128) >> 4 : 2;
+            int stage = 0;
+            uint32_t parity = 0;
+            bool ok = true;
+            int titer = 0;
+            for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x, ++titer) {
+                int k_iters;
+                if (P.mode == MODE_FPROP) {
+                    int p = 0;
+                    while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
+                    k_iters = P.passes * P.phases[p].tap_count * P.c_blocks;
+                } else {
+                    int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
+                    int z = (tile / P.n_tiles) / m_tiles;
+                    int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
+                    int kb_begin = z * per;
+                    int kb_end = min(kb_begin + per, P.kblocks_total);
+                    k_iters = P.passes * max(kb_end - kb_begin, 0);
+                }
+                const int buf = titer & 1;
+                const uint32_t tpar = (titer >> 1) & 1;
+                if (!mbar_wait(smem_u32(&tempty_bar[buf]), tpar ^ 1, abort_flag, P.err,
+                               ERR_WAIT_TMEM_EMPTY)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * P.bn;
+                for (int it = 0; it < k_iters; ++it) {
+                    if (!mbar_wait(smem_u32(&full_bar[stage]), parity, abort_flag, P.err,
+                                   ERR_WAIT_FULL)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    uint32_t sa = smem_u32(smem + stage * stage_bytes);
+                    uint32_t sb = sa + kStageABytes;
+                    uint64_t adesc = make_smem_desc(sa, lbo_a, 1024);
+                    uint64_t bdesc = make_smem_desc(sb, lbo_b, 1024);
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        uint32_t acc = (it > 0 || j > 0) ? 1u : 0u;
+                        if (P.kind == KIND_F16)
+                            umma_f16(d_tmem, adesc + j * adv_a, bdesc + j * adv_b, idesc, acc);
+                        else
+                            umma_tf32(d_tmem, adesc + j * adv_a, bdesc + j * adv_b, idesc, acc);
+                    }
+                    umma_commit(smem_u32(&empty_bar[stage]));
+                    if (++stage == P.stages) {
+                        stage = 0;
+                        parity ^= 1;
+                    }
+                }
+                if (!ok) break;
+                if (k_iters > 0)
+                    umma_commit(smem_u32(&tfull_bar[buf]));
+                else
+                    mbar_arrive(smem_u32(&tfull_bar[buf]));
+            }
+        }
+    }
+    // ------------------------------------------------------------ epilogue --
+    else {
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+        const int row = quarter * 32 + lane;
+        bool ok = true;
+        int titer = 0;
+        for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x, ++titer) {
+            const int buf = titer & 1;
+            const uint32_t tpar = (titer >> 1) & 1;
+            // tile decode
+            int ntile, k_iters;
+            bool row_valid;
+            size_t row_off = 0;     // NHWC / wgrad: element offset of column 0; NCHW: pixel offset
+            size_t col_stride = 1;  // element distance between consecutive columns
+            if (P.mode == MODE_FPROP) {
+                int p = 0;
+                while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
+                const Phase& ph = P.phases[p];
+                int local = tile - ph.tile_begin;
+                ntile = local % P.n_tiles;
+                int m = local / P.n_tiles;
+                int tw = m % ph.tiles_w;
+                int th = (m / ph.tiles_w) % ph.tiles_h;
+                int tn = m / (ph.tiles_w * ph.tiles_h);
+                int iw = (tw << P.wb_log2) + (row & (wb - 1));
+                int ih = (th << P.hb_log2) + ((row >> P.wb_log2) & (hb - 1));
+                int n = (tn << P.nb_log2) + (row >> (P.wb_log2 + P.hb_log2));
+                row_valid = (iw < ph.wq) && (ih < ph.hq) && (n < P.batch);
+                int ow = ph.pw + P.out_stride_w * iw;
+                int oh = ph.ph + P.out_stride_h * ih;
+                k_iters = ph.tap_count;
+                if (P.out_mode == OUT_NHWC) {
+                    row_off = ((static_cast<size_t>(n) * P.out_h + oh) * P.out_w + ow) * P.ld_out;
+                    col_stride = 1;
+                } else {
+                    row_off = (static_cast<size_t>(n) * P.c_out * P.out_h + oh) * P.out_w + ow;
+                    col_stride = static_cast<size_t>(P.out_h) * P.out_w;
+                }
+            } else {
+                ntile = tile % P.n_tiles;
+                int rest = tile / P.n_tiles;
+                int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
+                int mt = rest % m_tiles;
+                int z = rest / m_tiles;
+                int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
+                k_iters = max(min(z * per + per, P.kblocks_total) - z * per, 0);
+                int gi = mt * (kTileM / P.kb) + row / P.kb;
+                int t = gi / P.c_blocks;
+                int cib = gi - t * P.c_blocks;
+                int pc = cib * P.kb + (row % P.kb);
+                row_valid = (gi < P.groups_total) && (pc < P.c_patch);
+                // dW[plain][patch][tap]
+                row_off = static_cast<size_t>(pc) * P.n_taps + t;
+                col_stride = static_cast<size_t>(P.c_patch) * P.n_taps;
+            }
+            if (!mbar_wait(smem_u32(&tfull_bar[buf]), tpar, abort_flag, P.err, ERR_WAIT_TMEM_FULL)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * P.bn;
+            const int col_base = ntile * P.bn;
+            for (int c0 = 0; c0 < P.bn; c0 += 32) {
+                if (col_base + c0 >= P.c_out) break;  // uniform across the warp
+                uint32_t r[32];
+                if (k_iters > 0) {
+                    tmem_ld_32x32(t_row + c0, r);
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r[j] = 0u;
+                }
+                const int cg = col_base + c0;
+                const int ncols = min(32, P.c_out - cg);
+                if (P.mode == MODE_WGRAD) {
+                    if (row_valid && k_iters > 0) {
+                        float* o = reinterpret_cast<float*>(P.out) + row_off +
+                                   static_cast<size_t>(cg) * col_stride;
+#pragma unroll
+                        for (int j = 0; j < 32; ++j)
+                            if (j < ncols) atomicAdd(o + j * col_stride, __uint_as_float(r[j]));
+                    }
+                } else {
+                    float v[32];
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        float x = __uint_as_float(r[j]);
+                        if (P.bias != nullptr && j < ncols) x += P.bias[cg + j];
+                        if (P.round_f16) x = round_through_f16(x);
+                        v[j] = x;
+                    }
+                    if (row_valid) store_row_chunk(P, v, row_off, col_stride, cg, ncols);
+                }
+                __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[buf]));
+        }
+    }
+
+    // ------------------------------------------------------------ teardown --
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        tmem_dealloc(tmem_base, tmem_cols);
+    }
+}
+
+}  // namespace nml
