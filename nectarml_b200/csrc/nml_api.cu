@@ -67,9 +67,11 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
+enum { SWZ_NONE = 0, SWZ_128B = 1, SWZ_128B_ATOM32 = 2 };
+
 // Tensor map over a dense tensor given fastest-first dims; strides are the dense ones.
 static int encode_map(CUtensorMap* tm, const void* ptr, int elem_bytes, int rank, const uint64_t* dims,
-                      const uint32_t* box, const uint32_t* estr, bool swizzle128) {
+                      const uint32_t* box, const uint32_t* estr, int swizzle) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) {
         snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled not available");
@@ -87,7 +89,9 @@ static int encode_map(CUtensorMap* tm, const void* ptr, int elem_bytes, int rank
     }
     CUresult r = fn(tm, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                     rank, const_cast<void*>(ptr), gdim, gstr, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    swizzle == SWZ_128B ? CU_TENSOR_MAP_SWIZZLE_128B
+                    : swizzle == SWZ_128B_ATOM32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                                 : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         snprintf(g_last_error, sizeof(g_last_error),
@@ -408,17 +412,17 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         uint32_t abox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>((1 << P.wb_log2) * esw),
                             static_cast<uint32_t>((1 << P.hb_log2) * esh), static_cast<uint32_t>(1 << P.nb_log2)};
         uint32_t aes[4] = {1, static_cast<uint32_t>(esw), static_cast<uint32_t>(esh), 1};
-        rc = encode_map(&P.tmA[pl], a_planes[pl], mi.es, 4, adims, abox, aes, true);
+        rc = encode_map(&P.tmA[pl], a_planes[pl], mi.es, 4, adims, abox, aes, SWZ_128B);
         if (rc) return rc;
         uint32_t one[2] = {1, 1};
         if (!b_mn_major) {
             uint64_t bdims[2] = {static_cast<uint64_t>(direct_w ? K : T * kp), static_cast<uint64_t>(N)};
             uint32_t bbox[2] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(P.bn)};
-            rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 2, bdims, bbox, one, true);
+            rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 2, bdims, bbox, one, SWZ_128B);
         } else {
             uint64_t bdims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
             uint32_t bbox[2] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(mi.kb)};
-            rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 2, bdims, bbox, one, true);
+            rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 2, bdims, bbox, one, SWZ_128B);
         }
         if (rc) return rc;
     }
@@ -512,20 +516,22 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     P.split_k = split;
     P.num_tiles = mn_tiles * split;
 
+    // MN-major tf32 operands need the 32-byte-chunk swizzle, fp16 ones the plain 128-byte swizzle
+    const int mn_swz = (mi.es == 4) ? SWZ_128B_ATOM32 : SWZ_128B;
     for (int pl = 0; pl < mi.planes; ++pl) {
         uint64_t adims[4] = {static_cast<uint64_t>(cpa), static_cast<uint64_t>(g.patch_w),
                              static_cast<uint64_t>(g.patch_h), static_cast<uint64_t>(g.batch)};
         uint32_t abox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>((1 << P.wb_log2) * g.s_w),
                             static_cast<uint32_t>((1 << P.hb_log2) * g.s_h), static_cast<uint32_t>(1 << P.nb_log2)};
         uint32_t aes[4] = {1, static_cast<uint32_t>(g.s_w), static_cast<uint32_t>(g.s_h), 1};
-        rc = encode_map(&P.tmA[pl], pa[pl], mi.es, 4, adims, abox, aes, true);
+        rc = encode_map(&P.tmA[pl], pa[pl], mi.es, 4, adims, abox, aes, mn_swz);
         if (rc) return rc;
         uint64_t bdims[4] = {static_cast<uint64_t>(cpb), static_cast<uint64_t>(g.plain_w),
                              static_cast<uint64_t>(g.plain_h), static_cast<uint64_t>(g.batch)};
         uint32_t bbox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(1 << P.wb_log2),
                             static_cast<uint32_t>(1 << P.hb_log2), static_cast<uint32_t>(1 << P.nb_log2)};
         uint32_t bes[4] = {1, 1, 1, 1};
-        rc = encode_map(&P.tmB[pl], pb[pl], mi.es, 4, bdims, bbox, bes, true);
+        rc = encode_map(&P.tmB[pl], pb[pl], mi.es, 4, bdims, bbox, bes, mn_swz);
         if (rc) return rc;
     }
     return launch_kernel(P, ds, st);
@@ -979,7 +985,7 @@ int nml_debug_tma_box(const void* tensor, int elem_bytes, const int dims[4], con
     }
     if (bytes > 96 * 1024 || bytes > out_bytes || bytes % 16) return NML_ERR_INVALID;
     CUtensorMap tm;
-    rc = encode_map(&tm, tensor, elem_bytes, 4, gd, bx, es, false);
+    rc = encode_map(&tm, tensor, elem_bytes, 4, gd, bx, es, SWZ_NONE);
     if (rc) return rc;
     static bool attr = false;
     if (!attr) {

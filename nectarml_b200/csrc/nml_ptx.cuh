@@ -185,18 +185,20 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
 //   bits [0,14)  start address >> 4        bits [16,30) leading byte offset >> 4
 //   bits [32,46) stride byte offset >> 4   bits [46,48) version = 1 (Blackwell)
-//   bits [61,64) layout type, 2 = SWIZZLE_128B
+//   bits [61,64) layout type: 2 = SWIZZLE_128B (16-byte chunks), 1 = SWIZZLE_128B with 32-byte
+//                chunks, the only layout tcgen05 takes for MN-major 32-bit (tf32) operands; its
+//                pattern repeats every 4 rows, so its 4-k groups are SBO = 512 bytes apart
 // K-major operand (rows of 128 B along K): 8-row groups are SBO apart, LBO unused.
 // MN-major operand (rows of 128 B along M/N, one row per k): 8-k groups are SBO apart,
 // consecutive 128-byte column groups along M/N are LBO apart.
 __device__ __forceinline__ uint64_t make_smem_desc(uint32_t saddr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
+                                                   uint32_t sbo_bytes, uint32_t layout_type) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((saddr & 0x3FFFF) >> 4);
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
     d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
+    d |= static_cast<uint64_t>(layout_type & 7) << 61;
     return d;
 }
 

@@ -331,6 +331,11 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             const uint32_t lbo_a = P.a_mn_major ? box_bytes : 16;
             const uint32_t lbo_b = P.b_mn_major ? box_bytes : 16;
             const int umma_k = (P.kind == KIND_F16) ? 16 : 8;
+            // MN-major tf32 operands use the 32-byte-chunk flavour of the 128-byte swizzle
+            const bool a32 = P.a_mn_major && P.kind == KIND_TF32;
+            const bool b32 = P.b_mn_major && P.kind == KIND_TF32;
+            const uint32_t lay_a = a32 ? 1 : 2, lay_b = b32 ? 1 : 2;
+            const uint32_t sbo_a = a32 ? 512 : 1024, sbo_b = b32 ? 512 : 1024;
             // descriptor start-address advance per UMMA, in 16-byte units
             const uint32_t adv_a = P.a_mn_major ? (umma_k * 128) >> 4 : 2;
             const uint32_t adv_b = P.b_mn_major ? (umma_k * 128) >> 4 : 2;
@@ -370,8 +375,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     tc_fence_after();
                     uint32_t sa = smem_u32(smem + stage * stage_bytes);
                     uint32_t sb = sa + kStageABytes;
-                    uint64_t adesc = make_smem_desc(sa, lbo_a, 1024);
-                    uint64_t bdesc = make_smem_desc(sb, lbo_b, 1024);
+                    uint64_t adesc = make_smem_desc(sa, lbo_a, sbo_a, lay_a);
+                    uint64_t bdesc = make_smem_desc(sb, lbo_b, sbo_b, lay_b);
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         uint32_t acc = (it > 0 || j > 0) ? 1u : 0u;
