@@ -181,6 +181,10 @@ int nml_ref_conv_transpose2d_backward_weight(uintptr_t out_grad_ptr, uintptr_t i
 int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_rank,
                    const int* b_shape, int b_rank, int dtype, uintptr_t* result);
 
+/* Releases a pointer returned through *result above (cudaFree); the counterpart of the
+ * reference's `_nectarml.free_cuda` (nectarml/csrc/ops/system/memory.cpp:33-39). */
+int nml_ref_free(uintptr_t ptr);
+
 /* ---- test support ----------------------------------------------------------------------
  * Copies one TMA box of a row-major host-described 4-D tensor (dims fastest first) into a
  * linear device buffer without swizzle, so tests can pin the coordinate, element-stride and
@@ -188,6 +192,12 @@ int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_r
 int nml_debug_tma_box(const void* tensor, int elem_bytes, const int dims[4], const int box[4],
                       const int elem_strides[4], const int coords[4], void* out, size_t out_bytes,
                       void* stream);
+
+
+/* Blocking device-to-host copy of a result pointer, as the reference's tensor read-back does
+ * (nectarml/csrc/ops/system/device/device.cpp:39-64).  Lets a test read what nml_ref_* returned
+ * without wrapping the raw pointer in another framework's tensor. */
+int nml_debug_copy_to_host(void* host_dst, uintptr_t device_src, size_t bytes);
 
 #ifdef __cplusplus
 }

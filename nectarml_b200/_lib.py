@@ -60,6 +60,8 @@ SYMBOLS = {
     "nml_ref_conv2d_backward_weight": (_I, _ref_bwd_common + [_I, C.POINTER(_UP)]),
     "nml_ref_conv_transpose2d_backward_weight": (_I, _ref_bwd_common + [_I, C.POINTER(_UP)]),
     "nml_ref_matmul": (_I, [_UP, _UP, C.POINTER(_I), _I, C.POINTER(_I), _I, _I, C.POINTER(_UP)]),
+    "nml_ref_free": (_I, [_UP]),
+    "nml_debug_copy_to_host": (_I, [_VP, _UP, _SZ]),
     "nml_debug_tma_box": (_I, [_VP, _I, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), C.POINTER(_I),
                                _VP, _SZ, _VP]),
 }

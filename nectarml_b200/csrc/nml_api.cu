@@ -968,6 +968,11 @@ int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_r
     return NML_OK;
 }
 
+int nml_ref_free(uintptr_t ptr) {
+    if (ptr) NML_CUDA(cudaFree(reinterpret_cast<void*>(ptr)));
+    return NML_OK;
+}
+
 int nml_debug_tma_box(const void* tensor, int elem_bytes, const int dims[4], const int box[4],
                       const int elem_strides[4], const int coords[4], void* out, size_t out_bytes, void* stream) {
     if (!tensor || !out || (elem_bytes != 2 && elem_bytes != 4)) return NML_ERR_INVALID;
@@ -996,6 +1001,12 @@ int nml_debug_tma_box(const void* tensor, int elem_bytes, const int dims[4], con
         tm, coords[0], coords[1], coords[2], coords[3], static_cast<uint32_t>(bytes), static_cast<uint8_t*>(out),
         ds->err);
     NML_CUDA(cudaGetLastError());
+    return NML_OK;
+}
+
+int nml_debug_copy_to_host(void* host_dst, uintptr_t device_src, size_t bytes) {
+    if (!host_dst || !device_src) return NML_ERR_INVALID;
+    NML_CUDA(cudaMemcpy(host_dst, reinterpret_cast<const void*>(device_src), bytes, cudaMemcpyDeviceToHost));
     return NML_OK;
 }
 

@@ -66,7 +66,7 @@ struct KParams {
     int stages;
     int a_mn_major, b_mn_major;
     int kind;            // KIND_F16 / KIND_TF32
-    int passes;          // 1, or 3 for the 3xTF32 split (hi*hi, hi*lo, lo*hi)
+    int passes;          // 1, or 3 for the 3xTF32 split (hi*lo, lo*hi, hi*hi in that order)
     int kb;              // elements per 128-byte row (64 fp16, 32 tf32)
     int c_blocks;        // channel blocks of kb per tap (fprop) / per patch tensor (wgrad)
     int wb_log2, hb_log2, nb_log2;  // fprop: M-tile box; wgrad: K-block pixel box
@@ -228,8 +228,11 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         int t = rem / P.c_blocks;
                         int cb = rem - t * P.c_blocks;
                         const Tap& tap = P.taps[ph.tap_begin + t];
-                        const CUtensorMap* ta = &P.tmA[pass == 2 ? 1 : 0];
-                        const CUtensorMap* tb = &P.tmB[pass == 1 ? 1 : 0];
+                        // 3xTF32 order: hi*lo, lo*hi, then hi*hi -- the small cross terms go in
+                        // while the accumulator is small, so the tensor core's truncating
+                        // accumulation costs them nothing
+                        const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
+                        const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
                         if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err,
                                        ERR_WAIT_EMPTY)) {
                             ok = false;
@@ -266,8 +269,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     int g_per_tile = kTileM / P.kb;
                     int na = g_per_tile, nb = P.bn / P.kb;
                     for (int pass = 0; ok && pass < P.passes; ++pass) {
-                        const CUtensorMap* ta = &P.tmA[pass == 2 ? 1 : 0];
-                        const CUtensorMap* tb = &P.tmB[pass == 1 ? 1 : 0];
+                        const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
+                        const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
                         for (int kbi = kb_begin; kbi < kb_end; ++kbi) {
                             int tw = kbi % P.ktiles_w;
                             int th = (kbi / P.ktiles_w) % P.ktiles_h;

@@ -1,0 +1,222 @@
+"""CUDA path vs the CPU oracle and the reference-generated fixtures, all through the C ABI.
+
+Three call styles are covered for every golden geometry:
+  * reference-shaped fp32 (`_nectarml.tensor.conv.*`, 3xTF32)  -- tolerance 1e-5 of max|ref|
+  * reference-shaped autocast forward (fp32 tensors, fp16 arithmetic) -- 1e-2 rel / 1e-3 abs
+  * native fp16 NHWC (descriptor API)                              -- 1e-2 rel / 1e-3 abs
+fp16 comparisons use the oracle on fp16-rounded inputs, which is what the arithmetic sees."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+from gpu_util import DEV, F16, F32, assert_f16, assert_f32, dev, fetch, geometry, host, rel_max
+from nectarml_b200 import _nectarml, ops
+
+pytestmark = pytest.mark.gpu
+conv = _nectarml.tensor.conv
+
+
+def oracle_all(oracle, case, x, w, b, dy):
+    transposed, geom, _, _ = case
+    B, Ci, H, W, Co, KH, KW, s, p, d, op = geom
+    if not transposed:
+        return (oracle.conv2d(x, w, b, s, p, d), oracle.conv2d_backward_input(dy, w, x.shape, s, p, d),
+                oracle.conv2d_backward_weight(dy, x, w.shape, s, p, d), oracle.bias_grad(dy))
+    return (oracle.conv_transpose2d(x, w, b, s, p, d, op), oracle.conv_transpose2d_backward_input(dy, w, x.shape, s, p, d),
+            oracle.conv_transpose2d_backward_weight(dy, x, w.shape, s, p, d), oracle.bias_grad(dy))
+
+
+def shim_forward(case, xd, wd, bd, dtype, half):
+    transposed, geom, _, _ = case
+    B, Ci, H, W, Co, KH, KW, s, p, d, op = geom
+    Ho, Wo = cases.out_hw(transposed, geom)
+    common = (xd.data_ptr(), xd.numel(), wd.data_ptr(), wd.numel(), bd.data_ptr() if bd is not None else 0,
+              bd.numel() if bd is not None else 0, B * Co * Ho * Wo, B, Ci, H, W, Co, KH, KW, s[0], s[1], p[0], p[1],
+              d[0], d[1])
+    if transposed:
+        ptr = conv.conv_transpose2d(*common, op[0], op[1], 1, dtype, half)
+    else:
+        ptr = conv.conv2d(*common, 1, dtype, half)
+    return fetch(ptr, (B, Co, Ho, Wo), np.float32 if dtype == F32 else np.float16)
+
+
+def shim_backward(case, dyd, xd, wd, dtype):
+    transposed, geom, _, _ = case
+    B, Ci, H, W, Co, KH, KW, s, p, d, op = geom
+    Ho, Wo = cases.out_hw(transposed, geom)
+    args = (B, Ci, H, W, Co, KH, KW, Ho, Wo, s[0], s[1], p[0], p[1], d[0], d[1])
+    if transposed:
+        dx = conv.conv_transpose2d_backward_input(dyd.data_ptr(), wd.data_ptr(), *args, 1, dtype)
+        dw = conv.conv_transpose2d_backward_weight(dyd.data_ptr(), xd.data_ptr(), *args, dtype)
+        wshape = (Ci, Co, KH, KW)
+    else:
+        dx = conv.conv2d_backward_input(dyd.data_ptr(), wd.data_ptr(), *args, 1, dtype)
+        dw = conv.conv2d_backward_weight(dyd.data_ptr(), xd.data_ptr(), *args, dtype)
+        wshape = (Co, Ci, KH, KW)
+    return fetch(dx, (B, Ci, H, W)), fetch(dw, wshape)
+
+
+@pytest.mark.parametrize("name", sorted(cases.CONV_CASES))
+def test_reference_shaped_fp32(name, golden_small, oracle):
+    case = cases.CONV_CASES[name]
+    x, w, b, dy = cases.draw_conv(name, case)
+    y_o, dx_o, dw_o, db_o = oracle_all(oracle, case, x, w, b, dy)
+    xd, wd, dyd = dev(x), dev(w), dev(dy)
+    bd = dev(b) if b is not None else None
+    y = shim_forward(case, xd, wd, bd, F32, False)
+    dx, dw = shim_backward(case, dyd, xd, wd, F32)
+    ops.device_status()
+    for got, orc, key in ((y, y_o, "y"), (dx, dx_o, "dx"), (dw, dw_o, "dw")):
+        assert_f32(got, orc, f"{name} {key} vs oracle")
+        assert_f32(got, golden_small[f"{name}__{key}"], f"{name} {key} vs reference fixture")
+
+
+@pytest.mark.parametrize("name", sorted(cases.CONV_CASES))
+def test_reference_shaped_autocast_forward(name, oracle):
+    """half_precision=True: fp32 tensors, fp16 operands, fp32 result holding fp16-rounded values
+    (nectarml/csrc/ops/tensor/conv/conv2d.cpp:415-435)."""
+    case = cases.CONV_CASES[name]
+    transposed, geom, _, _ = case
+    x, w, b, dy = cases.draw_conv(name, case)
+    r = oracle.round_f16
+    y_o = oracle_all(oracle, case, r(x), r(w), r(b) if b is not None else None, dy)[0]
+    y = shim_forward(case, dev(x), dev(w), dev(b) if b is not None else None, F32, True)
+    ops.device_status()
+    assert_f16(y, y_o, f"{name} autocast y")
+    assert np.array_equal(y, y.astype(np.float16).astype(np.float32)), "result is not fp16-representable"
+
+
+@pytest.mark.parametrize("name", sorted(cases.CONV_CASES))
+def test_native_fp16_nhwc(name, oracle):
+    case = cases.CONV_CASES[name]
+    g = geometry(case)
+    x, w, b, dy = cases.draw_conv(name, case)
+    r = oracle.round_f16
+    y_o, dx_o, dw_o, db_o = oracle_all(oracle, case, r(x), r(w), r(b) if b is not None else None, r(dy))
+    xd, dyd = dev(x, torch.float16, nhwc=True), dev(dy, torch.float16, nhwc=True)
+    wd = dev(w, torch.float16)
+    bd = dev(b, torch.float16) if b is not None else None
+    y = ops.conv_forward(g, xd, wd, bd, layout="nhwc", math="f16")
+    dx = ops.conv_backward_data(g, dyd, wd, layout="nhwc", math="f16")
+    dw, db = ops.conv_backward_weight(g, xd, dyd, layout="nhwc", math="f16")
+    ops.device_status()
+    assert_f16(host(y, nhwc=True), y_o, f"{name} y")
+    assert_f16(host(dx, nhwc=True), dx_o, f"{name} dx")
+    # gradients of the weights come out in fp32 from fp32 accumulation
+    assert_f32(host(dw), dw_o, f"{name} dw", tol=2e-5)
+    assert_f32(host(db), db_o, f"{name} db", tol=2e-5)
+
+
+def test_config1_full_size(golden_config1, oracle):
+    """BASELINE config 1: Conv2d fp32 N=8 64->64 56x56 3x3 s1 p1, output, dX, dW and db."""
+    case = cases.CONFIG1
+    x, w, b, dy = cases.draw_conv("config1", case, cases.CONFIG1_SEED)
+    y_o, dx_o, dw_o, db_o = oracle_all(oracle, case, x, w, b, dy)
+    xd, wd, bd, dyd = dev(x), dev(w), dev(b), dev(dy)
+    y = shim_forward(case, xd, wd, bd, F32, False)
+    dx, dw = shim_backward(case, dyd, xd, wd, F32)
+    g = geometry(case)
+    db = host(ops.conv_backward_weight(g, xd, dyd, layout="nchw", math="3xtf32")[1])
+    ops.device_status()
+    assert_f32(y, y_o, "config1 y")
+    assert_f32(dx, dx_o, "config1 dx")
+    assert_f32(dw, dw_o, "config1 dw")
+    assert_f32(db, db_o, "config1 db")
+    gc = golden_config1
+    assert_f32(y.reshape(-1)[gc["y_idx"]], gc["y_val"], "config1 y vs reference samples")
+    assert_f32(dx.reshape(-1)[gc["dx_idx"]], gc["dx_val"], "config1 dx vs reference samples")
+    assert_f32(dw.reshape(-1)[gc["dw_idx"]], gc["dw_val"], "config1 dw vs reference samples", tol=3e-5)
+    assert_f32(db, gc["db"], "config1 db vs reference")
+
+
+@pytest.mark.parametrize("name", sorted(cases.LINEAR_CASES))
+def test_linear_fp32_and_fp16(name, golden_small, oracle):
+    x, w, b, dy = cases.draw_linear(name, cases.LINEAR_CASES[name])
+    xd, wd, bd, dyd = dev(x), dev(w), dev(b), dev(dy)
+    y = host(ops.linear_forward(xd, wd, bd, math="3xtf32"))
+    dx = host(ops.linear_backward_data(dyd, wd, math="3xtf32"))
+    dw, db = [host(t) for t in ops.linear_backward_weight(xd, dyd, math="3xtf32")]
+    ops.device_status()
+    for got, key in ((y, "y"), (dx, "dx"), (dw, "dw"), (db, "db")):
+        assert_f32(got, golden_small[f"{name}__{key}"], f"{name} {key}")
+    r = oracle.round_f16
+    y_o = oracle.linear_forward(r(x), r(w), r(b))
+    dx_o, dw_o, db_o = oracle.linear_backward(r(x), r(w), r(dy))
+    h = torch.float16
+    y16 = host(ops.linear_forward(dev(x, h), dev(w, h), dev(b, h), math="f16"))
+    dx16 = host(ops.linear_backward_data(dev(dy, h), dev(w, h), math="f16"))
+    dw16, db16 = [host(t) for t in ops.linear_backward_weight(dev(x, h), dev(dy, h), math="f16")]
+    ops.device_status()
+    assert_f16(y16, y_o, f"{name} fp16 y")
+    assert_f16(dx16, dx_o, f"{name} fp16 dx")
+    assert_f32(dw16, dw_o, f"{name} fp16 dw", tol=2e-5)
+    assert_f32(db16, db_o, f"{name} fp16 db", tol=2e-5)
+
+
+@pytest.mark.parametrize("rows,d", [(4096, 512), (1000, 520)])
+def test_linear_projection_shapes(rows, d, oracle):
+    """BASELINE config 2 family: X[rows, d] @ W^T[d, 4d] + b in fp16 with fp32 accumulation."""
+    rng = np.random.default_rng(1236)
+    x = rng.standard_normal((rows, d), dtype=np.float32)
+    bound = np.sqrt(6.0 / (d + 4 * d))
+    w = rng.uniform(-bound, bound, (4 * d, d)).astype(np.float32)
+    b = rng.uniform(-0.1, 0.1, 4 * d).astype(np.float32)
+    dy = rng.standard_normal((rows, 4 * d), dtype=np.float32)
+    r = oracle.round_f16
+    y_o = oracle.linear_forward(r(x), r(w), r(b))
+    dx_o, dw_o, db_o = oracle.linear_backward(r(x), r(w), r(dy))
+    h = torch.float16
+    xd, wd, bd, dyd = dev(x, h), dev(w, h), dev(b, h), dev(dy, h)
+    assert_f16(host(ops.linear_forward(xd, wd, bd)), y_o, "y")
+    assert_f16(host(ops.linear_backward_data(dyd, wd)), dx_o, "dx")
+    dw, db = ops.linear_backward_weight(xd, dyd)
+    ops.device_status()
+    assert_f32(host(dw), dw_o, "dw", tol=2e-5)
+    assert_f32(host(db), db_o, "db", tol=2e-5)
+
+
+def test_reference_shaped_matmul(oracle):
+    """`_nectarml.tensor.matmul`: 2-D, the 4x8 @ 8x4 case of the reference's tests
+    (tests/automatic/test_tensor_methods.py:237-249), and equal-batch 3-D operands."""
+    rng = np.random.default_rng(5)
+    for a_shape, b_shape in (((4, 8), (8, 4)), ((130, 72), (72, 200)), ((3, 33, 40), (3, 40, 24))):
+        a = rng.standard_normal(a_shape, dtype=np.float32)
+        b = rng.standard_normal(b_shape, dtype=np.float32)
+        a32, b32 = dev(a), dev(b)
+        ptr = _nectarml.tensor.matmul(a32.data_ptr(), b32.data_ptr(), list(a_shape), list(b_shape), F32)
+        got = fetch(ptr, a_shape[:-1] + (b_shape[-1],))
+        assert_f32(got, oracle.matmul(a, b), f"matmul {a_shape}x{b_shape}")
+        a16, b16 = dev(a, torch.float16), dev(b, torch.float16)
+        ptr = _nectarml.tensor.matmul(a16.data_ptr(), b16.data_ptr(), list(a_shape), list(b_shape), F16)
+        got = fetch(ptr, a_shape[:-1] + (b_shape[-1],), np.float16)
+        assert_f16(got, oracle.matmul(oracle.round_f16(a), oracle.round_f16(b)), f"matmul fp16 {a_shape}")
+    ops.device_status()
+
+
+def test_forward_is_bitwise_repeatable():
+    g = geometry(cases.CONV_CASES["c72"])
+    x, w, b, dy = cases.draw_conv("c72", cases.CONV_CASES["c72"])
+    xd, wd, bd = dev(x), dev(w), dev(b)
+    a = ops.conv_forward(g, xd, wd, bd, math="3xtf32")
+    c = ops.conv_forward(g, xd, wd, bd, math="3xtf32")
+    d1 = ops.conv_backward_data(g, dev(dy), wd, math="3xtf32")
+    d2 = ops.conv_backward_data(g, dev(dy), wd, math="3xtf32")
+    ops.device_status()
+    assert torch.equal(a, c) and torch.equal(d1, d2)
+
+
+def test_workspace_too_small_is_reported():
+    import ctypes as C
+    from nectarml_b200 import _lib
+    g = geometry(cases.CONV_CASES["c72"])
+    x, w, b, dy = cases.draw_conv("c72", cases.CONV_CASES["c72"])
+    xd, wd = dev(x), dev(w)
+    y = torch.empty(g.act_shape("out", "nchw"), device=DEV)
+    d = g.desc(_lib.NML_F32, "nchw", _lib.NML_F32, "nchw", _lib.NML_F32, "3xtf32", False)
+    small = torch.empty(1024, dtype=torch.uint8, device=DEV)
+    st = _lib.load().nml_conv_forward(C.byref(d), xd.data_ptr(), wd.data_ptr(), None, y.data_ptr(),
+                                      small.data_ptr(), small.numel(), None)
+    assert st == 2
+    st = _lib.load().nml_conv_forward(C.byref(d), None, wd.data_ptr(), None, y.data_ptr(), None, 0, None)
+    assert st == 1
