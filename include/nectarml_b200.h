@@ -130,8 +130,16 @@ int nml_linear_backward_weight(const nml_linear_desc* d, const void* x, const vo
  * entry points above never block, so this is how a caller learns of a device-side give-up. */
 int nml_device_status(int* code);
 
-/* Number of contraction-kernel launches this process has made (for launch accounting). */
+/* Number of kernels this library has launched in this process (contraction kernel plus its
+ * conversion / reduction helpers), for launch accounting. */
 long long nml_launch_count(void);
+
+/* Per-launch device timing of the contraction kernel.  After nml_profile_begin(n) each of the
+ * next n contraction launches is bracketed by CUDA events on its own stream; nml_profile_end
+ * synchronises, writes the durations in milliseconds in launch order and stops recording.
+ * Measurement support only: nothing else in the library depends on it. */
+int nml_profile_begin(int max_records);
+int nml_profile_end(float* ms_out, int capacity, int* count);
 
 /* ---- reference-shaped entry points ------------------------------------------------------
  * Same argument lists as the reference's host ops, which its pybind module registers as

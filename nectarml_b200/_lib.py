@@ -49,6 +49,8 @@ SYMBOLS = {
     "nml_linear_backward_weight": (_I, [C.POINTER(LinearDesc), _VP, _VP, _VP, _VP, _VP, _SZ, _VP]),
     "nml_device_status": (_I, [C.POINTER(_I)]),
     "nml_launch_count": (C.c_longlong, []),
+    "nml_profile_begin": (_I, [_I]),
+    "nml_profile_end": (_I, [C.POINTER(C.c_float), _I, C.POINTER(_I)]),
     # conv2d: ... dilation_w, groups, dtype, half_precision, result
     "nml_ref_conv2d": (_I, _ref_fwd_common + [_I, _I, _I, C.POINTER(_UP)]),
     # conv_transpose2d: ... dilation_w, outpad_h, outpad_w, groups, dtype, half_precision, result

@@ -114,6 +114,13 @@ static DeviceState g_dev[64];
 static std::mutex g_dev_mutex;
 static long long g_launches = 0;
 
+struct Profiler {
+    bool on = false;
+    int cap = 0, n = 0;
+    std::vector<cudaEvent_t> start, stop;
+};
+static Profiler g_prof;
+
 static int device_state(DeviceState** out) {
     int dev = 0;
     NML_CUDA(cudaGetDevice(&dev));
@@ -161,8 +168,8 @@ static int prepare_activation(const void* src, int dtype, int layout, int batch,
         if (colsum && !ws.dry) {
             int rows_per_block = 256;
             dim3 grid(ceil_div(c, 256), static_cast<unsigned>((pixels + rows_per_block - 1) / rows_per_block));
-            colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
-                                                             rows_per_block);
+            { colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
+                                                             rows_per_block); ++g_launches; }
         }
         return NML_OK;
     }
@@ -177,29 +184,29 @@ static int prepare_activation(const void* src, int dtype, int layout, int batch,
     if (layout == NML_NCHW && !(h == 1 && w == 1)) {
         dim3 grid(ceil_div(h * w, 64), ceil_div(Cp, 64), batch);
         if (dtype == NML_F32)
-            nchw_to_nhwc_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), p0, p1, mi.enc, c, Cp,
-                                                            h * w, colsum);
+            { nchw_to_nhwc_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), p0, p1, mi.enc, c, Cp,
+                                                            h * w, colsum); ++g_launches; }
         else
-            nchw_to_nhwc_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), p0, p1, mi.enc, c,
-                                                             Cp, h * w, colsum);
+            { nchw_to_nhwc_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), p0, p1, mi.enc, c,
+                                                             Cp, h * w, colsum); ++g_launches; }
     } else {
         size_t total = pixels * Cp;
         int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 16));
         if (dtype == NML_F32)
-            convert_rows_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(src), p0, p1, mi.enc, pixels,
-                                                              c, Cp);
+            { convert_rows_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(src), p0, p1, mi.enc, pixels,
+                                                              c, Cp); ++g_launches; }
         else
-            convert_rows_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(src), p0, p1, mi.enc,
-                                                               pixels, c, Cp);
+            { convert_rows_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(src), p0, p1, mi.enc,
+                                                               pixels, c, Cp); ++g_launches; }
         if (colsum) {
             int rows_per_block = 256;
             dim3 grid(ceil_div(c, 256), static_cast<unsigned>((pixels + rows_per_block - 1) / rows_per_block));
             if (dtype == NML_F32)
-                colsum_rows_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), colsum, pixels, c,
-                                                                rows_per_block);
+                { colsum_rows_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), colsum, pixels, c,
+                                                                rows_per_block); ++g_launches; }
             else
-                colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
-                                                                 rows_per_block);
+                { colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
+                                                                 rows_per_block); ++g_launches; }
         }
     }
     NML_CUDA(cudaGetLastError());
@@ -236,8 +243,11 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
     P.err = ds->err;
     int grid = std::min(P.num_tiles, ds->sms);
     if (grid <= 0) return NML_OK;
+    const bool rec = g_prof.on && g_prof.n < g_prof.cap;
+    if (rec) NML_CUDA(cudaEventRecord(g_prof.start[g_prof.n], st));
     umma_conv_kernel<<<grid, kThreads, smem, st>>>(P);
     NML_CUDA(cudaGetLastError());
+    if (rec) NML_CUDA(cudaEventRecord(g_prof.stop[g_prof.n++], st));
     ++g_launches;
     return NML_OK;
 }
@@ -300,11 +310,11 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
             size_t total = static_cast<size_t>(N) * T * kp;
             int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 8));
             if (f.w_dtype == NML_F32)
-                repack_weight_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(f.w), p0, p1, mi.enc,
-                                                                   f.d0, f.d1, T, f.k_is_dim0, kp);
+                { repack_weight_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(f.w), p0, p1, mi.enc,
+                                                                   f.d0, f.d1, T, f.k_is_dim0, kp); ++g_launches; }
             else
-                repack_weight_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(f.w), p0, p1, mi.enc,
-                                                                    f.d0, f.d1, T, f.k_is_dim0, kp);
+                { repack_weight_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(f.w), p0, p1, mi.enc,
+                                                                    f.d0, f.d1, T, f.k_is_dim0, kp); ++g_launches; }
             NML_CUDA(cudaGetLastError());
         }
     }
@@ -315,7 +325,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         bias32 = b;
         if (!ws.dry) {
             if (!ws.fits()) return NML_ERR_WORKSPACE;
-            to_float_kernel<__half><<<ceil_div(N, 256), 256, 0, st>>>(static_cast<const __half*>(f.bias), b, N);
+            { to_float_kernel<__half><<<ceil_div(N, 256), 256, 0, st>>>(static_cast<const __half*>(f.bias), b, N); ++g_launches; }
         }
     }
     if (ws.dry) return NML_OK;
@@ -785,6 +795,31 @@ int nml_device_status(int* code) {
 }
 
 long long nml_launch_count(void) { return g_launches; }
+
+int nml_profile_begin(int max_records) {
+    if (max_records <= 0 || max_records > 1 << 16) return NML_ERR_INVALID;
+    while (static_cast<int>(g_prof.start.size()) < max_records) {
+        cudaEvent_t a, b;
+        NML_CUDA(cudaEventCreate(&a));
+        NML_CUDA(cudaEventCreate(&b));
+        g_prof.start.push_back(a);
+        g_prof.stop.push_back(b);
+    }
+    g_prof.cap = max_records;
+    g_prof.n = 0;
+    g_prof.on = true;
+    return NML_OK;
+}
+
+int nml_profile_end(float* ms_out, int capacity, int* count) {
+    if (!ms_out || !count) return NML_ERR_INVALID;
+    g_prof.on = false;
+    NML_CUDA(cudaDeviceSynchronize());
+    int n = std::min(g_prof.n, capacity);
+    for (int i = 0; i < n; ++i) NML_CUDA(cudaEventElapsedTime(&ms_out[i], g_prof.start[i], g_prof.stop[i]));
+    *count = n;
+    return NML_OK;
+}
 
 // ---- reference-shaped entry points ----
 static void fill_conv_desc(nml_conv_desc* d, int transposed, int B, int C_in, int H, int W, int C_out, int KH,

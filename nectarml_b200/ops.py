@@ -259,6 +259,19 @@ def launch_count() -> int:
     return int(_lib.load().nml_launch_count())
 
 
+def profile_begin(max_records: int) -> None:
+    """Start bracketing the next ``max_records`` contraction-kernel launches with CUDA events."""
+    check(_lib.load().nml_profile_begin(int(max_records)))
+
+
+def profile_end(max_records: int):
+    """Synchronise and return the recorded per-launch durations (ms) in launch order."""
+    buf = (C.c_float * max_records)()
+    n = C.c_int(0)
+    check(_lib.load().nml_profile_end(buf, max_records, C.byref(n)))
+    return [float(buf[i]) for i in range(n.value)]
+
+
 def tma_box(t: torch.Tensor, box, elem_strides, coords) -> torch.Tensor:
     """Test support: returns one TMA box of a 4-D tensor (``t.shape`` slowest-first, as torch
     prints it; ``box``/``elem_strides``/``coords`` fastest-first, as TMA takes them)."""
