@@ -1,0 +1,89 @@
+"""The sharded (N > 1) path on CPU: two gloo ranks each own half of the batch, compute their
+weight / bias gradients with the oracle, and the all-reduced bucket must equal the full-batch
+gradients.  Forward and input-gradient are per-sample, so their shards simply concatenate."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import cases
+from nectarml_b200.parallel import GradientBucket, shard_range
+
+
+def test_shard_range_covers_everything():
+    for total in (0, 1, 7, 8, 64, 2048):
+        for world in (1, 2, 3, 8):
+            spans = [shard_range(total, world, r) for r in range(world)]
+            assert sum(c for _, c in spans) == total
+            pos = 0
+            for start, count in spans:
+                assert start == pos
+                pos += count
+            assert max(c for _, c in spans) - min(c for _, c in spans) <= 1
+    with pytest.raises(ValueError):
+        shard_range(8, 2, 2)
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from oracle import nectar_oracle as orc
+        name = "c72"
+        case = cases.CONV_CASES[name]
+        _, geom, _, _ = case
+        B, Ci, H, W, Co, KH, KW, s, p, d, op = geom
+        x, w, b, dy = cases.draw_conv(name, case)
+        start, count = shard_range(B, world, rank)
+        xs, dys = x[start:start + count], dy[start:start + count]
+        bucket = GradientBucket([w.shape, (Co,)], "cpu")
+        bucket.view(0).copy_(torch.from_numpy(orc.conv2d_backward_weight(dys, xs, w.shape, s, p, d)))
+        bucket.view(1).copy_(torch.from_numpy(orc.bias_grad(dys)))
+        bucket.all_reduce()
+        y_shard = orc.conv2d(xs, w, b, s, p, d)
+        ys = [None] * world
+        dist.all_gather_object(ys, y_shard)
+        if rank == 0:
+            full_dw = orc.conv2d_backward_weight(dy, x, w.shape, s, p, d)
+            full_db = orc.bias_grad(dy)
+            full_y = orc.conv2d(x, w, b, s, p, d)
+            ret["dw"] = float(np.abs(bucket.view(0).numpy() - full_dw).max() / np.abs(full_dw).max())
+            ret["db"] = float(np.abs(bucket.view(1).numpy() - full_db).max() / np.abs(full_db).max())
+            ret["y_equal"] = bool(np.array_equal(np.concatenate(ys, axis=0), full_y))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gradient_allreduce_matches_full_batch():
+    from oracle import nectar_oracle
+    nectar_oracle.build()
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=_worker, args=(r, 2, port, ret)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(120)
+            assert p.exitcode == 0
+        assert ret["y_equal"]
+        assert ret["dw"] < 2e-6 and ret["db"] < 2e-6
+
+
+def test_bucket_without_process_group_is_a_noop():
+    b = GradientBucket([(3, 4), (5,)], "cpu")
+    b.view(0).fill_(1.0)
+    assert b.all_reduce() is None
+    assert float(b.view(0).sum()) == 12.0 and b.view(1).shape == (5,)
