@@ -100,6 +100,31 @@ int nml_linear_workspace_size(const nml_linear_desc* d, int pass, size_t* bytes)
 int nml_conv_forward(const nml_conv_desc* d, const void* x, const void* w, const void* bias, void* y,
                      void* workspace, size_t workspace_bytes, void* stream);
 
+/* Forward for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference (whose host ops cudaMalloc freely); it exists for hosts where an allocation call is
+ * not an option at the point of the call -- a serving process that has handed every free byte of
+ * HBM to its own pool, so cudaMalloc would fail, or a latency-critical loop that must not hit the
+ * device-wide synchronisation cudaMalloc / cudaFree imply.  Same arithmetic and same arguments as
+ * nml_conv_forward, but no workspace argument: the converted operands go to a 64 MiB
+ * (67,108,864-byte) scratch array that is part of the library image, so every GPU that loads
+ * the library holds those 64 MiB until the process exits.  The call makes no cudaMalloc, cudaFree
+ * or other allocating call.
+ *   - A layer whose conversion scratch exceeds 64 MiB is refused with NML_ERR_WORKSPACE (the
+ *     message states the need and the limit); use nml_conv_forward with your own workspace.
+ *   - The first call on each device looks up the device address of the scratch array (with that
+ *     device current) and raises the kernel's shared-memory limit.  Make that first call
+ *     before any stream capture begins.
+ *   - All calls share the one array, and it keeps what the last call left there.  Each call
+ *     rewrites every byte it later reads, so stale contents are harmless, but two calls whose
+ *     work overlaps on the GPU (different streams, or different host threads) race on it:
+ *     serialise them.
+ *   - Kernels launched here report an abandoned bounded wait into a status word beside the
+ *     scratch array, not into the word nml_device_status reads.  Calling this function with
+ *     d == NULL (other arguments ignored) synchronises the device and returns NML_ERR_DEVICE
+ *     if such a give-up was recorded, clearing it. */
+int nml_conv_forward_static(const nml_conv_desc* d, const void* x, const void* w, const void* bias, void* y,
+                            void* stream);
+
 /* Input gradient: dx from dy.  Replaces run_conv2d_backward_input + col2im
  * (conv2d.cpp:213-274, 499-518) and conv_transpose2d_backward_input (conv2d.cpp:520-542). */
 int nml_conv_backward_data(const nml_conv_desc* d, const void* dy, const void* w, void* dx,

@@ -42,6 +42,7 @@ SYMBOLS = {
     "nml_conv_workspace_size": (_I, [C.POINTER(ConvDesc), _I, C.POINTER(_SZ)]),
     "nml_linear_workspace_size": (_I, [C.POINTER(LinearDesc), _I, C.POINTER(_SZ)]),
     "nml_conv_forward": (_I, [C.POINTER(ConvDesc), _VP, _VP, _VP, _VP, _VP, _SZ, _VP]),
+    "nml_conv_forward_static": (_I, [C.POINTER(ConvDesc), _VP, _VP, _VP, _VP, _VP]),
     "nml_conv_backward_data": (_I, [C.POINTER(ConvDesc), _VP, _VP, _VP, _VP, _SZ, _VP]),
     "nml_conv_backward_weight": (_I, [C.POINTER(ConvDesc), _VP, _VP, _VP, _VP, _VP, _SZ, _VP]),
     "nml_linear_forward": (_I, [C.POINTER(LinearDesc), _VP, _VP, _VP, _VP, _VP, _SZ, _VP]),

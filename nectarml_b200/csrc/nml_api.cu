@@ -28,6 +28,7 @@ namespace nml {
     } while (0)
 
 static thread_local char g_last_error[256] = {0};
+static thread_local char g_last_scratch_error[256] = {0};
 static void set_last_cuda_error(cudaError_t e, const char* what) {
     snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
 }
@@ -35,11 +36,14 @@ static void set_last_cuda_error(cudaError_t e, const char* what) {
 static inline size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
+struct DeviceState;
+
 // Bump allocator over the caller's workspace; in dry mode it only measures.
 struct Bump {
     uint8_t* base;
     size_t off, cap;
     bool dry;
+    DeviceState* ds = nullptr;  // when set, used instead of the lazily allocated per-device state
     void* take(size_t bytes) {
         off = round_up(off, 256);
         void* p = dry ? nullptr : base + off;
@@ -278,8 +282,8 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     if (f.batch <= 0 || f.a_c <= 0 || f.a_h <= 0 || f.a_w <= 0 || f.out_c <= 0 || f.out_h <= 0 || f.out_w <= 0)
         return NML_ERR_INVALID;
 
-    DeviceState* ds = nullptr;
-    if (!ws.dry) {
+    DeviceState* ds = ws.ds;
+    if (!ws.dry && !ds) {
         int rc = device_state(&ds);
         if (rc) return rc;
     }
@@ -707,7 +711,7 @@ const char* nml_status_string(int status) {
     switch (status) {
         case NML_OK: return "ok";
         case NML_ERR_INVALID: return "invalid argument";
-        case NML_ERR_WORKSPACE: return "workspace too small";
+        case NML_ERR_WORKSPACE: return g_last_scratch_error[0] ? g_last_scratch_error : "workspace too small";
         case NML_ERR_CUDA: return g_last_error[0] ? g_last_error : "CUDA error";
         case NML_ERR_UNSUPPORTED: return "unsupported configuration";
         case NML_ERR_DEVICE: return "a kernel abandoned a bounded wait";
@@ -819,6 +823,78 @@ int nml_profile_end(float* ms_out, int capacity, int* count) {
     for (int i = 0; i < n; ++i) NML_CUDA(cudaEventElapsedTime(&ms_out[i], g_prof.start[i], g_prof.stop[i]));
     *count = n;
     return NML_OK;
+}
+
+// ---- forward entry point that allocates nothing ----
+// Scratch for the converted operands lives in the library image instead of caller memory.
+// kStaticScratchBytes of every GPU that loads this library are held until the process exits.
+constexpr size_t kStaticScratchBytes = 64ull << 20;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+static __device__ int g_static_status;  // where kernels launched by this entry point report a give-up
+
+struct StaticState {
+    bool ready = false;
+    void* scratch = nullptr;  // DEVICE address of g_static_scratch on this device
+    DeviceState ds;           // status word = device address of g_static_status
+};
+static StaticState g_static[64];
+
+// Once per device, with that device current.  In host code `g_static_scratch` is only a handle for
+// the symbol, not an address a kernel may use: the device address comes from cudaGetSymbolAddress.
+static int static_state(StaticState** out) {
+    int dev = 0;
+    NML_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return NML_ERR_INVALID;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    StaticState& s = g_static[dev];
+    if (!s.ready) {
+        void* scratch = nullptr;
+        void* status = nullptr;
+        NML_CUDA(cudaGetSymbolAddress(&scratch, g_static_scratch));
+        NML_CUDA(cudaGetSymbolAddress(&status, g_static_status));
+        NML_CUDA(cudaMemset(status, 0, sizeof(int)));
+        NML_CUDA(cudaDeviceGetAttribute(&s.ds.sms, cudaDevAttrMultiProcessorCount, dev));
+        NML_CUDA(cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+        s.scratch = scratch;
+        s.ds.err = static_cast<int*>(status);
+        s.ds.attr_set = true;
+        s.ready = true;
+    }
+    *out = &s;
+    return NML_OK;
+}
+
+int nml_conv_forward_static(const nml_conv_desc* d, const void* x, const void* w, const void* bias, void* y,
+                            void* stream) {
+    StaticState* ss = nullptr;
+    if (!d) {  // query form: wait for the device, report and clear a recorded give-up
+        int rc = static_state(&ss);
+        if (rc) return rc;
+        NML_CUDA(cudaDeviceSynchronize());
+        int v = 0;
+        NML_CUDA(cudaMemcpy(&v, ss->ds.err, sizeof(int), cudaMemcpyDeviceToHost));
+        if (v == 0) return NML_OK;
+        NML_CUDA(cudaMemset(ss->ds.err, 0, sizeof(int)));
+        snprintf(g_last_error, sizeof(g_last_error), "a kernel abandoned bounded wait %d", v);
+        return NML_ERR_DEVICE;
+    }
+    if (!x || !w || !y) return NML_ERR_INVALID;
+    Bump dry{nullptr, 0, 0, true};
+    int rc = conv_pass(d, NML_PASS_FORWARD, nullptr, nullptr, bias ? d : nullptr, nullptr, nullptr, dry, nullptr);
+    if (rc) return rc;
+    const size_t need = round_up(dry.off, 256);
+    if (need > kStaticScratchBytes) {
+        snprintf(g_last_scratch_error, sizeof(g_last_scratch_error),
+                 "this layer needs %zu bytes of scratch; the built-in scratch array holds %zu "
+                 "(use nml_conv_forward with a caller workspace)", need, kStaticScratchBytes);
+        return NML_ERR_WORKSPACE;
+    }
+    rc = static_state(&ss);
+    if (rc) return rc;
+    // Every region of the scratch that the contraction reads is rewritten in full by the conversion
+    // passes of this call (channel and K padding included), so nothing from the last call survives.
+    Bump ws{static_cast<uint8_t*>(ss->scratch), 0, kStaticScratchBytes, false, &ss->ds};
+    return conv_pass(d, NML_PASS_FORWARD, x, w, bias, y, nullptr, ws, static_cast<cudaStream_t>(stream));
 }
 
 // ---- reference-shaped entry points ----
