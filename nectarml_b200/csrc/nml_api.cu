@@ -240,9 +240,9 @@ static void choose_box(int bits, int gw, int gh, int gn, int s_w, int s_h, int* 
 
 static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
     const int stage_bytes = kStageABytes + P.bn * 128;
-    int stages = std::min(8, (232448 - 1024 - 256) / stage_bytes);
+    int stages = std::min(8, (232448 - 1024 - 256 - kStagingBytes) / stage_bytes);
     P.stages = stages;
-    size_t smem = static_cast<size_t>(stages) * stage_bytes + 1024 + 256;
+    size_t smem = static_cast<size_t>(stages) * stage_bytes + kStagingBytes + 1024 + 256;
     smem = std::max<size_t>(smem, 120 * 1024);  // one CTA per SM: each allocates its own TMEM
     P.err = ds->err;
     int grid = std::min(P.num_tiles, ds->sms);

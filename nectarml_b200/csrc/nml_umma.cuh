@@ -42,6 +42,7 @@ constexpr int kMaxTaps = 128;
 constexpr int kTileM = 128;
 constexpr int kStageABytes = kTileM * 128;
 constexpr int kThreads = 192;
+constexpr int kStagingBytes = 4 * 4096;  // per epilogue warp: 32 rows x 128 bytes of output
 
 struct Tap {
     short dh, dw;  // offset of this tap's box from the tile origin, in input pixels
@@ -92,6 +93,21 @@ struct KParams {
 
 __device__ __forceinline__ float round_through_f16(float v) {
     return __half2float(__float2half_rn(v));
+}
+
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+                 : "memory");
+}
+__device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr)
+                 : "memory");
+    return v;
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
 }
 
 // Stores 32 (or fewer) consecutive output columns of one accumulator row.
@@ -154,7 +170,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                                                ~static_cast<uintptr_t>(1023));
     const int stage_b_bytes = P.bn * 128;
     const int stage_bytes = kStageABytes + stage_b_bytes;
-    uint8_t* ctrl = smem + P.stages * stage_bytes;
+    uint8_t* staging = smem + P.stages * stage_bytes;  // 4 epilogue warps x 4 KB
+    uint8_t* ctrl = staging + kStagingBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);          // [stages]
     uint64_t* empty_bar = full_bar + 8;                               // [stages]
     uint64_t* tfull_bar = empty_bar + 8;                              // [2]
@@ -464,6 +481,106 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             tc_fence_after();
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * P.bn;
             const int col_base = ntile * P.bn;
+            if (P.mode == MODE_FPROP && P.out_mode == OUT_NHWC) {
+                // Row-major output: each 128-byte piece of a row (64 fp16 / 32 fp32 columns) goes
+                // through a swizzled shared-memory tile so that a warp store writes four full
+                // 128-byte row pieces instead of 32 scattered 16-byte ones.
+                const int cpi = P.out_f16 ? 64 : 32;
+                const int esz = P.out_f16 ? 2 : 4;
+                const uint32_t stg = smem_u32(staging) + (warp - 2) * 4096;
+                const bool aligned = ((static_cast<size_t>(P.ld_out) * esz) & 15) == 0 &&
+                                     (reinterpret_cast<uintptr_t>(P.out) & 15) == 0 &&
+                                     (reinterpret_cast<uintptr_t>(P.bias) & 15) == 0;
+                for (int c0 = 0; c0 < P.bn; c0 += cpi) {
+                    const int cg = col_base + c0;
+                    if (cg >= P.c_out) break;  // uniform across the warp
+                    const int ncols = min(min(cpi, P.bn - c0), P.c_out - cg);
+                    uint32_t r0[32], r1[32];
+                    const bool second = (cpi == 64) && (c0 + 32 < P.bn);
+                    if (k_iters > 0) {
+                        tmem_ld_32x32(t_row + c0, r0);
+                        if (second) tmem_ld_32x32(t_row + c0 + 32, r1);
+                        tmem_ld_wait();
+                    }
+                    if (k_iters == 0) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r0[j] = 0u;
+                    }
+                    if (k_iters == 0 || !second) {
+#pragma unroll
+                        for (int j = 0; j < 32; ++j) r1[j] = 0u;
+                    }
+                    const bool has_bias = (P.bias != nullptr);
+                    if (ncols == cpi && aligned) {
+#pragma unroll
+                        for (int q = 0; q < 8; ++q) {
+                            float v[8];
+                            uint4 pk;
+                            if (P.out_f16) {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    v[j] = __uint_as_float(q < 4 ? r0[(8 * q + j) & 31] : r1[(8 * q + j) & 31]);
+                                if (has_bias) {
+                                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 8 * q));
+                                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 8 * q + 4));
+                                    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                                    v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                                }
+                                pk.x = pack_half2(v[0], v[1]);
+                                pk.y = pack_half2(v[2], v[3]);
+                                pk.z = pack_half2(v[4], v[5]);
+                                pk.w = pack_half2(v[6], v[7]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) v[j] = __uint_as_float(r0[4 * q + j]);
+                                if (has_bias) {
+                                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 4 * q));
+                                    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                                }
+                                if (P.round_f16) {
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) v[j] = round_through_f16(v[j]);
+                                }
+                                pk.x = __float_as_uint(v[0]);
+                                pk.y = __float_as_uint(v[1]);
+                                pk.z = __float_as_uint(v[2]);
+                                pk.w = __float_as_uint(v[3]);
+                            }
+                            st_shared_v4(stg + lane * 128 + ((q ^ (lane & 7)) << 4), pk);
+                        }
+                        __syncwarp();
+                        uint8_t* obase = reinterpret_cast<uint8_t*>(P.out);
+#pragma unroll
+                        for (int it = 0; it < 8; ++it) {
+                            const int rr = it * 4 + (lane >> 3);
+                            const int q = lane & 7;
+                            const uint4 pk = ld_shared_v4(stg + rr * 128 + ((q ^ (rr & 7)) << 4));
+                            const unsigned long long off = __shfl_sync(0xffffffffu, static_cast<unsigned long long>(row_off), rr);
+                            const int okr = __shfl_sync(0xffffffffu, row_valid ? 1 : 0, rr);
+                            if (okr) *reinterpret_cast<uint4*>(obase + (off + cg) * esz + q * 16) = pk;
+                        }
+                        __syncwarp();
+                    } else {
+                        // ragged tail or unaligned rows: per-thread stores, 32 columns at a time
+#pragma unroll 1
+                        for (int half = 0; half < 2; ++half) {
+                            const int cgh = cg + half * 32;
+                            const int nh = min(32, ncols - half * 32);
+                            if (nh <= 0) break;
+                            float v[32];
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) {
+                                float x = __uint_as_float(half == 0 ? r0[j] : r1[j]);
+                                if (has_bias && j < nh) x += P.bias[cgh + j];
+                                if (P.round_f16) x = round_through_f16(x);
+                                v[j] = x;
+                            }
+                            if (row_valid) store_row_chunk(P, v, row_off, col_stride, cgh, nh);
+                        }
+                        __syncwarp();
+                    }
+                }
+            } else
             for (int c0 = 0; c0 < P.bn; c0 += 32) {
                 if (col_base + c0 >= P.c_out) break;  // uniform across the warp
                 uint32_t r[32];
