@@ -111,12 +111,12 @@ def conv_flops(batch, c_in, hw, c_out, k, s, p):
     return 3 * 2.0 * batch * ho * ho * c_out * c_in * k * k
 
 
-def make_linear_host(seed):
+def make_linear_host(seed, sweep):
     """Pinned host buffers of one step's inputs, and the parameters."""
     import torch
     rng = np.random.default_rng(seed)
     layers = []
-    for rows, d in LINEAR_SWEEP:
+    for rows, d in sweep:
         bound = np.sqrt(6.0 / (d + 4 * d))
         layers.append({
             "rows": rows, "d": d,
@@ -149,7 +149,11 @@ def run_gpu(args):
     flops_per_launch = []  # algorithmic FLOPs of each contraction launch of one step, in launch order
 
     if args.workload == "linear":
-        host = make_linear_host(1235 + rank)
+        sweep = LINEAR_SWEEP
+        if args.only:  # profiling aid: one shape of the sweep, e.g. --only 16384x1024
+            r_, d_ = (int(v) for v in args.only.lower().split("x"))
+            sweep = [(r_, d_)]
+        host = make_linear_host(1235 + rank, sweep)
         layers = []
         for h in host:
             rows, d = h["rows"], h["d"]
@@ -416,6 +420,7 @@ def main():
     ap.add_argument("--impl", default="nectarml_b200", choices=["nectarml_b200", "reference"])
     ap.add_argument("--workload", default="linear", choices=["linear", "resnet"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--only", default="", help="linear workload: restrict the sweep to ROWSxD (for profiling captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <algorithm>
@@ -71,6 +72,13 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
+// Tuning overrides for experiments (unset in normal use): NML_TUNE_STAGES caps the ring depth,
+// NML_TUNE_BN caps the tile width, NML_TUNE_L2PROMO picks the TMA L2 promotion (0..3).
+static int tune_env(const char* name, int dflt) {
+    const char* v = getenv(name);
+    return (v && *v) ? atoi(v) : dflt;
+}
+
 enum { SWZ_NONE = 0, SWZ_128B = 1, SWZ_128B_ATOM32 = 2 };
 
 // Tensor map over a dense tensor given fastest-first dims; strides are the dense ones.
@@ -96,7 +104,8 @@ static int encode_map(CUtensorMap* tm, const void* ptr, int elem_bytes, int rank
                     swizzle == SWZ_128B ? CU_TENSOR_MAP_SWIZZLE_128B
                     : swizzle == SWZ_128B_ATOM32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
                                                  : CU_TENSOR_MAP_SWIZZLE_NONE,
-                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                    static_cast<CUtensorMapL2promotion>(tune_env("NML_TUNE_L2PROMO", 3)),
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         snprintf(g_last_error, sizeof(g_last_error),
                  "cuTensorMapEncodeTiled failed (%d): rank %d dims %llu %llu %llu %llu box %u %u %u %u",
@@ -238,13 +247,22 @@ static void choose_box(int bits, int gw, int gh, int gn, int s_w, int s_h, int* 
     }
 }
 
+#ifdef NML_TRACE
+static long long* g_trace_buf = nullptr;
+extern "C" void nml_trace_set(long long* p) { g_trace_buf = p; }
+#endif
+
 static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
     const int stage_bytes = kStageABytes + P.bn * 128;
     int stages = std::min(8, (232448 - 1024 - 256 - kStagingBytes) / stage_bytes);
+    stages = std::max(2, std::min(stages, tune_env("NML_TUNE_STAGES", 8)));
     P.stages = stages;
     size_t smem = static_cast<size_t>(stages) * stage_bytes + kStagingBytes + 1024 + 256;
     smem = std::max<size_t>(smem, 120 * 1024);  // one CTA per SM: each allocates its own TMEM
     P.err = ds->err;
+#ifdef NML_TRACE
+    P.trace = g_trace_buf;
+#endif
     int grid = std::min(P.num_tiles, ds->sms);
     if (grid <= 0) return NML_OK;
     const bool rec = g_prof.on && g_prof.n < g_prof.cap;
@@ -346,7 +364,8 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     P.a_mn_major = 0;
     P.b_mn_major = b_mn_major;
     P.batch = f.batch;
-    P.n_tiles = ceil_div(N, 256);
+    const int bn_cap = std::max(64, std::min(256, tune_env("NML_TUNE_BN", 256)));
+    P.n_tiles = ceil_div(N, bn_cap);
     P.bn = static_cast<int>(round_up(ceil_div(N, P.n_tiles), b_mn_major ? 64 : 32));
     P.out = f.out;
     P.bias = bias32;

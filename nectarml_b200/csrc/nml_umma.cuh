@@ -87,9 +87,21 @@ struct KParams {
     int out_h, out_w;    // output image
     int ld_out;          // NHWC: elements between consecutive pixels
     int* err;
+#ifdef NML_TRACE
+    long long* trace;  // [cta][tile iteration][8] clock64 stamps, diagnosis builds only
+#endif
     Phase phases[kMaxPhases];
     Tap taps[kMaxTaps];
 };
+
+#ifdef NML_TRACE
+#define NML_STAMP(titer, slot)                                                                  \
+    do {                                                                                        \
+        if (P.trace && (titer) < 64) P.trace[(static_cast<size_t>(blockIdx.x) * 64 + (titer)) * 8 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define NML_STAMP(titer, slot) do {} while (0)
+#endif
 
 __device__ __forceinline__ float round_through_f16(float v) {
     return __half2float(__float2half_rn(v));
@@ -385,6 +397,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     break;
                 }
                 tc_fence_after();
+                NML_STAMP(titer, 0);
                 const uint32_t d_tmem = tmem_base + buf * P.bn;
                 for (int it = 0; it < k_iters; ++it) {
                     if (!mbar_wait(smem_u32(&full_bar[stage]), parity, abort_flag, P.err,
@@ -392,6 +405,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         ok = false;
                         break;
                     }
+                    if (it == 0) NML_STAMP(titer, 1);
                     tc_fence_after();
                     uint32_t sa = smem_u32(smem + stage * stage_bytes);
                     uint32_t sb = sa + kStageABytes;
@@ -412,6 +426,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     }
                 }
                 if (!ok) break;
+                NML_STAMP(titer, 2);
                 if (k_iters > 0)
                     umma_commit(smem_u32(&tfull_bar[buf]));
                 else
@@ -479,87 +494,112 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 break;
             }
             tc_fence_after();
+            if (threadIdx.x == 64) NML_STAMP(titer, 3);
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * P.bn;
             const int col_base = ntile * P.bn;
             if (P.mode == MODE_FPROP && P.out_mode == OUT_NHWC) {
-                // Row-major output: each 128-byte piece of a row (64 fp16 / 32 fp32 columns) goes
+                // Row-major output.  Each 128-byte piece of a row (64 fp16 / 32 fp32 columns) goes
                 // through a swizzled shared-memory tile so that a warp store writes four full
-                // 128-byte row pieces instead of 32 scattered 16-byte ones.
+                // 128-byte row pieces instead of 32 scattered 16-byte ones.  The TMEM load of the
+                // next piece is in flight while the current one is written out, and the bias is
+                // added on the way out, where each lane owns the same 16 bytes of every row.
                 const int cpi = P.out_f16 ? 64 : 32;
                 const int esz = P.out_f16 ? 2 : 4;
                 const uint32_t stg = smem_u32(staging) + (warp - 2) * 4096;
+                const bool has_bias = (P.bias != nullptr);
                 const bool aligned = ((static_cast<size_t>(P.ld_out) * esz) & 15) == 0 &&
                                      (reinterpret_cast<uintptr_t>(P.out) & 15) == 0 &&
                                      (reinterpret_cast<uintptr_t>(P.bias) & 15) == 0;
+                // rows this lane writes out: rr = it*4 + lane/8
+                unsigned long long my_off[8];
+                uint32_t my_ok = 0;
+#pragma unroll
+                for (int it = 0; it < 8; ++it) {
+                    const int rr = it * 4 + (lane >> 3);
+                    my_off[it] = __shfl_sync(0xffffffffu, static_cast<unsigned long long>(row_off), rr);
+                    my_ok |= (__shfl_sync(0xffffffffu, row_valid ? 1u : 0u, rr) & 1u) << it;
+                }
+                const int q = lane & 7;
+                uint8_t* obase = reinterpret_cast<uint8_t*>(P.out);
+                uint32_t r0[32], r1[32];
+                const bool live = (k_iters > 0);
+                if (!live) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
+                }
+                if (live && col_base < P.c_out) {
+                    tmem_ld_32x32(t_row, r0);
+                    if (cpi == 64 && 32 < P.bn) tmem_ld_32x32(t_row + 32, r1);
+                    tmem_ld_wait();
+                }
                 for (int c0 = 0; c0 < P.bn; c0 += cpi) {
                     const int cg = col_base + c0;
                     if (cg >= P.c_out) break;  // uniform across the warp
                     const int ncols = min(min(cpi, P.bn - c0), P.c_out - cg);
-                    uint32_t r0[32], r1[32];
-                    const bool second = (cpi == 64) && (c0 + 32 < P.bn);
-                    if (k_iters > 0) {
-                        tmem_ld_32x32(t_row + c0, r0);
-                        if (second) tmem_ld_32x32(t_row + c0 + 32, r1);
-                        tmem_ld_wait();
-                    }
-                    if (k_iters == 0) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) r0[j] = 0u;
-                    }
-                    if (k_iters == 0 || !second) {
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) r1[j] = 0u;
-                    }
-                    const bool has_bias = (P.bias != nullptr);
+                    const int cn = c0 + cpi;   // next piece
+                    const bool more = live && cn < P.bn && col_base + cn < P.c_out;
                     if (ncols == cpi && aligned) {
 #pragma unroll
-                        for (int q = 0; q < 8; ++q) {
-                            float v[8];
+                        for (int qq = 0; qq < 8; ++qq) {
                             uint4 pk;
                             if (P.out_f16) {
-#pragma unroll
-                                for (int j = 0; j < 8; ++j)
-                                    v[j] = __uint_as_float(q < 4 ? r0[(8 * q + j) & 31] : r1[(8 * q + j) & 31]);
-                                if (has_bias) {
-                                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 8 * q));
-                                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 8 * q + 4));
-                                    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                                    v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
-                                }
-                                pk.x = pack_half2(v[0], v[1]);
-                                pk.y = pack_half2(v[2], v[3]);
-                                pk.z = pack_half2(v[4], v[5]);
-                                pk.w = pack_half2(v[6], v[7]);
+                                const uint32_t* src = (qq < 4) ? &r0[8 * qq] : &r1[8 * (qq - 4)];
+                                pk.x = pack_half2(__uint_as_float(src[0]), __uint_as_float(src[1]));
+                                pk.y = pack_half2(__uint_as_float(src[2]), __uint_as_float(src[3]));
+                                pk.z = pack_half2(__uint_as_float(src[4]), __uint_as_float(src[5]));
+                                pk.w = pack_half2(__uint_as_float(src[6]), __uint_as_float(src[7]));
                             } else {
-#pragma unroll
-                                for (int j = 0; j < 4; ++j) v[j] = __uint_as_float(r0[4 * q + j]);
-                                if (has_bias) {
-                                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 4 * q));
-                                    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                                }
-                                if (P.round_f16) {
-#pragma unroll
-                                    for (int j = 0; j < 4; ++j) v[j] = round_through_f16(v[j]);
-                                }
-                                pk.x = __float_as_uint(v[0]);
-                                pk.y = __float_as_uint(v[1]);
-                                pk.z = __float_as_uint(v[2]);
-                                pk.w = __float_as_uint(v[3]);
+                                pk.x = r0[4 * qq]; pk.y = r0[4 * qq + 1]; pk.z = r0[4 * qq + 2]; pk.w = r0[4 * qq + 3];
                             }
-                            st_shared_v4(stg + lane * 128 + ((q ^ (lane & 7)) << 4), pk);
+                            st_shared_v4(stg + lane * 128 + ((qq ^ (lane & 7)) << 4), pk);
+                        }
+                        if (more) {  // registers are free again: start the next TMEM load now
+                            tmem_ld_32x32(t_row + cn, r0);
+                            if (cpi == 64 && cn + 32 < P.bn) tmem_ld_32x32(t_row + cn + 32, r1);
                         }
                         __syncwarp();
-                        uint8_t* obase = reinterpret_cast<uint8_t*>(P.out);
+                        // this lane's slice of the bias: columns cg + q*8 .. +7 (fp16) or cg + q*4 .. +3 (fp32)
+                        float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
+                        if (has_bias) {
+                            if (P.out_f16) {
+                                b0 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 8 * q));
+                                b1 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 8 * q + 4));
+                            } else {
+                                b0 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 4 * q));
+                            }
+                        }
+                        const __half2 hb0 = __floats2half2_rn(b0.x, b0.y), hb1 = __floats2half2_rn(b0.z, b0.w);
+                        const __half2 hb2 = __floats2half2_rn(b1.x, b1.y), hb3 = __floats2half2_rn(b1.z, b1.w);
 #pragma unroll
                         for (int it = 0; it < 8; ++it) {
                             const int rr = it * 4 + (lane >> 3);
-                            const int q = lane & 7;
-                            const uint4 pk = ld_shared_v4(stg + rr * 128 + ((q ^ (rr & 7)) << 4));
-                            const unsigned long long off = __shfl_sync(0xffffffffu, static_cast<unsigned long long>(row_off), rr);
-                            const int okr = __shfl_sync(0xffffffffu, row_valid ? 1 : 0, rr);
-                            if (okr) *reinterpret_cast<uint4*>(obase + (off + cg) * esz + q * 16) = pk;
+                            uint4 pk = ld_shared_v4(stg + rr * 128 + ((q ^ (rr & 7)) << 4));
+                            if (has_bias) {
+                                if (P.out_f16) {
+                                    // fp16 add on the fp16-rounded product, as the reference's bias kernel does
+                                    __half2 h;
+                                    h = __hadd2(*reinterpret_cast<__half2*>(&pk.x), hb0); pk.x = *reinterpret_cast<uint32_t*>(&h);
+                                    h = __hadd2(*reinterpret_cast<__half2*>(&pk.y), hb1); pk.y = *reinterpret_cast<uint32_t*>(&h);
+                                    h = __hadd2(*reinterpret_cast<__half2*>(&pk.z), hb2); pk.z = *reinterpret_cast<uint32_t*>(&h);
+                                    h = __hadd2(*reinterpret_cast<__half2*>(&pk.w), hb3); pk.w = *reinterpret_cast<uint32_t*>(&h);
+                                } else {
+                                    pk.x = __float_as_uint(__uint_as_float(pk.x) + b0.x);
+                                    pk.y = __float_as_uint(__uint_as_float(pk.y) + b0.y);
+                                    pk.z = __float_as_uint(__uint_as_float(pk.z) + b0.z);
+                                    pk.w = __float_as_uint(__uint_as_float(pk.w) + b0.w);
+                                }
+                            }
+                            if (!P.out_f16 && P.round_f16) {
+                                pk.x = __float_as_uint(round_through_f16(__uint_as_float(pk.x)));
+                                pk.y = __float_as_uint(round_through_f16(__uint_as_float(pk.y)));
+                                pk.z = __float_as_uint(round_through_f16(__uint_as_float(pk.z)));
+                                pk.w = __float_as_uint(round_through_f16(__uint_as_float(pk.w)));
+                            }
+                            if ((my_ok >> it) & 1u)
+                                *reinterpret_cast<uint4*>(obase + (my_off[it] + cg) * esz + q * 16) = pk;
                         }
                         __syncwarp();
+                        if (more) tmem_ld_wait();
                     } else {
                         // ragged tail or unaligned rows: per-thread stores, 32 columns at a time
 #pragma unroll 1
@@ -570,14 +610,19 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                             float v[32];
 #pragma unroll
                             for (int j = 0; j < 32; ++j) {
-                                float x = __uint_as_float(half == 0 ? r0[j] : r1[j]);
-                                if (has_bias && j < nh) x += P.bias[cgh + j];
-                                if (P.round_f16) x = round_through_f16(x);
-                                v[j] = x;
+                                float xv = __uint_as_float(half == 0 ? r0[j] : r1[j]);
+                                if (has_bias && j < nh) xv += P.bias[cgh + j];
+                                if (P.round_f16) xv = round_through_f16(xv);
+                                v[j] = xv;
                             }
                             if (row_valid) store_row_chunk(P, v, row_off, col_stride, cgh, nh);
                         }
                         __syncwarp();
+                        if (more) {
+                            tmem_ld_32x32(t_row + cn, r0);
+                            if (cpi == 64 && cn + 32 < P.bn) tmem_ld_32x32(t_row + cn + 32, r1);
+                            tmem_ld_wait();
+                        }
                     }
                 }
             } else
@@ -616,6 +661,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             }
             tc_fence_before();
             __syncwarp();
+            if (threadIdx.x == 64) NML_STAMP(titer, 4);
             if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[buf]));
         }
     }
