@@ -83,7 +83,8 @@ enum { SWZ_NONE = 0, SWZ_128B = 1, SWZ_128B_ATOM32 = 2 };
 
 // Tensor map over a dense tensor given fastest-first dims; strides are the dense ones.
 static int encode_map(CUtensorMap* tm, const void* ptr, int elem_bytes, int rank, const uint64_t* dims,
-                      const uint32_t* box, const uint32_t* estr, int swizzle) {
+                      const uint32_t* box, const uint32_t* estr, int swizzle,
+                      const uint64_t* stride_bytes = nullptr) {
     EncodeTiledFn fn = get_encode_fn();
     if (!fn) {
         snprintf(g_last_error, sizeof(g_last_error), "cuTensorMapEncodeTiled not available");
@@ -97,7 +98,7 @@ static int encode_map(CUtensorMap* tm, const void* ptr, int elem_bytes, int rank
         b[i] = box[i];
         es[i] = estr[i];
         pitch *= dims[i];
-        if (i + 1 < rank) gstr[i] = pitch;  // stride of dim i+1
+        if (i + 1 < rank) gstr[i] = stride_bytes ? stride_bytes[i] : pitch;  // stride of dim i+1
     }
     CUresult r = fn(tm, elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32,
                     rank, const_cast<void*>(ptr), gdim, gstr, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -262,6 +263,8 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
     P.err = ds->err;
 #ifdef NML_TRACE
     P.trace = g_trace_buf;
+    P.dbg_skip = tune_env("NML_DBG_SKIP", 0);
+    P.dbg_alt = tune_env("NML_DBG_ALT", 0);
 #endif
     int grid = std::min(P.num_tiles, ds->sms);
     if (grid <= 0) return NML_OK;
@@ -452,6 +455,15 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
             uint64_t bdims[2] = {static_cast<uint64_t>(direct_w ? K : T * kp), static_cast<uint64_t>(N)};
             uint32_t bbox[2] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(P.bn)};
             rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 2, bdims, bbox, one, SWZ_128B);
+        } else if (N % mi.kb == 0) {
+            // one box per stage: the outermost dimension walks the 128-byte column groups
+            P.b_grouped = 1;
+            uint64_t bdims[3] = {static_cast<uint64_t>(mi.kb), static_cast<uint64_t>(K), static_cast<uint64_t>(N / mi.kb)};
+            uint64_t bstr[2] = {static_cast<uint64_t>(N) * mi.es, static_cast<uint64_t>(mi.kb) * mi.es};
+            uint32_t bbox[3] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(mi.kb),
+                                static_cast<uint32_t>(P.bn / mi.kb)};
+            uint32_t one3[3] = {1, 1, 1};
+            rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 3, bdims, bbox, one3, SWZ_128B, bstr);
         } else {
             uint64_t bdims[2] = {static_cast<uint64_t>(N), static_cast<uint64_t>(K)};
             uint32_t bbox[2] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(mi.kb)};
@@ -557,14 +569,35 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
         uint32_t abox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>((1 << P.wb_log2) * g.s_w),
                             static_cast<uint32_t>((1 << P.hb_log2) * g.s_h), static_cast<uint32_t>(1 << P.nb_log2)};
         uint32_t aes[4] = {1, static_cast<uint32_t>(g.s_w), static_cast<uint32_t>(g.s_h), 1};
-        rc = encode_map(&P.tmA[pl], pa[pl], mi.es, 4, adims, abox, aes, mn_swz);
+        const int G = kTileM / mi.kb;
+        if (cpa % mi.kb == 0 && P.c_blocks % G == 0) {
+            P.a_grouped = 1;
+            uint64_t d5[5] = {static_cast<uint64_t>(mi.kb), adims[1], adims[2], adims[3], static_cast<uint64_t>(cpa / mi.kb)};
+            uint64_t s5[4] = {static_cast<uint64_t>(cpa) * mi.es, adims[1] * cpa * mi.es, adims[1] * adims[2] * cpa * mi.es,
+                              static_cast<uint64_t>(mi.kb) * mi.es};
+            uint32_t b5[5] = {abox[0], abox[1], abox[2], abox[3], static_cast<uint32_t>(G)};
+            uint32_t e5[5] = {1, aes[1], aes[2], 1, 1};
+            rc = encode_map(&P.tmA[pl], pa[pl], mi.es, 5, d5, b5, e5, mn_swz, s5);
+        } else {
+            rc = encode_map(&P.tmA[pl], pa[pl], mi.es, 4, adims, abox, aes, mn_swz);
+        }
         if (rc) return rc;
         uint64_t bdims[4] = {static_cast<uint64_t>(cpb), static_cast<uint64_t>(g.plain_w),
                              static_cast<uint64_t>(g.plain_h), static_cast<uint64_t>(g.batch)};
         uint32_t bbox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(1 << P.wb_log2),
                             static_cast<uint32_t>(1 << P.hb_log2), static_cast<uint32_t>(1 << P.nb_log2)};
         uint32_t bes[4] = {1, 1, 1, 1};
-        rc = encode_map(&P.tmB[pl], pb[pl], mi.es, 4, bdims, bbox, bes, mn_swz);
+        if (cpb % mi.kb == 0) {
+            P.b_grouped = 1;
+            uint64_t d5[5] = {static_cast<uint64_t>(mi.kb), bdims[1], bdims[2], bdims[3], static_cast<uint64_t>(cpb / mi.kb)};
+            uint64_t s5[4] = {static_cast<uint64_t>(cpb) * mi.es, bdims[1] * cpb * mi.es, bdims[1] * bdims[2] * cpb * mi.es,
+                              static_cast<uint64_t>(mi.kb) * mi.es};
+            uint32_t b5[5] = {bbox[0], bbox[1], bbox[2], bbox[3], static_cast<uint32_t>(P.bn / mi.kb)};
+            uint32_t e5[5] = {1, 1, 1, 1, 1};
+            rc = encode_map(&P.tmB[pl], pb[pl], mi.es, 5, d5, b5, e5, mn_swz, s5);
+        } else {
+            rc = encode_map(&P.tmB[pl], pb[pl], mi.es, 4, bdims, bbox, bes, mn_swz);
+        }
         if (rc) return rc;
     }
     return launch_kernel(P, ds, st);

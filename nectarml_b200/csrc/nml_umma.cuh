@@ -66,6 +66,8 @@ struct KParams {
     int bn;              // UMMA N of one tile
     int stages;
     int a_mn_major, b_mn_major;
+    int a_grouped, b_grouped;  // MN-major operand fetched as ONE box whose outermost dimension walks
+                               // the 128-byte column groups (needs the channel count to be a multiple of kb)
     int kind;            // KIND_F16 / KIND_TF32
     int passes;          // 1, or 3 for the 3xTF32 split (hi*lo, lo*hi, hi*hi in that order)
     int kb;              // elements per 128-byte row (64 fp16, 32 tf32)
@@ -89,6 +91,8 @@ struct KParams {
     int* err;
 #ifdef NML_TRACE
     long long* trace;  // [cta][tile iteration][8] clock64 stamps, diagnosis builds only
+    int dbg_alt;
+    int dbg_skip;      // 1: skip the B loads, 2: skip the A loads (results are garbage; timing only)
 #endif
     Phase phases[kMaxPhases];
     Tap taps[kMaxTaps];
@@ -249,13 +253,12 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     int w0 = (tw << P.wb_log2) * P.a_stride_w;
                     int h0 = (th << P.hb_log2) * P.a_stride_h;
                     int n0 = tn << P.nb_log2;
-                    int per_pass = ph.tap_count * P.c_blocks;
-                    int k_iters = P.passes * per_pass;
+                    int k_iters = P.passes * ph.tap_count * P.c_blocks;
+#ifdef NML_TRACE
+                    if (P.dbg_skip == 3) k_iters = 0;  // MMA-rate experiment: no loads at all
+#endif
+                    int pass = 0, t = 0, cb = 0;
                     for (int it = 0; it < k_iters; ++it) {
-                        int pass = it / per_pass;
-                        int rem = it - pass * per_pass;
-                        int t = rem / P.c_blocks;
-                        int cb = rem - t * P.c_blocks;
                         const Tap& tap = P.taps[ph.tap_begin + t];
                         // 3xTF32 order: hi*lo, lo*hi, then hi*hi -- the small cross terms go in
                         // while the accumulator is small, so the tensor core's truncating
@@ -274,6 +277,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         tma_load_4d(sa, ta, fb, cb * P.kb, w0 + tap.dw, h0 + tap.dh, n0);
                         if (!P.b_mn_major) {
                             tma_load_2d(sb, tb, fb, tap.wk + cb * P.kb, ntile * P.bn);
+                        } else if (P.b_grouped) {
+                            tma_load_3d(sb, tb, fb, 0, tap.wk + cb * P.kb, (ntile * P.bn) / P.kb);
                         } else {
                             int nb = P.bn / P.kb;
                             for (int j = 0; j < nb; ++j)
@@ -284,6 +289,13 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         if (++stage == P.stages) {
                             stage = 0;
                             parity ^= 1;
+                        }
+                        if (++cb == P.c_blocks) {
+                            cb = 0;
+                            if (++t == ph.tap_count) {
+                                t = 0;
+                                ++pass;
+                            }
                         }
                     }
                 } else {  // MODE_WGRAD
@@ -300,10 +312,14 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     for (int pass = 0; ok && pass < P.passes; ++pass) {
                         const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
                         const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
+                        int tw = kb_begin % P.ktiles_w;
+                        int th = (kb_begin / P.ktiles_w) % P.ktiles_h;
+                        int tn = kb_begin / (P.ktiles_w * P.ktiles_h);
+                        // groups of this M tile: with a_grouped they share one tap
+                        const int g0 = min(mt * g_per_tile, P.groups_total - 1);
+                        const int t0 = g0 / P.c_blocks;
+                        const int cib0 = g0 - t0 * P.c_blocks;
                         for (int kbi = kb_begin; kbi < kb_end; ++kbi) {
-                            int tw = kbi % P.ktiles_w;
-                            int th = (kbi / P.ktiles_w) % P.ktiles_h;
-                            int tn = kbi / (P.ktiles_w * P.ktiles_h);
                             int w0 = tw << P.wb_log2, h0 = th << P.hb_log2, n0 = tn << P.nb_log2;
                             if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag,
                                            P.err, ERR_WAIT_EMPTY)) {
@@ -314,21 +330,38 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                             uint32_t sa = smem_u32(smem + stage * stage_bytes);
                             uint32_t sb = sa + kStageABytes;
                             mbar_arrive_expect_tx(fb, tx_bytes);
-                            for (int g = 0; g < na; ++g) {
-                                int gi = min(mt * g_per_tile + g, P.groups_total - 1);
-                                int t = gi / P.c_blocks;
-                                int cib = gi - t * P.c_blocks;
-                                const Tap& tap = P.taps[t];
-                                tma_load_4d(sa + g * box_bytes, ta, fb, cib * P.kb,
-                                            w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0);
+                            if (P.a_grouped) {
+                                const Tap& tap = P.taps[t0];
+                                tma_load_5d(sa, ta, fb, 0, w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0,
+                                            cib0);
+                            } else {
+                                for (int g = 0; g < na; ++g) {
+                                    int gi = min(mt * g_per_tile + g, P.groups_total - 1);
+                                    int t = gi / P.c_blocks;
+                                    int cib = gi - t * P.c_blocks;
+                                    const Tap& tap = P.taps[t];
+                                    tma_load_4d(sa + g * box_bytes, ta, fb, cib * P.kb,
+                                                w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0);
+                                }
                             }
-                            for (int j = 0; j < nb; ++j)
-                                tma_load_4d(sb + j * box_bytes, tb, fb, ntile * P.bn + j * P.kb, w0,
-                                            h0, n0);
+                            if (P.b_grouped) {
+                                tma_load_5d(sb, tb, fb, 0, w0, h0, n0, (ntile * P.bn) / P.kb);
+                            } else {
+                                for (int j = 0; j < nb; ++j)
+                                    tma_load_4d(sb + j * box_bytes, tb, fb, ntile * P.bn + j * P.kb, w0,
+                                                h0, n0);
+                            }
                             ++issued;
                             if (++stage == P.stages) {
                                 stage = 0;
                                 parity ^= 1;
+                            }
+                            if (++tw == P.ktiles_w) {
+                                tw = 0;
+                                if (++th == P.ktiles_h) {
+                                    th = 0;
+                                    ++tn;
+                                }
                             }
                         }
                     }
@@ -358,74 +391,86 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
     }
     // ---------------------------------------------------------- MMA issuer --
     else if (warp == 1) {
-        if (lane == 0) {
-            const uint32_t idesc = make_instr_desc(P.kind, P.a_mn_major, P.b_mn_major, kTileM, P.bn);
-            const uint32_t lbo_a = P.a_mn_major ? box_bytes : 16;
-            const uint32_t lbo_b = P.b_mn_major ? box_bytes : 16;
-            const int umma_k = (P.kind == KIND_F16) ? 16 : 8;
-            // MN-major tf32 operands use the 32-byte-chunk flavour of the 128-byte swizzle
-            const bool a32 = P.a_mn_major && P.kind == KIND_TF32;
-            const bool b32 = P.b_mn_major && P.kind == KIND_TF32;
-            const uint32_t lay_a = a32 ? 1 : 2, lay_b = b32 ? 1 : 2;
-            const uint32_t sbo_a = a32 ? 512 : 1024, sbo_b = b32 ? 512 : 1024;
-            // descriptor start-address advance per UMMA, in 16-byte units
-            const uint32_t adv_a = P.a_mn_major ? (umma_k * 128) >> 4 : 2;
-            const uint32_t adv_b = P.b_mn_major ? (umma_k * 128) >> 4 : 2;
-            int stage = 0;
-            uint32_t parity = 0;
-            bool ok = true;
-            int titer = 0;
-            for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x, ++titer) {
-                int k_iters;
-                if (P.mode == MODE_FPROP) {
-                    int p = 0;
-                    while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
-                    k_iters = P.passes * P.phases[p].tap_count * P.c_blocks;
-                } else {
-                    int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
-                    int z = (tile / P.n_tiles) / m_tiles;
-                    int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
-                    int kb_begin = z * per;
-                    int kb_end = min(kb_begin + per, P.kblocks_total);
-                    k_iters = P.passes * max(kb_end - kb_begin, 0);
-                }
-                const int buf = titer & 1;
-                const uint32_t tpar = (titer >> 1) & 1;
-                if (!mbar_wait(smem_u32(&tempty_bar[buf]), tpar ^ 1, abort_flag, P.err,
-                               ERR_WAIT_TMEM_EMPTY)) {
+        // The whole warp walks the loop (so loop state and descriptors stay warp-uniform and every
+        // lane observes the barriers itself); lane 0 issues the MMAs and their commits.  The loop
+        // body is kept minimal: one MMA must be issued every 128 clocks to keep the tensor pipe
+        // busy, and everything here is on that single thread's critical path.
+        const uint32_t idesc = make_instr_desc(P.kind, P.a_mn_major, P.b_mn_major, kTileM, P.bn);
+        const uint32_t lbo_a = P.a_mn_major ? box_bytes : 16;
+        const uint32_t lbo_b = P.b_mn_major ? box_bytes : 16;
+        const int umma_k = (P.kind == KIND_F16) ? 16 : 8;
+        // MN-major tf32 operands use the 32-byte-chunk flavour of the 128-byte swizzle
+        const bool a32 = P.a_mn_major && P.kind == KIND_TF32;
+        const bool b32 = P.b_mn_major && P.kind == KIND_TF32;
+        // descriptor start-address advance per UMMA, in 16-byte units
+        const uint32_t adv_a = P.a_mn_major ? (umma_k * 128) >> 4 : 2;
+        const uint32_t adv_b = P.b_mn_major ? (umma_k * 128) >> 4 : 2;
+        const uint64_t adesc0 = make_smem_desc(smem_u32(smem), lbo_a, a32 ? 512 : 1024, a32 ? 1 : 2);
+        const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + kStageABytes, lbo_b, b32 ? 512 : 1024, b32 ? 1 : 2);
+        const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4;
+        const bool f16 = (P.kind == KIND_F16);
+        int stage = 0;
+        uint32_t parity = 0;
+        bool ok = true;
+        int titer = 0;
+        for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x, ++titer) {
+            int k_iters;
+            if (P.mode == MODE_FPROP) {
+                int p = 0;
+                while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
+                k_iters = P.passes * P.phases[p].tap_count * P.c_blocks;
+            } else {
+                int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
+                int z = (tile / P.n_tiles) / m_tiles;
+                int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
+                int kb_begin = z * per;
+                int kb_end = min(kb_begin + per, P.kblocks_total);
+                k_iters = P.passes * max(kb_end - kb_begin, 0);
+            }
+            const int buf = titer & 1;
+            const uint32_t tpar = (titer >> 1) & 1;
+            if (!mbar_wait(smem_u32(&tempty_bar[buf]), tpar ^ 1, abort_flag, P.err, ERR_WAIT_TMEM_EMPTY)) {
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            if (lane == 0) NML_STAMP(titer, 0);
+            const uint32_t d_tmem = tmem_base + buf * P.bn;
+            uint32_t acc = 0;
+            for (int it = 0; it < k_iters; ++it) {
+#ifdef NML_TRACE
+                if (P.dbg_skip != 3)
+#endif
+                if (!mbar_wait(smem_u32(&full_bar[stage]), parity, abort_flag, P.err, ERR_WAIT_FULL)) {
                     ok = false;
                     break;
                 }
+                if (it == 0 && lane == 0) NML_STAMP(titer, 1);
                 tc_fence_after();
-                NML_STAMP(titer, 0);
-                const uint32_t d_tmem = tmem_base + buf * P.bn;
-                for (int it = 0; it < k_iters; ++it) {
-                    if (!mbar_wait(smem_u32(&full_bar[stage]), parity, abort_flag, P.err,
-                                   ERR_WAIT_FULL)) {
-                        ok = false;
-                        break;
-                    }
-                    if (it == 0) NML_STAMP(titer, 1);
-                    tc_fence_after();
-                    uint32_t sa = smem_u32(smem + stage * stage_bytes);
-                    uint32_t sb = sa + kStageABytes;
-                    uint64_t adesc = make_smem_desc(sa, lbo_a, sbo_a, lay_a);
-                    uint64_t bdesc = make_smem_desc(sb, lbo_b, sbo_b, lay_b);
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        uint32_t acc = (it > 0 || j > 0) ? 1u : 0u;
-                        if (P.kind == KIND_F16)
-                            umma_f16(d_tmem, adesc + j * adv_a, bdesc + j * adv_b, idesc, acc);
-                        else
-                            umma_tf32(d_tmem, adesc + j * adv_a, bdesc + j * adv_b, idesc, acc);
+                if (lane == 0) {
+                    const uint64_t adesc = adesc0 + static_cast<uint64_t>(stage * stage_step);
+                    const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(stage * stage_step);
+                    if (f16) {
+                        umma_f16(d_tmem, adesc, bdesc, idesc, acc);
+                        umma_f16(d_tmem, adesc + adv_a, bdesc + adv_b, idesc, 1u);
+                        umma_f16(d_tmem, adesc + 2 * adv_a, bdesc + 2 * adv_b, idesc, 1u);
+                        umma_f16(d_tmem, adesc + 3 * adv_a, bdesc + 3 * adv_b, idesc, 1u);
+                    } else {
+                        umma_tf32(d_tmem, adesc, bdesc, idesc, acc);
+                        umma_tf32(d_tmem, adesc + adv_a, bdesc + adv_b, idesc, 1u);
+                        umma_tf32(d_tmem, adesc + 2 * adv_a, bdesc + 2 * adv_b, idesc, 1u);
+                        umma_tf32(d_tmem, adesc + 3 * adv_a, bdesc + 3 * adv_b, idesc, 1u);
                     }
                     umma_commit(smem_u32(&empty_bar[stage]));
-                    if (++stage == P.stages) {
-                        stage = 0;
-                        parity ^= 1;
-                    }
                 }
-                if (!ok) break;
+                acc = 1u;
+                if (++stage == P.stages) {
+                    stage = 0;
+                    parity ^= 1;
+                }
+            }
+            if (!ok) break;
+            if (lane == 0) {
                 NML_STAMP(titer, 2);
                 if (k_iters > 0)
                     umma_commit(smem_u32(&tfull_bar[buf]));
