@@ -180,10 +180,18 @@ static int prepare_activation(const void* src, int dtype, int layout, int batch,
         planes[1] = nullptr;
         *cp = c;
         if (colsum && !ws.dry) {
-            int rows_per_block = 256;
-            dim3 grid(ceil_div(c, 256), static_cast<unsigned>((pixels + rows_per_block - 1) / rows_per_block));
-            { colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
-                                                             rows_per_block); ++g_launches; }
+            // enough row blocks to fill the GPU, few enough that the atomics stay negligible
+            int col_blocks = ceil_div(c, 256);
+            int rows_per_block = static_cast<int>(std::max<size_t>(64, round_up(ceil_div(static_cast<int>(std::min<size_t>(pixels, 1u << 30)), std::max(1, 1184 / col_blocks)), 8)));
+            dim3 grid(col_blocks, static_cast<unsigned>((pixels + rows_per_block - 1) / rows_per_block));
+            if (c % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+                colsum_rows_f16x8_kernel<<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
+                                                               rows_per_block);
+                ++g_launches;
+            } else {
+                { colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
+                                                                 rows_per_block); ++g_launches; }
+            }
         }
         return NML_OK;
     }
@@ -553,11 +561,25 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     P.kblocks_total = P.ktiles_w * P.ktiles_h * ceil_div(g.batch, 1 << P.nb_log2);
     const int m_tiles = ceil_div(P.groups_total * mi.kb, kTileM);
     const int mn_tiles = m_tiles * P.n_tiles;
-    int split = std::max(1, ds->sms / mn_tiles);
-    split = std::min(split, P.kblocks_total);
-    // every slice gets at least one K block
-    int per = ceil_div(P.kblocks_total, split);
-    split = ceil_div(P.kblocks_total, per);
+    // Split K so that the CTAs finish together: the makespan is (rounds of tiles per CTA) x (K
+    // blocks per slice, plus a few blocks' worth of prologue / epilogue per tile).  Pick the split
+    // that minimises it; ties go to the smaller split (fewer atomics).
+    int split = 1;
+    {
+        long long best = -1;
+        const int max_split = std::min(P.kblocks_total, 64);
+        for (int sp = 1; sp <= max_split; ++sp) {
+            int per_sp = ceil_div(P.kblocks_total, sp);
+            int real = ceil_div(P.kblocks_total, per_sp);  // every slice gets at least one K block
+            if (real != sp) continue;
+            long long rounds = ceil_div(mn_tiles * sp, ds->sms);
+            long long cost = rounds * (per_sp + 4);
+            if (best < 0 || cost < best) {
+                best = cost;
+                split = sp;
+            }
+        }
+    }
     P.split_k = split;
     P.num_tiles = mn_tiles * split;
 

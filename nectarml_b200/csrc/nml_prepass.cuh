@@ -93,6 +93,41 @@ __global__ void __launch_bounds__(256) colsum_rows_kernel(const TIn* __restrict_
     }
 }
 
+// Vectorised column sums for fp16 rows whose length is a multiple of 8: every thread owns 8
+// adjacent columns (one 16-byte load per row), a warp covers 256 columns, blockDim.y warps take
+// interleaved rows, and each block adds its partial sums with one atomic per column.
+__global__ void __launch_bounds__(256) colsum_rows_f16x8_kernel(const __half* __restrict__ in, float* colsum,
+                                                                size_t R, int C, int rows_per_block) {
+    __shared__ float part[8][256];
+    const int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
+    const int c0 = (blockIdx.x * 32 + lane) * 8;
+    size_t r0 = static_cast<size_t>(blockIdx.y) * rows_per_block;
+    size_t r1 = r0 + rows_per_block < R ? r0 + rows_per_block : R;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (c0 < C) {
+        for (size_t r = r0 + wy; r < r1; r += 8) {
+            uint4 v = __ldg(reinterpret_cast<const uint4*>(in + r * C + c0));
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float2 f = __half22float2(h[j]);
+                acc[2 * j] += f.x;
+                acc[2 * j + 1] += f.y;
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) part[wy][lane * 8 + j] = acc[j];
+    __syncthreads();
+    const int c = blockIdx.x * 256 + threadIdx.x;
+    if (c < C) {
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) sum += part[w][threadIdx.x];
+        atomicAdd(colsum + c, sum);
+    }
+}
+
 // Weights [D0][D1][T] -> K-major operand dst[n][t][kp]:
 //   k_is_dim0 == 0 : n = D0 index, k = D1 index   (Conv2d forward, ConvTranspose2d dgrad)
 //   k_is_dim0 == 1 : n = D1 index, k = D0 index   (Conv2d dgrad, ConvTranspose2d forward)

@@ -265,11 +265,17 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         // accumulation costs them nothing
                         const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
                         const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
+#ifdef NML_TRACE
+                        long long pw0 = clock64();
+#endif
                         if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err,
                                        ERR_WAIT_EMPTY)) {
                             ok = false;
                             break;
                         }
+#ifdef NML_TRACE
+                        if (P.trace) P.trace[(static_cast<size_t>(blockIdx.x) * 64 + 63) * 8 + 6] += clock64() - pw0;
+#endif
                         uint32_t fb = smem_u32(&full_bar[stage]);
                         uint32_t sa = smem_u32(smem + stage * stage_bytes);
                         uint32_t sb = sa + kStageABytes;
@@ -392,7 +398,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
     // ---------------------------------------------------------- MMA issuer --
     else if (warp == 1) {
         // The whole warp walks the loop (so loop state and descriptors stay warp-uniform and every
-        // lane observes the barriers itself); lane 0 issues the MMAs and their commits.  The loop
+        // lane observes the barriers itself); one elected lane issues the MMAs and their commits.  The loop
         // body is kept minimal: one MMA must be issued every 128 clocks to keep the tensor pipe
         // busy, and everything here is on that single thread's critical path.
         const uint32_t idesc = make_instr_desc(P.kind, P.a_mn_major, P.b_mn_major, kTileM, P.bn);
@@ -439,15 +445,20 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             uint32_t acc = 0;
             for (int it = 0; it < k_iters; ++it) {
 #ifdef NML_TRACE
+                long long tw0 = clock64();
                 if (P.dbg_skip != 3)
 #endif
                 if (!mbar_wait(smem_u32(&full_bar[stage]), parity, abort_flag, P.err, ERR_WAIT_FULL)) {
                     ok = false;
                     break;
                 }
+#ifdef NML_TRACE
+                if (lane == 0 && P.trace && titer < 64)
+                    P.trace[(static_cast<size_t>(blockIdx.x) * 64 + titer) * 8 + 5] += clock64() - tw0;
+#endif
                 if (it == 0 && lane == 0) NML_STAMP(titer, 1);
                 tc_fence_after();
-                if (lane == 0) {
+                if (elect_one()) {  // elect.sync keeps the issue path on the uniform datapath
                     const uint64_t adesc = adesc0 + static_cast<uint64_t>(stage * stage_step);
                     const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(stage * stage_step);
                     if (f16) {
@@ -470,7 +481,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 }
             }
             if (!ok) break;
-            if (lane == 0) {
+            if (elect_one()) {
                 NML_STAMP(titer, 2);
                 if (k_iters > 0)
                     umma_commit(smem_u32(&tfull_bar[buf]));
