@@ -135,6 +135,23 @@ struct Profiler {
 };
 static Profiler g_prof;
 
+// The five instances of the contraction kernel, and the one that serves a given launch.
+typedef void (*UmmaKernel)(const KParams);
+static UmmaKernel kernel_for(const KParams& P) {
+    if (P.mode == MODE_WGRAD) return umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false>;
+    if (P.out_mode == OUT_NHWC)
+        return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC, true> : umma_conv_kernel<MODE_FPROP, OUT_NHWC, false>;
+    return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NCHW, true> : umma_conv_kernel<MODE_FPROP, OUT_NCHW, false>;
+}
+static int raise_smem_limit() {
+    UmmaKernel all[5] = {umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false>, umma_conv_kernel<MODE_FPROP, OUT_NHWC, true>,
+                         umma_conv_kernel<MODE_FPROP, OUT_NHWC, false>, umma_conv_kernel<MODE_FPROP, OUT_NCHW, true>,
+                         umma_conv_kernel<MODE_FPROP, OUT_NCHW, false>};
+    for (UmmaKernel k : all)
+        NML_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+    return NML_OK;
+}
+
 static int device_state(DeviceState** out) {
     int dev = 0;
     NML_CUDA(cudaGetDevice(&dev));
@@ -147,7 +164,8 @@ static int device_state(DeviceState** out) {
         NML_CUDA(cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev));
     }
     if (!s.attr_set) {
-        NML_CUDA(cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+        int rc_attr = raise_smem_limit();
+        if (rc_attr) return rc_attr;
         s.attr_set = true;
     }
     *out = &s;
@@ -278,7 +296,7 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
     if (grid <= 0) return NML_OK;
     const bool rec = g_prof.on && g_prof.n < g_prof.cap;
     if (rec) NML_CUDA(cudaEventRecord(g_prof.start[g_prof.n], st));
-    umma_conv_kernel<<<grid, kThreads, smem, st>>>(P);
+    kernel_for(P)<<<grid, kThreads, smem, st>>>(P);
     NML_CUDA(cudaGetLastError());
     if (rec) NML_CUDA(cudaEventRecord(g_prof.stop[g_prof.n++], st));
     ++g_launches;
@@ -928,7 +946,8 @@ static int static_state(StaticState** out) {
         NML_CUDA(cudaGetSymbolAddress(&status, g_static_status));
         NML_CUDA(cudaMemset(status, 0, sizeof(int)));
         NML_CUDA(cudaDeviceGetAttribute(&s.ds.sms, cudaDevAttrMultiProcessorCount, dev));
-        NML_CUDA(cudaFuncSetAttribute(umma_conv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
+        int rc_attr = raise_smem_limit();
+        if (rc_attr) return rc_attr;
         s.scratch = scratch;
         s.ds.err = static_cast<int*>(status);
         s.ds.attr_set = true;

@@ -52,16 +52,21 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+// Upper bound, in nanoseconds, on how long one try_wait may keep the thread suspended in hardware
+// before it returns false; a waiting thread sleeps instead of polling, which leaves the issue
+// slots of its scheduler to the warps that have work.
+constexpr uint32_t kTryWaitHintNs = 20000;
+
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t"
         ".reg .pred P;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, P;\n\t"
         "}\n"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(kTryWaitHintNs)
         : "memory");
     return ok != 0;
 }
@@ -80,7 +85,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     uint64_t t0 = 0;
     for (uint32_t it = 1;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if ((it & 0xFF) == 0) {
+        if ((it & 0xF) == 0) {
             if (*abort_flag) return false;
             uint64_t now = globaltimer_ns();
             if (t0 == 0) {

@@ -127,7 +127,7 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 }
 
 // Stores 32 (or fewer) consecutive output columns of one accumulator row.
-__device__ __forceinline__ void store_row_chunk(const KParams& P, const float (&v)[32], size_t row_off,
+__device__ __noinline__ void store_row_chunk(const KParams& P, const float (&v)[32], size_t row_off,
                                                 size_t col_stride, int cg, int ncols) {
     if (P.out_mode == OUT_NHWC) {
         if (P.out_f16) {
@@ -179,6 +179,10 @@ __device__ __forceinline__ void store_row_chunk(const KParams& P, const float (&
     }
 }
 
+// Specialised on the tile walk, the output layout and the output type so that each instance's hot
+// loops stay small: the epilogue warps run alone on their schedulers and stall on instruction fetch
+// when the straight-line code of every variant is laid out in one kernel.
+template <int kMode, int kOutMode, bool kOutF16>
 __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_constant__ KParams P) {
     extern __shared__ uint8_t smem_raw[];
     // stages need 1024-byte alignment for the 128-byte swizzle pattern
@@ -240,7 +244,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             const uint32_t a_bytes = kStageABytes;
             const uint32_t tx_bytes = a_bytes + stage_b_bytes;
             for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x) {
-                if (P.mode == MODE_FPROP) {
+                if (kMode == MODE_FPROP) {
                     int p = 0;
                     while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
                     const Phase& ph = P.phases[p];
@@ -421,7 +425,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
         int titer = 0;
         for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x, ++titer) {
             int k_iters;
-            if (P.mode == MODE_FPROP) {
+            if (kMode == MODE_FPROP) {
                 int p = 0;
                 while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
                 k_iters = P.passes * P.phases[p].tap_count * P.c_blocks;
@@ -504,7 +508,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             bool row_valid;
             size_t row_off = 0;     // NHWC / wgrad: element offset of column 0; NCHW: pixel offset
             size_t col_stride = 1;  // element distance between consecutive columns
-            if (P.mode == MODE_FPROP) {
+            if (kMode == MODE_FPROP) {
                 int p = 0;
                 while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
                 const Phase& ph = P.phases[p];
@@ -521,7 +525,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 int ow = ph.pw + P.out_stride_w * iw;
                 int oh = ph.ph + P.out_stride_h * ih;
                 k_iters = ph.tap_count;
-                if (P.out_mode == OUT_NHWC) {
+                if (kOutMode == OUT_NHWC) {
                     row_off = ((static_cast<size_t>(n) * P.out_h + oh) * P.out_w + ow) * P.ld_out;
                     col_stride = 1;
                 } else {
@@ -553,14 +557,14 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             if (threadIdx.x == 64) NML_STAMP(titer, 3);
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * P.bn;
             const int col_base = ntile * P.bn;
-            if (P.mode == MODE_FPROP && P.out_mode == OUT_NHWC) {
+            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC) {
                 // Row-major output.  Each 128-byte piece of a row (64 fp16 / 32 fp32 columns) goes
                 // through a swizzled shared-memory tile so that a warp store writes four full
                 // 128-byte row pieces instead of 32 scattered 16-byte ones.  The TMEM load of the
                 // next piece is in flight while the current one is written out, and the bias is
                 // added on the way out, where each lane owns the same 16 bytes of every row.
-                const int cpi = P.out_f16 ? 64 : 32;
-                const int esz = P.out_f16 ? 2 : 4;
+                const int cpi = kOutF16 ? 64 : 32;
+                const int esz = kOutF16 ? 2 : 4;
                 const uint32_t stg = smem_u32(staging) + (warp - 2) * 4096;
                 const bool has_bias = (P.bias != nullptr);
                 const bool aligned = ((static_cast<size_t>(P.ld_out) * esz) & 15) == 0 &&
@@ -598,7 +602,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
 #pragma unroll
                         for (int qq = 0; qq < 8; ++qq) {
                             uint4 pk;
-                            if (P.out_f16) {
+                            if (kOutF16) {
                                 const uint32_t* src = (qq < 4) ? &r0[8 * qq] : &r1[8 * (qq - 4)];
                                 pk.x = pack_half2(__uint_as_float(src[0]), __uint_as_float(src[1]));
                                 pk.y = pack_half2(__uint_as_float(src[2]), __uint_as_float(src[3]));
@@ -617,7 +621,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         // this lane's slice of the bias: columns cg + q*8 .. +7 (fp16) or cg + q*4 .. +3 (fp32)
                         float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
                         if (has_bias) {
-                            if (P.out_f16) {
+                            if (kOutF16) {
                                 b0 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 8 * q));
                                 b1 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 8 * q + 4));
                             } else {
@@ -631,7 +635,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                             const int rr = it * 4 + (lane >> 3);
                             uint4 pk = ld_shared_v4(stg + rr * 128 + ((q ^ (rr & 7)) << 4));
                             if (has_bias) {
-                                if (P.out_f16) {
+                                if (kOutF16) {
                                     // fp16 add on the fp16-rounded product, as the reference's bias kernel does
                                     __half2 h;
                                     h = __hadd2(*reinterpret_cast<__half2*>(&pk.x), hb0); pk.x = *reinterpret_cast<uint32_t*>(&h);
@@ -645,7 +649,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                                     pk.w = __float_as_uint(__uint_as_float(pk.w) + b0.w);
                                 }
                             }
-                            if (!P.out_f16 && P.round_f16) {
+                            if (!kOutF16 && P.round_f16) {
                                 pk.x = __float_as_uint(round_through_f16(__uint_as_float(pk.x)));
                                 pk.y = __float_as_uint(round_through_f16(__uint_as_float(pk.y)));
                                 pk.z = __float_as_uint(round_through_f16(__uint_as_float(pk.z)));
@@ -694,7 +698,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 }
                 const int cg = col_base + c0;
                 const int ncols = min(32, P.c_out - cg);
-                if (P.mode == MODE_WGRAD) {
+                if (kMode == MODE_WGRAD) {
                     if (row_valid && k_iters > 0) {
                         float* o = reinterpret_cast<float*>(P.out) + row_off +
                                    static_cast<size_t>(cg) * col_stride;
