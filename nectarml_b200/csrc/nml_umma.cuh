@@ -549,6 +549,23 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 row_off = static_cast<size_t>(pc) * P.n_taps + t;
                 col_stride = static_cast<size_t>(P.c_patch) * P.n_taps;
             }
+            // Row-major epilogue: this lane's bias slice for the first 128-byte piece is fetched before
+            // the wait, and each later slice one piece ahead, so the load latency never shows.
+            float4 nb0 = make_float4(0.f, 0.f, 0.f, 0.f), nb1 = nb0;
+            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC && P.bias != nullptr &&
+                (reinterpret_cast<uintptr_t>(P.bias) & 15) == 0) {
+                const int cpi0 = kOutF16 ? 64 : 32;
+                const int cgf = ntile * P.bn;
+                if (cgf + cpi0 <= P.c_out) {
+                    const int ql = lane & 7;
+                    if (kOutF16) {
+                        nb0 = __ldg(reinterpret_cast<const float4*>(P.bias + cgf + 8 * ql));
+                        nb1 = __ldg(reinterpret_cast<const float4*>(P.bias + cgf + 8 * ql + 4));
+                    } else {
+                        nb0 = __ldg(reinterpret_cast<const float4*>(P.bias + cgf + 4 * ql));
+                    }
+                }
+            }
             if (!mbar_wait(smem_u32(&tfull_bar[buf]), tpar, abort_flag, P.err, ERR_WAIT_TMEM_FULL)) {
                 ok = false;
                 break;
@@ -619,13 +636,16 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         }
                         __syncwarp();
                         // this lane's slice of the bias: columns cg + q*8 .. +7 (fp16) or cg + q*4 .. +3 (fp32)
-                        float4 b0 = make_float4(0.f, 0.f, 0.f, 0.f), b1 = b0;
-                        if (has_bias) {
-                            if (kOutF16) {
-                                b0 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 8 * q));
-                                b1 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 8 * q + 4));
-                            } else {
-                                b0 = __ldg(reinterpret_cast<const float4*>(P.bias + cg + 4 * q));
+                        const float4 b0 = nb0, b1 = nb1;
+                        if (has_bias) {  // fetch the next piece's slice now; it is used one piece later
+                            const int cgn = cg + cpi;
+                            if (c0 + cpi < P.bn && cgn + cpi <= P.c_out) {
+                                if (kOutF16) {
+                                    nb0 = __ldg(reinterpret_cast<const float4*>(P.bias + cgn + 8 * q));
+                                    nb1 = __ldg(reinterpret_cast<const float4*>(P.bias + cgn + 8 * q + 4));
+                                } else {
+                                    nb0 = __ldg(reinterpret_cast<const float4*>(P.bias + cgn + 4 * q));
+                                }
                             }
                         }
                         const __half2 hb0 = __floats2half2_rn(b0.x, b0.y), hb1 = __floats2half2_rn(b0.z, b0.w);
