@@ -600,6 +600,12 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     }
     P.split_k = split;
     P.num_tiles = mn_tiles * split;
+    // A wave of CTAs re-reads one operand in full; make that the smaller tensor.
+    {
+        const double patch_bytes = static_cast<double>(g.batch) * g.patch_h * g.patch_w * cpa * mi.es;
+        const double plain_bytes = static_cast<double>(g.batch) * g.plain_h * g.plain_w * cpb * mi.es;
+        P.m_fastest = (patch_bytes < plain_bytes) ? 1 : 0;
+    }
 
     // MN-major tf32 operands need the 32-byte-chunk swizzle, fp16 ones the plain 128-byte swizzle
     const int mn_swz = (mi.es == 4) ? SWZ_128B_ATOM32 : SWZ_128B;

@@ -81,6 +81,7 @@ struct KParams {
     int groups_total;    // taps * c_blocks column groups of kb patch channels
     int split_k, kblocks_total, ktiles_h, ktiles_w;
     int c_patch, c_plain, n_taps;
+    int m_fastest;       // wgrad tile order: consecutive CTAs share the plain operand's columns (re-read the smaller tensor)
     // epilogue
     void* out;
     const float* bias;
@@ -106,6 +107,20 @@ struct KParams {
 #else
 #define NML_STAMP(titer, slot) do {} while (0)
 #endif
+
+// Tile id -> (column tile, row tile, K slice) of a weight-gradient launch.
+__device__ __forceinline__ void decode_wgrad_tile(const KParams& P, int tile, int m_tiles, int& ntile, int& mt, int& z) {
+    const int mn = m_tiles * P.n_tiles;
+    z = tile / mn;
+    const int r = tile - z * mn;
+    if (P.m_fastest) {
+        ntile = r / m_tiles;
+        mt = r - ntile * m_tiles;
+    } else {
+        mt = r / P.n_tiles;
+        ntile = r - mt * P.n_tiles;
+    }
+}
 
 __device__ __forceinline__ float round_through_f16(float v) {
     return __half2float(__float2half_rn(v));
@@ -309,11 +324,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         }
                     }
                 } else {  // MODE_WGRAD
-                    int ntile = tile % P.n_tiles;
-                    int rest = tile / P.n_tiles;
                     int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
-                    int mt = rest % m_tiles;
-                    int z = rest / m_tiles;
+                    int ntile, mt, z;
+                    decode_wgrad_tile(P, tile, m_tiles, ntile, mt, z);
                     int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
                     int kb_begin = z * per;
                     int kb_end = min(kb_begin + per, P.kblocks_total);
@@ -431,7 +444,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 k_iters = P.passes * P.phases[p].tap_count * P.c_blocks;
             } else {
                 int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
-                int z = (tile / P.n_tiles) / m_tiles;
+                int z = tile / (P.n_tiles * m_tiles);
                 int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
                 int kb_begin = z * per;
                 int kb_end = min(kb_begin + per, P.kblocks_total);
@@ -533,11 +546,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     col_stride = static_cast<size_t>(P.out_h) * P.out_w;
                 }
             } else {
-                ntile = tile % P.n_tiles;
-                int rest = tile / P.n_tiles;
                 int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
-                int mt = rest % m_tiles;
-                int z = rest / m_tiles;
+                int mt, z;
+                decode_wgrad_tile(P, tile, m_tiles, ntile, mt, z);
                 int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
                 k_iters = max(min(z * per + per, P.kblocks_total) - z * per, 0);
                 int gi = mt * (kTileM / P.kb) + row / P.kb;
