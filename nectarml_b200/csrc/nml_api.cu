@@ -280,7 +280,10 @@ extern "C" void nml_trace_set(long long* p) { g_trace_buf = p; }
 #endif
 
 static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
-    const int stage_bytes = kStageABytes + P.bn * 128;
+    // Narrow tiles finish a 64-deep K slice in well under the barrier round trip of a stage, so they
+    // take two slices per stage (8 MMAs per round trip); 256-wide tiles already fill 512 clocks.
+    P.ka = std::max(1, std::min(2, tune_env("NML_TUNE_KA", P.bn >= 192 ? 1 : 2)));
+    const int stage_bytes = P.ka * (kStageABytes + P.bn * 128);
     int stages = std::min(8, (232448 - 1024 - 256 - kStagingBytes) / stage_bytes);
     stages = std::max(2, std::min(stages, tune_env("NML_TUNE_STAGES", 8)));
     P.stages = stages;

@@ -1,8 +1,10 @@
 // The one contraction kernel of this library: a persistent, warp-specialised
 // implicit-GEMM for sm_100a.  One CTA per SM walks a static list of output tiles.
 //
-//   warp 0      TMA producer   : tiled cp.async.bulk.tensor loads (never multicast) into a
-//                                ring of 128-byte-swizzled shared-memory stages
+//   warps 0, 6  TMA producers  : tiled cp.async.bulk.tensor loads (never multicast) into a ring of
+//                                128-byte-swizzled shared-memory stages; warp 0 fetches the A
+//                                operand, warp 6 the B operand (issuing a TMA costs its thread a
+//                                few hundred clocks, so one thread cannot feed narrow tiles)
 //   warp 1      MMA issuer     : one thread issues tcgen05.mma, accumulators live in TMEM,
 //                                two TMEM buffers so the epilogue of tile i overlaps tile i+1
 //   warps 2..5  epilogue       : tcgen05.ld -> bias / rounding / cast -> global stores
@@ -41,7 +43,7 @@ constexpr int kMaxPhases = 16;
 constexpr int kMaxTaps = 128;
 constexpr int kTileM = 128;
 constexpr int kStageABytes = kTileM * 128;
-constexpr int kThreads = 192;
+constexpr int kThreads = 224;  // warp 0: A loads, warp 1: MMA issue, warps 2-5: epilogue, warp 6: B loads
 constexpr int kStagingBytes = 4 * 4096;  // per epilogue warp: 32 rows x 128 bytes of output
 
 struct Tap {
@@ -65,6 +67,8 @@ struct KParams {
     int num_tiles, n_tiles;
     int bn;              // UMMA N of one tile
     int stages;
+    int ka;              // K atoms (128-byte-wide operand slices) per stage; narrow tiles take 2 to amortise the
+                         // per-stage barrier round trip over 8 MMAs
     int a_mn_major, b_mn_major;
     int a_grouped, b_grouped;  // MN-major operand fetched as ONE box whose outermost dimension walks
                                // the 128-byte column groups (needs the channel count to be a multiple of kb)
@@ -203,8 +207,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
     // stages need 1024-byte alignment for the 128-byte swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
-    const int stage_b_bytes = P.bn * 128;
-    const int stage_bytes = kStageABytes + stage_b_bytes;
+    const int stage_b_bytes = P.bn * 128;                        // one atom of B
+    const int stage_bytes = P.ka * (kStageABytes + stage_b_bytes);  // [A atoms][B atoms]
+    const int b_off = P.ka * kStageABytes;                        // first B atom within a stage
     uint8_t* staging = smem + P.stages * stage_bytes;  // 4 epilogue warps x 4 KB
     uint8_t* ctrl = staging + kStagingBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);          // [stages]
@@ -221,7 +226,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.stages; ++s) {
-            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&full_bar[s]), 2);  // one arrival (with its byte count) per producer warp
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
@@ -250,14 +255,15 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
     const int wb = 1 << P.wb_log2, hb = 1 << P.hb_log2;
 
     // ------------------------------------------------------------ producer --
-    if (warp == 0) {
+    if (warp == 0 || warp == 6) {
+        const bool do_a = (warp == 0), do_b = (warp == 6);
         if (lane == 0) {
             int stage = 0;
             uint32_t parity = 0;
             bool ok = true;
             int issued = 0;
             const uint32_t a_bytes = kStageABytes;
-            const uint32_t tx_bytes = a_bytes + stage_b_bytes;
+            const uint32_t tx_bytes = do_a ? a_bytes : stage_b_bytes;  // this producer's share of one atom
             for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x) {
                 if (kMode == MODE_FPROP) {
                     int p = 0;
@@ -277,6 +283,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     if (P.dbg_skip == 3) k_iters = 0;  // MMA-rate experiment: no loads at all
 #endif
                     int pass = 0, t = 0, cb = 0;
+                    int slot = 0, n_in_stage = 0;
                     for (int it = 0; it < k_iters; ++it) {
                         const Tap& tap = P.taps[ph.tap_begin + t];
                         // 3xTF32 order: hi*lo, lo*hi, then hi*hi -- the small cross terms go in
@@ -284,23 +291,21 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         // accumulation costs them nothing
                         const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
                         const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
-#ifdef NML_TRACE
-                        long long pw0 = clock64();
-#endif
-                        if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err,
-                                       ERR_WAIT_EMPTY)) {
-                            ok = false;
-                            break;
-                        }
-#ifdef NML_TRACE
-                        if (P.trace) P.trace[(static_cast<size_t>(blockIdx.x) * 64 + 63) * 8 + 6] += clock64() - pw0;
-#endif
                         uint32_t fb = smem_u32(&full_bar[stage]);
-                        uint32_t sa = smem_u32(smem + stage * stage_bytes);
-                        uint32_t sb = sa + kStageABytes;
-                        mbar_arrive_expect_tx(fb, tx_bytes);
-                        tma_load_4d(sa, ta, fb, cb * P.kb, w0 + tap.dw, h0 + tap.dh, n0);
-                        if (!P.b_mn_major) {
+                        if (slot == 0) {
+                            if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err,
+                                           ERR_WAIT_EMPTY)) {
+                                ok = false;
+                                break;
+                            }
+                            n_in_stage = min(P.ka, k_iters - it);
+                            mbar_arrive_expect_tx(fb, n_in_stage * tx_bytes);
+                        }
+                        uint32_t sa = smem_u32(smem + stage * stage_bytes) + slot * kStageABytes;
+                        uint32_t sb = smem_u32(smem + stage * stage_bytes) + b_off + slot * stage_b_bytes;
+                        if (do_a) tma_load_4d(sa, ta, fb, cb * P.kb, w0 + tap.dw, h0 + tap.dh, n0);
+                        if (!do_b) {
+                        } else if (!P.b_mn_major) {
                             tma_load_2d(sb, tb, fb, tap.wk + cb * P.kb, ntile * P.bn);
                         } else if (P.b_grouped) {
                             tma_load_3d(sb, tb, fb, 0, tap.wk + cb * P.kb, (ntile * P.bn) / P.kb);
@@ -310,10 +315,13 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                                 tma_load_2d(sb + j * box_bytes, tb, fb, ntile * P.bn + j * P.kb,
                                             tap.wk + cb * P.kb);
                         }
-                        ++issued;
-                        if (++stage == P.stages) {
-                            stage = 0;
-                            parity ^= 1;
+                        if (++slot == n_in_stage) {
+                            slot = 0;
+                            ++issued;
+                            if (++stage == P.stages) {
+                                stage = 0;
+                                parity ^= 1;
+                            }
                         }
                         if (++cb == P.c_blocks) {
                             cb = 0;
@@ -332,6 +340,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     int kb_end = min(kb_begin + per, P.kblocks_total);
                     int g_per_tile = kTileM / P.kb;
                     int na = g_per_tile, nb = P.bn / P.kb;
+                    int left = P.passes * max(kb_end - kb_begin, 0);  // K iterations still to load for this tile
+                    int slot = 0, n_in_stage = 0;
                     for (int pass = 0; ok && pass < P.passes; ++pass) {
                         const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
                         const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
@@ -344,16 +354,21 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         const int cib0 = g0 - t0 * P.c_blocks;
                         for (int kbi = kb_begin; kbi < kb_end; ++kbi) {
                             int w0 = tw << P.wb_log2, h0 = th << P.hb_log2, n0 = tn << P.nb_log2;
-                            if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag,
-                                           P.err, ERR_WAIT_EMPTY)) {
-                                ok = false;
-                                break;
-                            }
                             uint32_t fb = smem_u32(&full_bar[stage]);
-                            uint32_t sa = smem_u32(smem + stage * stage_bytes);
-                            uint32_t sb = sa + kStageABytes;
-                            mbar_arrive_expect_tx(fb, tx_bytes);
-                            if (P.a_grouped) {
+                            if (slot == 0) {
+                                if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag,
+                                               P.err, ERR_WAIT_EMPTY)) {
+                                    ok = false;
+                                    break;
+                                }
+                                n_in_stage = min(P.ka, left);
+                                mbar_arrive_expect_tx(fb, n_in_stage * tx_bytes);
+                            }
+                            --left;
+                            uint32_t sa = smem_u32(smem + stage * stage_bytes) + slot * kStageABytes;
+                            uint32_t sb = smem_u32(smem + stage * stage_bytes) + b_off + slot * stage_b_bytes;
+                            if (!do_a) {
+                            } else if (P.a_grouped) {
                                 const Tap& tap = P.taps[t0];
                                 tma_load_5d(sa, ta, fb, 0, w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0,
                                             cib0);
@@ -367,17 +382,21 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                                                 w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0);
                                 }
                             }
-                            if (P.b_grouped) {
+                            if (!do_b) {
+                            } else if (P.b_grouped) {
                                 tma_load_5d(sb, tb, fb, 0, w0, h0, n0, (ntile * P.bn) / P.kb);
                             } else {
                                 for (int j = 0; j < nb; ++j)
                                     tma_load_4d(sb + j * box_bytes, tb, fb, ntile * P.bn + j * P.kb, w0,
                                                 h0, n0);
                             }
-                            ++issued;
-                            if (++stage == P.stages) {
-                                stage = 0;
-                                parity ^= 1;
+                            if (++slot == n_in_stage) {
+                                slot = 0;
+                                ++issued;
+                                if (++stage == P.stages) {
+                                    stage = 0;
+                                    parity ^= 1;
+                                }
                             }
                             if (++tw == P.ktiles_w) {
                                 tw = 0;
@@ -429,7 +448,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
         const uint32_t adv_a = P.a_mn_major ? (umma_k * 128) >> 4 : 2;
         const uint32_t adv_b = P.b_mn_major ? (umma_k * 128) >> 4 : 2;
         const uint64_t adesc0 = make_smem_desc(smem_u32(smem), lbo_a, a32 ? 512 : 1024, a32 ? 1 : 2);
-        const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + kStageABytes, lbo_b, b32 ? 512 : 1024, b32 ? 1 : 2);
+        const uint64_t bdesc0 = make_smem_desc(smem_u32(smem) + b_off, lbo_b, b32 ? 512 : 1024, b32 ? 1 : 2);
+        const uint32_t a_atom_step = static_cast<uint32_t>(kStageABytes) >> 4;
+        const uint32_t b_atom_step = static_cast<uint32_t>(stage_b_bytes) >> 4;
         const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4;
         const bool f16 = (P.kind == KIND_F16);
         int stage = 0;
@@ -460,34 +481,36 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             if (lane == 0) NML_STAMP(titer, 0);
             const uint32_t d_tmem = tmem_base + buf * P.bn;
             uint32_t acc = 0;
-            for (int it = 0; it < k_iters; ++it) {
+            for (int it = 0; it < k_iters; it += P.ka) {
+                const int n_atoms = min(P.ka, k_iters - it);
 #ifdef NML_TRACE
-                long long tw0 = clock64();
                 if (P.dbg_skip != 3)
 #endif
                 if (!mbar_wait(smem_u32(&full_bar[stage]), parity, abort_flag, P.err, ERR_WAIT_FULL)) {
                     ok = false;
                     break;
                 }
-#ifdef NML_TRACE
-                if (lane == 0 && P.trace && titer < 64)
-                    P.trace[(static_cast<size_t>(blockIdx.x) * 64 + titer) * 8 + 5] += clock64() - tw0;
-#endif
                 if (it == 0 && lane == 0) NML_STAMP(titer, 1);
                 tc_fence_after();
                 if (elect_one()) {  // elect.sync keeps the issue path on the uniform datapath
-                    const uint64_t adesc = adesc0 + static_cast<uint64_t>(stage * stage_step);
-                    const uint64_t bdesc = bdesc0 + static_cast<uint64_t>(stage * stage_step);
-                    if (f16) {
-                        umma_f16(d_tmem, adesc, bdesc, idesc, acc);
-                        umma_f16(d_tmem, adesc + adv_a, bdesc + adv_b, idesc, 1u);
-                        umma_f16(d_tmem, adesc + 2 * adv_a, bdesc + 2 * adv_b, idesc, 1u);
-                        umma_f16(d_tmem, adesc + 3 * adv_a, bdesc + 3 * adv_b, idesc, 1u);
-                    } else {
-                        umma_tf32(d_tmem, adesc, bdesc, idesc, acc);
-                        umma_tf32(d_tmem, adesc + adv_a, bdesc + adv_b, idesc, 1u);
-                        umma_tf32(d_tmem, adesc + 2 * adv_a, bdesc + 2 * adv_b, idesc, 1u);
-                        umma_tf32(d_tmem, adesc + 3 * adv_a, bdesc + 3 * adv_b, idesc, 1u);
+                    uint64_t adesc = adesc0 + static_cast<uint64_t>(stage * stage_step);
+                    uint64_t bdesc = bdesc0 + static_cast<uint64_t>(stage * stage_step);
+                    uint32_t first = acc;
+                    for (int a = 0; a < n_atoms; ++a) {
+                        if (f16) {
+                            umma_f16(d_tmem, adesc, bdesc, idesc, first);
+                            umma_f16(d_tmem, adesc + adv_a, bdesc + adv_b, idesc, 1u);
+                            umma_f16(d_tmem, adesc + 2 * adv_a, bdesc + 2 * adv_b, idesc, 1u);
+                            umma_f16(d_tmem, adesc + 3 * adv_a, bdesc + 3 * adv_b, idesc, 1u);
+                        } else {
+                            umma_tf32(d_tmem, adesc, bdesc, idesc, first);
+                            umma_tf32(d_tmem, adesc + adv_a, bdesc + adv_b, idesc, 1u);
+                            umma_tf32(d_tmem, adesc + 2 * adv_a, bdesc + 2 * adv_b, idesc, 1u);
+                            umma_tf32(d_tmem, adesc + 3 * adv_a, bdesc + 3 * adv_b, idesc, 1u);
+                        }
+                        first = 1u;
+                        adesc += a_atom_step;
+                        bdesc += b_atom_step;
                     }
                     umma_commit(smem_u32(&empty_bar[stage]));
                 }
