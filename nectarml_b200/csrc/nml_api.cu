@@ -253,6 +253,32 @@ static int prepare_activation(const void* src, int dtype, int layout, int batch,
     return NML_OK;
 }
 
+// Few-channel path: the activation as a zero-padded [N][Hp][Wp][8] fp16 image (see pad_pack_c8_kernel).
+// Wp leaves room for the 8-pixel window of the last output column.
+struct WindowImage {
+    const void* ptr;
+    int hp, wp;
+};
+static bool window_eligible(int c, int kw, int d_w, int enc) { return c <= 8 && kw <= 8 && d_w == 1 && enc == ENC_F16; }
+static int prepare_window(const void* src, int dtype, int layout, int batch, int c, int h, int w, int p_h, int p_w,
+                          int s_w, int out_w, Bump& ws, cudaStream_t st, WindowImage* img) {
+    img->hp = h + 2 * p_h;
+    img->wp = std::max(w + 2 * p_w, (out_w - 1) * s_w + 8);
+    const size_t pixels = static_cast<size_t>(batch) * img->hp * img->wp;
+    void* p = ws.take(pixels * 16);
+    img->ptr = p;
+    if (ws.dry) return NML_OK;
+    if (!ws.fits()) return NML_ERR_WORKSPACE;
+    int blocks = static_cast<int>(std::min<size_t>((pixels + 255) / 256, 148 * 32));
+    const int nchw = (layout == NML_NCHW) ? 1 : 0;
+    if (dtype == NML_F32)
+        { pad_pack_c8_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(src), nchw, static_cast<__half*>(p), batch, c, h, w, p_h, p_w, img->hp, img->wp); ++g_launches; }
+    else
+        { pad_pack_c8_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(src), nchw, static_cast<__half*>(p), batch, c, h, w, p_h, p_w, img->hp, img->wp); ++g_launches; }
+    NML_CUDA(cudaGetLastError());
+    return NML_OK;
+}
+
 // Picks a power-of-two pixel box (w, h, n) with 2^bits pixels that covers the grid with the
 // fewest boxes; ties go to the wider box.  box extents times the element stride stay <= 256.
 static void choose_box(int bits, int gw, int gh, int gn, int s_w, int s_h, int* wl, int* hl, int* nl) {
@@ -337,21 +363,44 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         int rc = device_state(&ds);
         if (rc) return rc;
     }
+    // Few input channels (RGB stems): one K slice per kernel ROW, holding (kw, c) for 8 taps, read
+    // as overlapping 8-pixel windows of a padded 8-channel image -- instead of one mostly empty
+    // 64-channel slice per tap.
+    const bool window = !f.gather && !f.k_is_dim0 && T > 1 && window_eligible(f.a_c, f.kw, f.d_w, mi.enc);
+    WindowImage wimg = {nullptr, 0, 0};
     // activation operand
-    const void* a_planes[2];
+    const void* a_planes[2] = {nullptr, nullptr};
     int Cp = 0;
-    int rc = prepare_activation(f.a, f.a_dtype, f.a_layout, f.batch, f.a_c, f.a_h, f.a_w, mi, ws, st, a_planes, &Cp,
+    int rc;
+    if (window)
+        rc = prepare_window(f.a, f.a_dtype, f.a_layout, f.batch, f.a_c, f.a_h, f.a_w, f.p_h, f.p_w, f.s_w, f.out_w, ws, st,
+                            &wimg);
+    else
+        rc = prepare_activation(f.a, f.a_dtype, f.a_layout, f.batch, f.a_c, f.a_h, f.a_w, mi, ws, st, a_planes, &Cp,
                                 nullptr);
     if (rc) return rc;
+    if (window) a_planes[0] = wimg.ptr;
     // weight operand
-    const int c_blocks = ceil_div(K, mi.kb);
+    const int c_blocks = window ? 1 : ceil_div(K, mi.kb);
     const int kp = c_blocks * mi.kb;
     const int align = 16 / mi.es;
-    bool direct_w = f.w_direct && T == 1 && mi.enc == ENC_F16 && f.w_dtype == NML_F16 &&
+    bool direct_w = !window && f.w_direct && T == 1 && mi.enc == ENC_F16 && f.w_dtype == NML_F16 &&
                     ((f.k_is_dim0 ? N : K) % align == 0);
     const void* w_planes[2] = {f.w, nullptr};
     int b_mn_major = 0;
-    if (direct_w) {
+    if (window) {
+        void* p0 = ws.take(static_cast<size_t>(N) * f.kh * 64 * 2);
+        w_planes[0] = p0;
+        if (!ws.dry) {
+            if (!ws.fits()) return NML_ERR_WORKSPACE;
+            int blocks = std::min(ceil_div(N * f.kh * 64, 256), 148 * 8);
+            if (f.w_dtype == NML_F32)
+                { repack_weight_c8_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(f.w), static_cast<__half*>(p0), N, K, f.kh, f.kw); ++g_launches; }
+            else
+                { repack_weight_c8_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(f.w), static_cast<__half*>(p0), N, K, f.kh, f.kw); ++g_launches; }
+            NML_CUDA(cudaGetLastError());
+        }
+    } else if (direct_w) {
         b_mn_major = f.k_is_dim0 ? 1 : 0;
     } else {
         size_t bytes = static_cast<size_t>(N) * T * kp * mi.es;
@@ -409,7 +458,24 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
 
     // phases and taps
     int n_taps = 0, n_phases = 0;
-    if (!f.gather) {
+    if (window) {
+        Phase& ph = P.phases[0];
+        ph.ph = ph.pw = 0;
+        ph.hq = f.out_h;
+        ph.wq = f.out_w;
+        ph.tap_begin = 0;
+        for (int kh = 0; kh < f.kh; ++kh) {  // the padding is physical: offsets start at 0
+            Tap& t = P.taps[n_taps++];
+            t.dh = static_cast<short>(kh * f.d_h);
+            t.dw = 0;
+            t.wk = kh * 64;
+        }
+        ph.tap_count = static_cast<short>(n_taps);
+        n_phases = 1;
+        P.a_stride_h = f.s_h;  // rows of the padded image
+        P.a_stride_w = 1;      // the window dimension is already indexed by output column
+        P.out_stride_h = P.out_stride_w = 1;
+    } else if (!f.gather) {
         Phase& ph = P.phases[0];
         ph.ph = ph.pw = 0;
         ph.hq = f.out_h;
@@ -457,7 +523,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     }
     P.n_phases = n_phases;
     // M-tile box from the largest phase grid
-    const int esw = f.gather ? 1 : f.s_w, esh = f.gather ? 1 : f.s_h;
+    const int esw = (f.gather || window) ? 1 : f.s_w, esh = f.gather ? 1 : f.s_h;
     choose_box(7, P.phases[0].wq, P.phases[0].hq, f.batch, esw, esh, &P.wb_log2, &P.hb_log2, &P.nb_log2);
     // Tile width: 256 columns run the tensor pipe best, but when that leaves SMs idle (few row tiles,
     // narrow N) a narrower tile wins.  Cost per column relative to a 256-wide tile, measured on B200:
@@ -502,11 +568,20 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         uint32_t abox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>((1 << P.wb_log2) * esw),
                             static_cast<uint32_t>((1 << P.hb_log2) * esh), static_cast<uint32_t>(1 << P.nb_log2)};
         uint32_t aes[4] = {1, static_cast<uint32_t>(esw), static_cast<uint32_t>(esh), 1};
-        rc = encode_map(&P.tmA[pl], a_planes[pl], mi.es, 4, adims, abox, aes, SWZ_128B);
+        if (window) {
+            // dims: (64 elements = 8 pixels x 8 channels, output column, padded row, image); consecutive
+            // output columns start s_w pixels apart, so the windows overlap
+            uint64_t wd[4] = {64, static_cast<uint64_t>(f.out_w), static_cast<uint64_t>(wimg.hp), static_cast<uint64_t>(f.batch)};
+            uint64_t wstr[3] = {static_cast<uint64_t>(f.s_w) * 16, static_cast<uint64_t>(wimg.wp) * 16,
+                                static_cast<uint64_t>(wimg.hp) * wimg.wp * 16};
+            rc = encode_map(&P.tmA[pl], a_planes[pl], 2, 4, wd, abox, aes, SWZ_128B, wstr);
+        } else {
+            rc = encode_map(&P.tmA[pl], a_planes[pl], mi.es, 4, adims, abox, aes, SWZ_128B);
+        }
         if (rc) return rc;
         uint32_t one[2] = {1, 1};
         if (!b_mn_major) {
-            uint64_t bdims[2] = {static_cast<uint64_t>(direct_w ? K : T * kp), static_cast<uint64_t>(N)};
+            uint64_t bdims[2] = {static_cast<uint64_t>(direct_w ? K : (window ? f.kh * 64 : T * kp)), static_cast<uint64_t>(N)};
             uint32_t bbox[2] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(P.bn)};
             rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 2, bdims, bbox, one, SWZ_128B);
         } else if (N % mi.kb == 0) {
@@ -560,11 +635,23 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
         }
         NML_CUDA(cudaMemsetAsync(g.dw, 0, sizeof(float) * static_cast<size_t>(g.plain_c) * g.patch_c * T, st));
     }
-    const void* pa[2];
+    const void* pa[2] = {nullptr, nullptr};
     const void* pb[2];
     int cpa = 0, cpb = 0;
-    int rc = prepare_activation(g.patch, g.dtype, g.layout, g.batch, g.patch_c, g.patch_h, g.patch_w, mi, ws, st, pa,
+    // Few-channel layer input (RGB stems): patches come as 8-pixel windows of the padded 8-channel image,
+    // one kernel row per tap, (kw, c) packed in the 64 patch columns.
+    const bool window = T > 1 && !g.colsum_of_patch && window_eligible(g.patch_c, g.kw, g.d_w, mi.enc);
+    WindowImage wimg = {nullptr, 0, 0};
+    int rc;
+    if (window) {
+        rc = prepare_window(g.patch, g.dtype, g.layout, g.batch, g.patch_c, g.patch_h, g.patch_w, g.p_h, g.p_w, g.s_w,
+                            g.plain_w, ws, st, &wimg);
+        pa[0] = wimg.ptr;
+        cpa = 8;
+    } else {
+        rc = prepare_activation(g.patch, g.dtype, g.layout, g.batch, g.patch_c, g.patch_h, g.patch_w, mi, ws, st, pa,
                                 &cpa, g.colsum_of_patch ? g.colsum : nullptr);
+    }
     if (rc) return rc;
     rc = prepare_activation(g.plain, g.dtype, g.layout, g.batch, g.plain_c, g.plain_h, g.plain_w, mi, ws, st, pb, &cpb,
                             g.colsum_of_patch ? nullptr : g.colsum);
@@ -581,18 +668,28 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     P.a_mn_major = 1;
     P.b_mn_major = 1;
     P.batch = g.batch;
-    P.c_blocks = ceil_div(g.patch_c, mi.kb);
-    P.groups_total = T * P.c_blocks;
+    P.c_blocks = window ? 1 : ceil_div(g.patch_c, mi.kb);
+    P.groups_total = (window ? g.kh : T) * P.c_blocks;
     P.c_patch = g.patch_c;
     P.c_plain = g.plain_c;
-    P.n_taps = T;
+    P.n_taps = window ? g.kh : T;
+    P.kw_pack = window ? 1 : 0;
+    P.kw_count = g.kw;
     P.n_tiles = ceil_div(g.plain_c, 256);
     P.bn = static_cast<int>(round_up(ceil_div(g.plain_c, P.n_tiles), 64));
     P.c_out = g.plain_c;
     P.out = g.dw;
     P.a_stride_h = g.s_h;
-    P.a_stride_w = g.s_w;
+    P.a_stride_w = window ? 1 : g.s_w;
     P.out_stride_h = P.out_stride_w = 1;
+    if (window) {
+        for (int kh = 0; kh < g.kh; ++kh) {
+            Tap& t = P.taps[kh];
+            t.dh = static_cast<short>(kh * g.d_h);
+            t.dw = 0;
+            t.wk = kh;
+        }
+    } else
     for (int kh = 0; kh < g.kh; ++kh)
         for (int kw = 0; kw < g.kw; ++kw) {
             Tap& t = P.taps[kh * g.kw + kw];
@@ -601,7 +698,7 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
             t.wk = kh * g.kw + kw;
         }
     const int bits = (mi.kb == 64) ? 6 : 5;
-    choose_box(bits, g.plain_w, g.plain_h, g.batch, g.s_w, g.s_h, &P.wb_log2, &P.hb_log2, &P.nb_log2);
+    choose_box(bits, g.plain_w, g.plain_h, g.batch, window ? 1 : g.s_w, g.s_h, &P.wb_log2, &P.hb_log2, &P.nb_log2);
     P.ktiles_w = ceil_div(g.plain_w, 1 << P.wb_log2);
     P.ktiles_h = ceil_div(g.plain_h, 1 << P.hb_log2);
     P.kblocks_total = P.ktiles_w * P.ktiles_h * ceil_div(g.batch, 1 << P.nb_log2);
@@ -644,7 +741,15 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
                             static_cast<uint32_t>((1 << P.hb_log2) * g.s_h), static_cast<uint32_t>(1 << P.nb_log2)};
         uint32_t aes[4] = {1, static_cast<uint32_t>(g.s_w), static_cast<uint32_t>(g.s_h), 1};
         const int G = kTileM / mi.kb;
-        if (cpa % mi.kb == 0 && P.c_blocks % G == 0) {
+        if (window) {
+            uint64_t wd[4] = {64, static_cast<uint64_t>(g.plain_w), static_cast<uint64_t>(wimg.hp), static_cast<uint64_t>(g.batch)};
+            uint64_t wstr[3] = {static_cast<uint64_t>(g.s_w) * 16, static_cast<uint64_t>(wimg.wp) * 16,
+                                static_cast<uint64_t>(wimg.hp) * wimg.wp * 16};
+            uint32_t wbox[4] = {64, static_cast<uint32_t>(1 << P.wb_log2), static_cast<uint32_t>((1 << P.hb_log2) * g.s_h),
+                                static_cast<uint32_t>(1 << P.nb_log2)};
+            uint32_t wes[4] = {1, 1, static_cast<uint32_t>(g.s_h), 1};
+            rc = encode_map(&P.tmA[pl], pa[pl], 2, 4, wd, wbox, wes, mn_swz, wstr);
+        } else if (cpa % mi.kb == 0 && P.c_blocks % G == 0) {
             P.a_grouped = 1;
             uint64_t d5[5] = {static_cast<uint64_t>(mi.kb), adims[1], adims[2], adims[3], static_cast<uint64_t>(cpa / mi.kb)};
             uint64_t s5[4] = {static_cast<uint64_t>(cpa) * mi.es, adims[1] * cpa * mi.es, adims[1] * adims[2] * cpa * mi.es,

@@ -154,6 +154,53 @@ __global__ void __launch_bounds__(256) repack_weight_kernel(const TIn* __restric
     }
 }
 
+// Few-channel activations (C <= 8, e.g. RGB stems): copy into a zero-padded NHWC image with exactly 8
+// fp16 channels per pixel, [N][Hp][Wp][8], the original at offset (pad_h, pad_w).  One thread per
+// padded pixel, one 16-byte store each.  A row of 8 consecutive pixels of this image is one 128-byte
+// K slice holding (kw, c) for 8 taps, which is what the small-channel contraction path reads.
+template <typename TIn>
+__global__ void __launch_bounds__(256) pad_pack_c8_kernel(const TIn* __restrict__ in, int nchw, __half* __restrict__ out,
+                                                          int N, int C, int H, int W, int pad_h, int pad_w, int Hp,
+                                                          int Wp) {
+    const size_t total = static_cast<size_t>(N) * Hp * Wp;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int wp = static_cast<int>(i % Wp);
+        const size_t r = i / Wp;
+        const int hp = static_cast<int>(r % Hp);
+        const int n = static_cast<int>(r / Hp);
+        const int h = hp - pad_h, w = wp - pad_w;
+        __half v[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) v[c] = __float2half_rn(0.f);
+        if (h >= 0 && h < H && w >= 0 && w < W) {
+            for (int c = 0; c < C; ++c) {
+                size_t src = nchw ? ((static_cast<size_t>(n) * C + c) * H + h) * W + w
+                                  : ((static_cast<size_t>(n) * H + h) * W + w) * C + c;
+                v[c] = __float2half_rn(load_as_float(in, src));
+            }
+        }
+        reinterpret_cast<uint4*>(out)[i] = *reinterpret_cast<const uint4*>(v);
+    }
+}
+
+// Weights [C_out][C][KH][KW] -> [C_out][KH][64] with k = kw*8 + c (zero where c >= C or kw >= KW):
+// the K-major operand matching pad_pack_c8's (kw, c) slices.
+template <typename TIn>
+__global__ void __launch_bounds__(256) repack_weight_c8_kernel(const TIn* __restrict__ w, __half* __restrict__ out,
+                                                               int Cout, int C, int KH, int KW) {
+    const int total = Cout * KH * 64;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int k = i & 63;
+        const int kh = (i >> 6) % KH;
+        const int co = (i >> 6) / KH;
+        const int kw = k >> 3, c = k & 7;
+        float v = 0.f;
+        if (c < C && kw < KW) v = load_as_float(w, ((static_cast<size_t>(co) * C + c) * KH + kh) * KW + kw);
+        out[i] = __float2half_rn(v);
+    }
+}
+
 template <typename TIn>
 __global__ void __launch_bounds__(256) to_float_kernel(const TIn* __restrict__ in, float* out, int n) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;

@@ -85,6 +85,8 @@ struct KParams {
     int groups_total;    // taps * c_blocks column groups of kb patch channels
     int split_k, kblocks_total, ktiles_h, ktiles_w;
     int c_patch, c_plain, n_taps;
+    int kw_pack;         // wgrad, few-channel path: patch index j of a tap means (kw = j / 8, c = j % 8)
+    int kw_count;        //   ... with kw_count valid kw per tap row; dW index = ((plain*C + c)*KH + kh)*KW + kw
     int m_fastest;       // wgrad tile order: consecutive CTAs share the plain operand's columns (re-read the smaller tensor)
     // epilogue
     void* out;
@@ -578,10 +580,18 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 int t = gi / P.c_blocks;
                 int cib = gi - t * P.c_blocks;
                 int pc = cib * P.kb + (row % P.kb);
-                row_valid = (gi < P.groups_total) && (pc < P.c_patch);
-                // dW[plain][patch][tap]
-                row_off = static_cast<size_t>(pc) * P.n_taps + t;
-                col_stride = static_cast<size_t>(P.c_patch) * P.n_taps;
+                if (P.kw_pack) {
+                    // few-channel path: tap t is a kernel row kh, patch index pc packs (kw, c)
+                    const int kwi = pc >> 3, c = pc & 7;
+                    row_valid = (gi < P.groups_total) && (c < P.c_patch) && (kwi < P.kw_count);
+                    row_off = (static_cast<size_t>(c) * P.n_taps + t) * P.kw_count + kwi;
+                    col_stride = static_cast<size_t>(P.c_patch) * P.n_taps * P.kw_count;
+                } else {
+                    row_valid = (gi < P.groups_total) && (pc < P.c_patch);
+                    // dW[plain][patch][tap]
+                    row_off = static_cast<size_t>(pc) * P.n_taps + t;
+                    col_stride = static_cast<size_t>(P.c_patch) * P.n_taps;
+                }
             }
             // Row-major epilogue: this lane's bias slice for the first 128-byte piece is fetched before
             // the wait, and each later slice one piece ahead, so the load latency never shows.
