@@ -139,12 +139,15 @@ static Profiler g_prof;
 typedef void (*UmmaKernel)(const KParams);
 static UmmaKernel kernel_for(const KParams& P) {
     if (P.mode == MODE_WGRAD) return umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false>;
+    if (P.out_mode == OUT_NHWC_TMA)
+        return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true> : umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false>;
     if (P.out_mode == OUT_NHWC)
         return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC, true> : umma_conv_kernel<MODE_FPROP, OUT_NHWC, false>;
     return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NCHW, true> : umma_conv_kernel<MODE_FPROP, OUT_NCHW, false>;
 }
 static int raise_smem_limit() {
-    UmmaKernel all[5] = {umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false>, umma_conv_kernel<MODE_FPROP, OUT_NHWC, true>,
+    UmmaKernel all[7] = {umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true>, umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false>,
+                         umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false>, umma_conv_kernel<MODE_FPROP, OUT_NHWC, true>,
                          umma_conv_kernel<MODE_FPROP, OUT_NHWC, false>, umma_conv_kernel<MODE_FPROP, OUT_NCHW, true>,
                          umma_conv_kernel<MODE_FPROP, OUT_NCHW, false>};
     for (UmmaKernel k : all)
@@ -310,10 +313,16 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
     // take two slices per stage (8 MMAs per round trip); 256-wide tiles already fill 512 clocks.
     P.ka = std::max(1, std::min(2, tune_env("NML_TUNE_KA", P.bn >= 192 ? 1 : 2)));
     const int stage_bytes = P.ka * (kStageABytes + P.bn * 128);
-    int stages = std::min(8, (232448 - 1024 - 256 - kStagingBytes) / stage_bytes);
+    // Shared memory: the operand ring, then the epilogue's staging buffers (two per warp if that does not
+    // cost a ring stage, else one), the per-warp bias tiles, and the barriers.
+    const int fixed = 1024 + 256 + kBiasTileBytes;
+    int stages2 = (232448 - fixed - 4 * 2 * kStagingBufBytes) / stage_bytes;
+    int stages1 = (232448 - fixed - 4 * 1 * kStagingBufBytes) / stage_bytes;
+    P.stg_bufs = (stages2 >= std::min(stages1, 8)) ? 2 : 1;
+    int stages = std::min(8, P.stg_bufs == 2 ? stages2 : stages1);
     stages = std::max(2, std::min(stages, tune_env("NML_TUNE_STAGES", 8)));
     P.stages = stages;
-    size_t smem = static_cast<size_t>(stages) * stage_bytes + kStagingBytes + 1024 + 256;
+    size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * P.stg_bufs * kStagingBufBytes + fixed;
     smem = std::max<size_t>(smem, 120 * 1024);  // one CTA per SM: each allocates its own TMEM
     P.err = ds->err;
 #ifdef NML_TRACE
@@ -599,6 +608,23 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
             rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 2, bdims, bbox, one, SWZ_128B);
         }
         if (rc) return rc;
+    }
+    // Row-major output through TMA stores when the geometry allows: the box is the 32 consecutive tile
+    // rows one epilogue warp owns (a sub-box of the tile's pixel box), 128 bytes of columns wide.
+    if (P.out_mode == OUT_NHWC && tune_env("NML_TUNE_TMASTORE", 1)) {
+        const int esz = P.out_f16 ? 2 : 4;
+        const int cpi = 128 / esz;
+        if (P.bn % cpi == 0 && (static_cast<size_t>(N) * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(f.out) & 15) == 0) {
+            const int wbx = 1 << P.wb_log2, hbx = 1 << P.hb_log2;
+            const int bw = std::min(wbx, 32), bh = std::min(hbx, 32 / bw), bnn = 32 / (bw * bh);
+            uint64_t cd[4] = {static_cast<uint64_t>(N), static_cast<uint64_t>(f.out_w), static_cast<uint64_t>(f.out_h),
+                              static_cast<uint64_t>(f.batch)};
+            uint32_t cb[4] = {static_cast<uint32_t>(cpi), static_cast<uint32_t>(bw * P.out_stride_w),
+                              static_cast<uint32_t>(bh * P.out_stride_h), static_cast<uint32_t>(bnn)};
+            uint32_t ce[4] = {1, static_cast<uint32_t>(P.out_stride_w), static_cast<uint32_t>(P.out_stride_h), 1};
+            if (cb[1] <= 256 && cb[2] <= 256 && encode_map(&P.tmC, f.out, esz, 4, cd, cb, ce, SWZ_128B) == NML_OK)
+                P.out_mode = OUT_NHWC_TMA;
+        }
     }
     return launch_kernel(P, ds, st);
 }

@@ -27,7 +27,7 @@
 namespace nml {
 
 enum { MODE_FPROP = 0, MODE_WGRAD = 1 };
-enum { OUT_NHWC = 0, OUT_NCHW = 1 };
+enum { OUT_NHWC = 0, OUT_NCHW = 1, OUT_NHWC_TMA = 2 };  // _TMA: row-major output written by TMA stores
 enum { KIND_F16 = 0, KIND_TF32 = 2 };
 
 // Error codes written to the status word by a kernel that gave up on a wait.
@@ -44,7 +44,8 @@ constexpr int kMaxTaps = 128;
 constexpr int kTileM = 128;
 constexpr int kStageABytes = kTileM * 128;
 constexpr int kThreads = 224;  // warp 0: A loads, warp 1: MMA issue, warps 2-5: epilogue, warp 6: B loads
-constexpr int kStagingBytes = 4 * 4096;  // per epilogue warp: 32 rows x 128 bytes of output
+constexpr int kStagingBufBytes = 4096;         // one staging buffer: 32 rows x 128 bytes of output
+constexpr int kBiasTileBytes = 4 * 256 * 4;   // per epilogue warp: the current tile's bias values
 
 struct Tap {
     short dh, dw;  // offset of this tap's box from the tile origin, in input pixels
@@ -63,10 +64,12 @@ struct KParams {
     CUtensorMap tmA[2];  // fprop: activation (plane 0 = value or tf32 "hi", plane 1 = tf32 "lo")
                          // wgrad: the tensor patches are cut from
     CUtensorMap tmB[2];  // fprop: weights; wgrad: the plainly indexed tensor
+    CUtensorMap tmC;     // OUT_NHWC_TMA: the output, box = the 32 rows x 128 bytes one epilogue warp owns
     int mode, out_mode;
     int num_tiles, n_tiles;
     int bn;              // UMMA N of one tile
     int stages;
+    int stg_bufs;        // staging buffers per epilogue warp (4 KB each): 2 when shared memory allows, else 1
     int ka;              // K atoms (128-byte-wide operand slices) per stage; narrow tiles take 2 to amortise the
                          // per-stage barrier round trip over 8 MMAs
     int a_mn_major, b_mn_major;
@@ -213,7 +216,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
     const int stage_bytes = P.ka * (kStageABytes + stage_b_bytes);  // [A atoms][B atoms]
     const int b_off = P.ka * kStageABytes;                        // first B atom within a stage
     uint8_t* staging = smem + P.stages * stage_bytes;  // 4 epilogue warps x 4 KB
-    uint8_t* ctrl = staging + kStagingBytes;
+    const int staging_bytes = 4 * P.stg_bufs * kStagingBufBytes;
+    float* bias_tile = reinterpret_cast<float*>(staging + staging_bytes);
+    uint8_t* ctrl = staging + staging_bytes + kBiasTileBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);          // [stages]
     uint64_t* empty_bar = full_bar + 8;                               // [stages]
     uint64_t* tfull_bar = empty_bar + 8;                              // [2]
@@ -538,6 +543,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
         const int row = quarter * 32 + lane;
         bool ok = true;
         int titer = 0;
+        uint32_t store_seq = 0;  // TMA-store pieces issued by this warp so far (selects the staging buffer)
         for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x, ++titer) {
             const int buf = titer & 1;
             const uint32_t tpar = (titer >> 1) & 1;
@@ -563,7 +569,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 int ow = ph.pw + P.out_stride_w * iw;
                 int oh = ph.ph + P.out_stride_h * ih;
                 k_iters = ph.tap_count;
-                if (kOutMode == OUT_NHWC) {
+                if (kOutMode != OUT_NCHW) {
                     row_off = ((static_cast<size_t>(n) * P.out_h + oh) * P.out_w + ow) * P.ld_out;
                     col_stride = 1;
                 } else {
@@ -593,6 +599,14 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     col_stride = static_cast<size_t>(P.c_patch) * P.n_taps;
                 }
             }
+            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC_TMA && P.bias != nullptr) {
+                // this tile's bias values, one copy per warp (no cross-warp barrier to get stuck on)
+                float* btw = bias_tile + (warp - 2) * 256;
+                const int cb0 = ntile * P.bn;
+                __syncwarp();
+                for (int j = lane; j < P.bn; j += 32) btw[j] = (cb0 + j < P.c_out) ? __ldg(P.bias + cb0 + j) : 0.f;
+                __syncwarp();
+            }
             // Row-major epilogue: this lane's bias slice for the first 128-byte piece is fetched before
             // the wait, and each later slice one piece ahead, so the load latency never shows.
             float4 nb0 = make_float4(0.f, 0.f, 0.f, 0.f), nb1 = nb0;
@@ -618,6 +632,102 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             if (threadIdx.x == 64) NML_STAMP(titer, 3);
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * P.bn;
             const int col_base = ntile * P.bn;
+            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC_TMA) {
+                // Row-major output through TMA: each warp converts 128-byte row pieces of its 32 rows into a
+                // swizzled 4 KB buffer and one lane hands the buffer to a TMA store, whose box is exactly
+                // those 32 rows; rows and columns outside the tensor are clipped by the hardware.  Two
+                // buffers alternate, so packing the next piece overlaps the store of the previous one.
+                constexpr int cpi = kOutF16 ? 64 : 32;
+                const uint32_t stg0 = smem_u32(staging) + (warp - 2) * P.stg_bufs * kStagingBufBytes;
+                const float* bt = bias_tile + (warp - 2) * 256;
+                const bool has_bias = (P.bias != nullptr);
+                // store coordinates of this warp's first row
+                int sw, sh, sn;
+                {
+                    int p = 0;
+                    while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
+                    const Phase& ph = P.phases[p];
+                    int local = tile - ph.tile_begin;
+                    int m = local / P.n_tiles;
+                    int tw = m % ph.tiles_w;
+                    int th = (m / ph.tiles_w) % ph.tiles_h;
+                    int tn = m / (ph.tiles_w * ph.tiles_h);
+                    const int row0 = quarter * 32;
+                    sw = ph.pw + P.out_stride_w * ((tw << P.wb_log2) + (row0 & (wb - 1)));
+                    sh = ph.ph + P.out_stride_h * ((th << P.hb_log2) + ((row0 >> P.wb_log2) & (hb - 1)));
+                    sn = (tn << P.nb_log2) + (row0 >> (P.wb_log2 + P.hb_log2));
+                }
+                uint32_t r0[32], r1[32];
+                const bool live = (k_iters > 0);
+                if (!live) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
+                }
+                if (live && col_base < P.c_out) {
+                    tmem_ld_32x32(t_row, r0);
+                    if (cpi == 64) tmem_ld_32x32(t_row + 32, r1);
+                    tmem_ld_wait();
+                }
+                for (int c0 = 0; c0 < P.bn; c0 += cpi) {
+                    const int cg = col_base + c0;
+                    if (cg >= P.c_out) break;  // uniform across the warp
+                    const int cn = c0 + cpi;
+                    const bool more = live && cn < P.bn && col_base + cn < P.c_out;
+                    const uint32_t buf_addr = stg0 + ((P.stg_bufs == 2) ? (store_seq & 1) * kStagingBufBytes : 0);
+                    // the store that last read this buffer must be done reading it
+                    if (lane == 0) {
+                        if (P.stg_bufs == 2) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int qq = 0; qq < 8; ++qq) {
+                        uint4 pk;
+                        if (kOutF16) {
+                            const uint32_t* src = (qq < 4) ? &r0[8 * qq] : &r1[8 * (qq - 4)];
+                            float v[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(src[j]);
+                            if (has_bias) {
+                                const float4 ba = *reinterpret_cast<const float4*>(bt + c0 + 8 * qq);
+                                const float4 bb = *reinterpret_cast<const float4*>(bt + c0 + 8 * qq + 4);
+                                v[0] += ba.x; v[1] += ba.y; v[2] += ba.z; v[3] += ba.w;
+                                v[4] += bb.x; v[5] += bb.y; v[6] += bb.z; v[7] += bb.w;
+                            }
+                            pk.x = pack_half2(v[0], v[1]);
+                            pk.y = pack_half2(v[2], v[3]);
+                            pk.z = pack_half2(v[4], v[5]);
+                            pk.w = pack_half2(v[6], v[7]);
+                        } else {
+                            float v[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) v[j] = __uint_as_float(r0[4 * qq + j]);
+                            if (has_bias) {
+                                const float4 ba = *reinterpret_cast<const float4*>(bt + c0 + 4 * qq);
+                                v[0] += ba.x; v[1] += ba.y; v[2] += ba.z; v[3] += ba.w;
+                            }
+                            if (P.round_f16) {
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) v[j] = round_through_f16(v[j]);
+                            }
+                            pk.x = __float_as_uint(v[0]); pk.y = __float_as_uint(v[1]);
+                            pk.z = __float_as_uint(v[2]); pk.w = __float_as_uint(v[3]);
+                        }
+                        st_shared_v4(buf_addr + lane * 128 + ((qq ^ (lane & 7)) << 4), pk);
+                    }
+                    if (more) {  // registers are free again: start the next TMEM load now
+                        tmem_ld_32x32(t_row + cn, r0);
+                        if (cpi == 64) tmem_ld_32x32(t_row + cn + 32, r1);
+                    }
+                    fence_proxy_async();  // make the generic-proxy writes visible to the TMA engine
+                    __syncwarp();
+                    if (lane == 0) {
+                        tma_store_4d(&P.tmC, buf_addr, cg, sw, sh, sn);
+                        bulk_commit_group();
+                    }
+                    ++store_seq;
+                    if (more) tmem_ld_wait();
+                }
+            } else
             if (kMode == MODE_FPROP && kOutMode == OUT_NHWC) {
                 // Row-major output.  Each 128-byte piece of a row (64 fp16 / 32 fp32 columns) goes
                 // through a swizzled shared-memory tile so that a warp store writes four full
@@ -626,7 +736,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 // added on the way out, where each lane owns the same 16 bytes of every row.
                 const int cpi = kOutF16 ? 64 : 32;
                 const int esz = kOutF16 ? 2 : 4;
-                const uint32_t stg = smem_u32(staging) + (warp - 2) * 4096;
+                const uint32_t stg = smem_u32(staging) + (warp - 2) * P.stg_bufs * kStagingBufBytes;
                 const bool has_bias = (P.bias != nullptr);
                 const bool aligned = ((static_cast<size_t>(P.ld_out) * esz) & 15) == 0 &&
                                      (reinterpret_cast<uintptr_t>(P.out) & 15) == 0 &&
@@ -788,6 +898,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             if (threadIdx.x == 64) NML_STAMP(titer, 4);
             if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[buf]));
         }
+        if (kOutMode == OUT_NHWC_TMA && lane == 0) bulk_wait_group<0>();  // stores must land before the CTA ends
     }
 
     // ------------------------------------------------------------ teardown --
