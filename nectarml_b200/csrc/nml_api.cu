@@ -135,21 +135,30 @@ struct Profiler {
 };
 static Profiler g_prof;
 
-// The five instances of the contraction kernel, and the one that serves a given launch.
+// The instances of the contraction kernel, and the one that serves a given launch.
 typedef void (*UmmaKernel)(const KParams);
 static UmmaKernel kernel_for(const KParams& P) {
-    if (P.mode == MODE_WGRAD) return umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false>;
+    if (P.mode == MODE_WGRAD) return umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, false>;
+    if (P.pair) {
+        if (P.out_mode == OUT_NHWC_TMA)
+            return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true, true>
+                             : umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false, true>;
+        return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NCHW, true, true> : umma_conv_kernel<MODE_FPROP, OUT_NCHW, false, true>;
+    }
     if (P.out_mode == OUT_NHWC_TMA)
-        return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true> : umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false>;
+        return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true, false>
+                         : umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false, false>;
     if (P.out_mode == OUT_NHWC)
-        return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC, true> : umma_conv_kernel<MODE_FPROP, OUT_NHWC, false>;
-    return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NCHW, true> : umma_conv_kernel<MODE_FPROP, OUT_NCHW, false>;
+        return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC, true, false> : umma_conv_kernel<MODE_FPROP, OUT_NHWC, false, false>;
+    return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NCHW, true, false> : umma_conv_kernel<MODE_FPROP, OUT_NCHW, false, false>;
 }
 static int raise_smem_limit() {
-    UmmaKernel all[7] = {umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true>, umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false>,
-                         umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false>, umma_conv_kernel<MODE_FPROP, OUT_NHWC, true>,
-                         umma_conv_kernel<MODE_FPROP, OUT_NHWC, false>, umma_conv_kernel<MODE_FPROP, OUT_NCHW, true>,
-                         umma_conv_kernel<MODE_FPROP, OUT_NCHW, false>};
+    UmmaKernel all[11] = {umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, false>,
+                          umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true, false>, umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false, false>,
+                          umma_conv_kernel<MODE_FPROP, OUT_NHWC, true, false>, umma_conv_kernel<MODE_FPROP, OUT_NHWC, false, false>,
+                          umma_conv_kernel<MODE_FPROP, OUT_NCHW, true, false>, umma_conv_kernel<MODE_FPROP, OUT_NCHW, false, false>,
+                          umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true, true>, umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false, true>,
+                          umma_conv_kernel<MODE_FPROP, OUT_NCHW, true, true>, umma_conv_kernel<MODE_FPROP, OUT_NCHW, false, true>};
     for (UmmaKernel k : all)
         NML_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     return NML_OK;
@@ -311,8 +320,8 @@ extern "C" void nml_trace_set(long long* p) { g_trace_buf = p; }
 static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
     // Narrow tiles finish a 64-deep K slice in well under the barrier round trip of a stage, so they
     // take two slices per stage (8 MMAs per round trip); 256-wide tiles already fill 512 clocks.
-    P.ka = std::max(1, std::min(2, tune_env("NML_TUNE_KA", P.bn >= 192 ? 1 : 2)));
-    const int stage_bytes = P.ka * (kStageABytes + P.bn * 128);
+    P.ka = P.pair ? 1 : std::max(1, std::min(2, tune_env("NML_TUNE_KA", P.bn >= 192 ? 1 : 2)));
+    const int stage_bytes = P.ka * (kStageABytes + (P.pair ? P.bn / 2 : P.bn) * 128);
     // Shared memory: the operand ring, then the epilogue's staging buffers (two per warp if that does not
     // cost a ring stage, else one), the per-warp bias tiles, and the barriers.
     const int fixed = 1024 + 256 + kBiasTileBytes;
@@ -330,11 +339,28 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
     P.dbg_skip = tune_env("NML_DBG_SKIP", 0);
     P.dbg_alt = tune_env("NML_DBG_ALT", 0);
 #endif
-    int grid = std::min(P.num_tiles, ds->sms);
+    int grid = P.pair ? 2 * std::min(P.num_tiles, ds->sms / 2) : std::min(P.num_tiles, ds->sms);
     if (grid <= 0) return NML_OK;
     const bool rec = g_prof.on && g_prof.n < g_prof.cap;
     if (rec) NML_CUDA(cudaEventRecord(g_prof.start[g_prof.n], st));
-    kernel_for(P)<<<grid, kThreads, smem, st>>>(P);
+    if (P.pair) {
+        cudaLaunchConfig_t cfg;
+        memset(&cfg, 0, sizeof(cfg));
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        NML_CUDA(cudaLaunchKernelEx(&cfg, kernel_for(P), P));
+    } else {
+        kernel_for(P)<<<grid, kThreads, smem, st>>>(P);
+    }
     NML_CUDA(cudaGetLastError());
     if (rec) NML_CUDA(cudaEventRecord(g_prof.stop[g_prof.n++], st));
     ++g_launches;
@@ -560,13 +586,35 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
             }
         }
     }
+    // Row-major output through TMA stores when the geometry allows: the box is the 32 consecutive tile
+    // rows one epilogue warp owns (a sub-box of the tile's pixel box), 128 bytes of columns wide.
+    if (P.out_mode == OUT_NHWC && tune_env("NML_TUNE_TMASTORE", 1)) {
+        const int esz = P.out_f16 ? 2 : 4;
+        const int cpi = 128 / esz;
+        if (P.bn % cpi == 0 && (static_cast<size_t>(N) * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(f.out) & 15) == 0) {
+            const int wbx = 1 << P.wb_log2, hbx = 1 << P.hb_log2;
+            const int bw = std::min(wbx, 32), bh = std::min(hbx, 32 / bw), bnn = 32 / (bw * bh);
+            uint64_t cd[4] = {static_cast<uint64_t>(N), static_cast<uint64_t>(f.out_w), static_cast<uint64_t>(f.out_h),
+                              static_cast<uint64_t>(f.batch)};
+            uint32_t cb[4] = {static_cast<uint32_t>(cpi), static_cast<uint32_t>(bw * P.out_stride_w),
+                              static_cast<uint32_t>(bh * P.out_stride_h), static_cast<uint32_t>(bnn)};
+            uint32_t ce[4] = {1, static_cast<uint32_t>(P.out_stride_w), static_cast<uint32_t>(P.out_stride_h), 1};
+            if (cb[1] <= 256 && cb[2] <= 256 && encode_map(&P.tmC, f.out, esz, 4, cd, cb, ce, SWZ_128B) == NML_OK)
+                P.out_mode = OUT_NHWC_TMA;
+        }
+    }
+    // Pairs of CTAs (cta_group::2) for 256-wide tiles of problems large enough to fill the pairs: a
+    // tile id then names two consecutive row tiles of one phase.
+    P.pair = (tune_env("NML_TUNE_PAIR", 1) && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) &&
+              (P.out_mode == OUT_NHWC_TMA || P.out_mode == OUT_NCHW) && ds->sms >= 2) ? 1 : 0;
     int tiles = 0;
     for (int p = 0; p < n_phases; ++p) {
         Phase& ph = P.phases[p];
         ph.tiles_w = ceil_div(ph.wq, 1 << P.wb_log2);
         ph.tiles_h = ceil_div(ph.hq, 1 << P.hb_log2);
         ph.tile_begin = tiles;
-        tiles += ph.tiles_w * ph.tiles_h * ceil_div(f.batch, 1 << P.nb_log2) * P.n_tiles;
+        int m_tiles = ph.tiles_w * ph.tiles_h * ceil_div(f.batch, 1 << P.nb_log2);
+        tiles += (P.pair ? ceil_div(m_tiles, 2) : m_tiles) * P.n_tiles;
     }
     P.num_tiles = tiles;
 
@@ -591,7 +639,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         uint32_t one[2] = {1, 1};
         if (!b_mn_major) {
             uint64_t bdims[2] = {static_cast<uint64_t>(direct_w ? K : (window ? f.kh * 64 : T * kp)), static_cast<uint64_t>(N)};
-            uint32_t bbox[2] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(P.bn)};
+            uint32_t bbox[2] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(P.pair ? P.bn / 2 : P.bn)};
             rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 2, bdims, bbox, one, SWZ_128B);
         } else if (N % mi.kb == 0) {
             // one box per stage: the outermost dimension walks the 128-byte column groups
@@ -599,7 +647,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
             uint64_t bdims[3] = {static_cast<uint64_t>(mi.kb), static_cast<uint64_t>(K), static_cast<uint64_t>(N / mi.kb)};
             uint64_t bstr[2] = {static_cast<uint64_t>(N) * mi.es, static_cast<uint64_t>(mi.kb) * mi.es};
             uint32_t bbox[3] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>(mi.kb),
-                                static_cast<uint32_t>(P.bn / mi.kb)};
+                                static_cast<uint32_t>((P.pair ? P.bn / 2 : P.bn) / mi.kb)};
             uint32_t one3[3] = {1, 1, 1};
             rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 3, bdims, bbox, one3, SWZ_128B, bstr);
         } else {
@@ -608,23 +656,6 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
             rc = encode_map(&P.tmB[pl], w_planes[pl], mi.es, 2, bdims, bbox, one, SWZ_128B);
         }
         if (rc) return rc;
-    }
-    // Row-major output through TMA stores when the geometry allows: the box is the 32 consecutive tile
-    // rows one epilogue warp owns (a sub-box of the tile's pixel box), 128 bytes of columns wide.
-    if (P.out_mode == OUT_NHWC && tune_env("NML_TUNE_TMASTORE", 1)) {
-        const int esz = P.out_f16 ? 2 : 4;
-        const int cpi = 128 / esz;
-        if (P.bn % cpi == 0 && (static_cast<size_t>(N) * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(f.out) & 15) == 0) {
-            const int wbx = 1 << P.wb_log2, hbx = 1 << P.hb_log2;
-            const int bw = std::min(wbx, 32), bh = std::min(hbx, 32 / bw), bnn = 32 / (bw * bh);
-            uint64_t cd[4] = {static_cast<uint64_t>(N), static_cast<uint64_t>(f.out_w), static_cast<uint64_t>(f.out_h),
-                              static_cast<uint64_t>(f.batch)};
-            uint32_t cb[4] = {static_cast<uint32_t>(cpi), static_cast<uint32_t>(bw * P.out_stride_w),
-                              static_cast<uint32_t>(bh * P.out_stride_h), static_cast<uint32_t>(bnn)};
-            uint32_t ce[4] = {1, static_cast<uint32_t>(P.out_stride_w), static_cast<uint32_t>(P.out_stride_h), 1};
-            if (cb[1] <= 256 && cb[2] <= 256 && encode_map(&P.tmC, f.out, esz, 4, cd, cb, ce, SWZ_128B) == NML_OK)
-                P.out_mode = OUT_NHWC_TMA;
-        }
     }
     return launch_kernel(P, ds, st);
 }

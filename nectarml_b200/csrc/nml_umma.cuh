@@ -69,6 +69,7 @@ struct KParams {
     int num_tiles, n_tiles;
     int bn;              // UMMA N of one tile
     int stages;
+    int pair;            // 1: launched as clusters of two CTAs sharing 256x256 tiles (cta_group::2)
     int stg_bufs;        // staging buffers per epilogue warp (4 KB each): 2 when shared memory allows, else 1
     int ka;              // K atoms (128-byte-wide operand slices) per stage; narrow tiles take 2 to amortise the
                          // per-stage barrier round trip over 8 MMAs
@@ -206,13 +207,20 @@ __device__ __noinline__ void store_row_chunk(const KParams& P, const float (&v)[
 // Specialised on the tile walk, the output layout and the output type so that each instance's hot
 // loops stay small: the epilogue warps run alone on their schedulers and stall on instruction fetch
 // when the straight-line code of every variant is laid out in one kernel.
-template <int kMode, int kOutMode, bool kOutF16>
+// kPair: two CTAs of a cluster compute one 256-row x 256-column tile with cta_group::2 MMAs issued by
+// the rank-0 CTA; each CTA loads its own 128 rows of A and its own 128-column half of B (no multicast),
+// which halves the B traffic and the MMA issue cost per SM and leaves room for 6 stages.
+template <int kMode, int kOutMode, bool kOutF16, bool kPair>
 __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_constant__ KParams P) {
     extern __shared__ uint8_t smem_raw[];
     // stages need 1024-byte alignment for the 128-byte swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                                ~static_cast<uintptr_t>(1023));
-    const int stage_b_bytes = P.bn * 128;                        // one atom of B
+    const uint32_t cta_rank = kPair ? cluster_ctarank() : 0u;
+    const bool leader = (cta_rank == 0);
+    const int tile_first = kPair ? (blockIdx.x >> 1) : blockIdx.x;
+    const int tile_step = kPair ? (gridDim.x >> 1) : gridDim.x;
+    const int stage_b_bytes = (kPair ? P.bn / 2 : P.bn) * 128;   // one atom of B (a pair member holds half the columns)
     const int stage_bytes = P.ka * (kStageABytes + stage_b_bytes);  // [A atoms][B atoms]
     const int b_off = P.ka * kStageABytes;                        // first B atom within a stage
     uint8_t* staging = smem + P.stages * stage_bytes;  // 4 epilogue warps x 4 KB
@@ -238,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&tfull_bar[b]), 1);
-            mbar_init(smem_u32(&tempty_bar[b]), 4);
+            mbar_init(smem_u32(&tempty_bar[b]), kPair ? 8 : 4);  // the leader also hears the partner's epilogue warps
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -250,11 +258,17 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
         }
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), tmem_cols);
-        tmem_relinquish();
+        if (kPair) {
+            tmem_alloc_pair(smem_u32(tmem_slot), tmem_cols);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(smem_u32(tmem_slot), tmem_cols);
+            tmem_relinquish();
+        }
     }
     tc_fence_before();
     __syncthreads();
+    if (kPair) cluster_sync_all();  // the partner's barriers must be initialised before anything arrives on them
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
@@ -271,7 +285,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             int issued = 0;
             const uint32_t a_bytes = kStageABytes;
             const uint32_t tx_bytes = do_a ? a_bytes : stage_b_bytes;  // this producer's share of one atom
-            for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x) {
+            for (int tile = tile_first; ok && tile < P.num_tiles; tile += tile_step) {
                 if (kMode == MODE_FPROP) {
                     int p = 0;
                     while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
@@ -279,6 +293,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     int local = tile - ph.tile_begin;
                     int ntile = local % P.n_tiles;
                     int m = local / P.n_tiles;
+                    if (kPair) m = 2 * m + static_cast<int>(cta_rank);  // the pair's two row tiles
                     int tw = m % ph.tiles_w;
                     int th = (m / ph.tiles_w) % ph.tiles_h;
                     int tn = m / (ph.tiles_w * ph.tiles_h);
@@ -298,7 +313,9 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         // accumulation costs them nothing
                         const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
                         const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
+                        // in a pair every load signals the LEADER's barrier, which expects both members' bytes
                         uint32_t fb = smem_u32(&full_bar[stage]);
+                        if (kPair) fb = map_to_cta(fb, 0);
                         if (slot == 0) {
                             if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err,
                                            ERR_WAIT_EMPTY)) {
@@ -306,12 +323,21 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                                 break;
                             }
                             n_in_stage = min(P.ka, k_iters - it);
-                            mbar_arrive_expect_tx(fb, n_in_stage * tx_bytes);
+                            if (!kPair) mbar_arrive_expect_tx(fb, n_in_stage * tx_bytes);
+                            else if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * n_in_stage * tx_bytes);
                         }
                         uint32_t sa = smem_u32(smem + stage * stage_bytes) + slot * kStageABytes;
                         uint32_t sb = smem_u32(smem + stage * stage_bytes) + b_off + slot * stage_b_bytes;
+                        if (kPair) {
+                            const int ncol = ntile * P.bn + static_cast<int>(cta_rank) * (P.bn / 2);  // this member's half of B
+                            if (do_a) tma_load_4d_pair(sa, ta, fb, cb * P.kb, w0 + tap.dw, h0 + tap.dh, n0);
+                            if (do_b) {
+                                if (!P.b_mn_major) tma_load_2d_pair(sb, tb, fb, tap.wk + cb * P.kb, ncol);
+                                else tma_load_3d_pair(sb, tb, fb, 0, tap.wk + cb * P.kb, ncol / P.kb);
+                            }
+                        } else
                         if (do_a) tma_load_4d(sa, ta, fb, cb * P.kb, w0 + tap.dw, h0 + tap.dh, n0);
-                        if (!do_b) {
+                        if (kPair || !do_b) {
                         } else if (!P.b_mn_major) {
                             tma_load_2d(sb, tb, fb, tap.wk + cb * P.kb, ntile * P.bn);
                         } else if (P.b_grouped) {
@@ -444,7 +470,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
         // lane observes the barriers itself); one elected lane issues the MMAs and their commits.  The loop
         // body is kept minimal: one MMA must be issued every 128 clocks to keep the tensor pipe
         // busy, and everything here is on that single thread's critical path.
-        const uint32_t idesc = make_instr_desc(P.kind, P.a_mn_major, P.b_mn_major, kTileM, P.bn);
+        const uint32_t idesc = make_instr_desc(P.kind, P.a_mn_major, P.b_mn_major, kPair ? 2 * kTileM : kTileM, P.bn);
         const uint32_t lbo_a = P.a_mn_major ? box_bytes : 16;
         const uint32_t lbo_b = P.b_mn_major ? box_bytes : 16;
         const int umma_k = (P.kind == KIND_F16) ? 16 : 8;
@@ -464,7 +490,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
         uint32_t parity = 0;
         bool ok = true;
         int titer = 0;
-        for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x, ++titer) {
+        for (int tile = tile_first; ok && (!kPair || leader) && tile < P.num_tiles; tile += tile_step, ++titer) {
             int k_iters;
             if (kMode == MODE_FPROP) {
                 int p = 0;
@@ -504,7 +530,19 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     uint64_t bdesc = bdesc0 + static_cast<uint64_t>(stage * stage_step);
                     uint32_t first = acc;
                     for (int a = 0; a < n_atoms; ++a) {
-                        if (f16) {
+                        if (kPair) {
+                            if (f16) {
+                                umma_f16_pair(d_tmem, adesc, bdesc, idesc, first);
+                                umma_f16_pair(d_tmem, adesc + adv_a, bdesc + adv_b, idesc, 1u);
+                                umma_f16_pair(d_tmem, adesc + 2 * adv_a, bdesc + 2 * adv_b, idesc, 1u);
+                                umma_f16_pair(d_tmem, adesc + 3 * adv_a, bdesc + 3 * adv_b, idesc, 1u);
+                            } else {
+                                umma_tf32_pair(d_tmem, adesc, bdesc, idesc, first);
+                                umma_tf32_pair(d_tmem, adesc + adv_a, bdesc + adv_b, idesc, 1u);
+                                umma_tf32_pair(d_tmem, adesc + 2 * adv_a, bdesc + 2 * adv_b, idesc, 1u);
+                                umma_tf32_pair(d_tmem, adesc + 3 * adv_a, bdesc + 3 * adv_b, idesc, 1u);
+                            }
+                        } else if (f16) {
                             umma_f16(d_tmem, adesc, bdesc, idesc, first);
                             umma_f16(d_tmem, adesc + adv_a, bdesc + adv_b, idesc, 1u);
                             umma_f16(d_tmem, adesc + 2 * adv_a, bdesc + 2 * adv_b, idesc, 1u);
@@ -519,7 +557,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         adesc += a_atom_step;
                         bdesc += b_atom_step;
                     }
-                    umma_commit(smem_u32(&empty_bar[stage]));
+                    if (kPair) umma_commit_pair(smem_u32(&empty_bar[stage]));  // frees the stage in both CTAs
+                    else umma_commit(smem_u32(&empty_bar[stage]));
                 }
                 acc = 1u;
                 if (++stage == P.stages) {
@@ -530,7 +569,14 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             if (!ok) break;
             if (elect_one()) {
                 NML_STAMP(titer, 2);
-                if (k_iters > 0)
+                if (kPair) {
+                    if (k_iters > 0) {
+                        umma_commit_pair(smem_u32(&tfull_bar[buf]));
+                    } else {
+                        mbar_arrive(smem_u32(&tfull_bar[buf]));
+                        mbar_arrive_cluster(map_to_cta(smem_u32(&tfull_bar[buf]), 1));
+                    }
+                } else if (k_iters > 0)
                     umma_commit(smem_u32(&tfull_bar[buf]));
                 else
                     mbar_arrive(smem_u32(&tfull_bar[buf]));
@@ -544,7 +590,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
         bool ok = true;
         int titer = 0;
         uint32_t store_seq = 0;  // TMA-store pieces issued by this warp so far (selects the staging buffer)
-        for (int tile = blockIdx.x; ok && tile < P.num_tiles; tile += gridDim.x, ++titer) {
+        for (int tile = tile_first; ok && tile < P.num_tiles; tile += tile_step, ++titer) {
             const int buf = titer & 1;
             const uint32_t tpar = (titer >> 1) & 1;
             // tile decode
@@ -559,6 +605,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 int local = tile - ph.tile_begin;
                 ntile = local % P.n_tiles;
                 int m = local / P.n_tiles;
+                    if (kPair) m = 2 * m + static_cast<int>(cta_rank);  // the pair's two row tiles
                 int tw = m % ph.tiles_w;
                 int th = (m / ph.tiles_w) % ph.tiles_h;
                 int tn = m / (ph.tiles_w * ph.tiles_h);
@@ -649,6 +696,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     const Phase& ph = P.phases[p];
                     int local = tile - ph.tile_begin;
                     int m = local / P.n_tiles;
+                    if (kPair) m = 2 * m + static_cast<int>(cta_rank);  // the pair's two row tiles
                     int tw = m % ph.tiles_w;
                     int th = (m / ph.tiles_w) % ph.tiles_h;
                     int tn = m / (ph.tiles_w * ph.tiles_h);
@@ -896,7 +944,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             tc_fence_before();
             __syncwarp();
             if (threadIdx.x == 64) NML_STAMP(titer, 4);
-            if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[buf]));
+            if (lane == 0) {
+                if (kPair && !leader) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
+                else mbar_arrive(smem_u32(&tempty_bar[buf]));
+            }
         }
         if (kOutMode == OUT_NHWC_TMA && lane == 0) bulk_wait_group<0>();  // stores must land before the CTA ends
     }
@@ -904,10 +955,12 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
     // ------------------------------------------------------------ teardown --
     tc_fence_before();
     __syncthreads();
+    if (kPair) cluster_sync_all();  // neither CTA may leave (or free TMEM) while the partner can still touch it
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        tmem_dealloc(tmem_base, tmem_cols);
+        if (kPair) tmem_dealloc_pair(tmem_base, tmem_cols);
+        else tmem_dealloc(tmem_base, tmem_cols);
     }
 }
 
