@@ -138,7 +138,8 @@ static Profiler g_prof;
 // The instances of the contraction kernel, and the one that serves a given launch.
 typedef void (*UmmaKernel)(const KParams);
 static UmmaKernel kernel_for(const KParams& P) {
-    if (P.mode == MODE_WGRAD) return umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, false>;
+    if (P.mode == MODE_WGRAD)
+        return P.pair ? umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, true> : umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, false>;
     if (P.pair) {
         if (P.out_mode == OUT_NHWC_TMA)
             return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true, true>
@@ -153,7 +154,7 @@ static UmmaKernel kernel_for(const KParams& P) {
     return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NCHW, true, false> : umma_conv_kernel<MODE_FPROP, OUT_NCHW, false, false>;
 }
 static int raise_smem_limit() {
-    UmmaKernel all[11] = {umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, false>,
+    UmmaKernel all[12] = {umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, false>, umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, true>,
                           umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true, false>, umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false, false>,
                           umma_conv_kernel<MODE_FPROP, OUT_NHWC, true, false>, umma_conv_kernel<MODE_FPROP, OUT_NHWC, false, false>,
                           umma_conv_kernel<MODE_FPROP, OUT_NCHW, true, false>, umma_conv_kernel<MODE_FPROP, OUT_NCHW, false, false>,
@@ -605,7 +606,9 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     }
     // Pairs of CTAs (cta_group::2) for 256-wide tiles of problems large enough to fill the pairs: a
     // tile id then names two consecutive row tiles of one phase.
-    P.pair = (tune_env("NML_TUNE_PAIR", 1) && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) &&
+    // (short K loops are epilogue-bound, where pairing only halves the number of independent tiles)
+    const int k_iters_min = P.passes * P.c_blocks * std::max<int>(1, P.phases[0].tap_count);
+    P.pair = (tune_env("NML_TUNE_PAIR", 1) && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) && k_iters_min >= 4 &&
               (P.out_mode == OUT_NHWC_TMA || P.out_mode == OUT_NCHW) && ds->sms >= 2) ? 1 : 0;
     int tiles = 0;
     for (int p = 0; p < n_phases; ++p) {
@@ -759,7 +762,12 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     P.ktiles_w = ceil_div(g.plain_w, 1 << P.wb_log2);
     P.ktiles_h = ceil_div(g.plain_h, 1 << P.hb_log2);
     P.kblocks_total = P.ktiles_w * P.ktiles_h * ceil_div(g.batch, 1 << P.nb_log2);
-    const int m_tiles = ceil_div(P.groups_total * mi.kb, kTileM);
+    // CTA pairs when both operands come as grouped boxes and the tile is 256 columns wide
+    const int G_ = kTileM / mi.kb;
+    const bool a_grp = !window && (cpa % mi.kb == 0) && (P.c_blocks % G_ == 0);
+    const bool b_grp = (cpb % mi.kb == 0);
+    P.pair = (tune_env("NML_TUNE_PAIR", 1) && P.bn == 256 && a_grp && b_grp && ds->sms >= 2) ? 1 : 0;
+    const int m_tiles = P.pair ? ceil_div(ceil_div(P.groups_total * mi.kb, kTileM), 2) : ceil_div(P.groups_total * mi.kb, kTileM);
     const int mn_tiles = m_tiles * P.n_tiles;
     // Split K so that the CTAs finish together: the makespan is (rounds of tiles per CTA) x (K
     // blocks per slice, plus a few blocks' worth of prologue / epilogue per tile).  Pick the split
@@ -772,7 +780,7 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
             int per_sp = ceil_div(P.kblocks_total, sp);
             int real = ceil_div(P.kblocks_total, per_sp);  // every slice gets at least one K block
             if (real != sp) continue;
-            long long rounds = ceil_div(mn_tiles * sp, ds->sms);
+            long long rounds = ceil_div(mn_tiles * sp, P.pair ? ds->sms / 2 : ds->sms);
             long long cost = rounds * (per_sp + 4);
             if (best < 0 || cost < best) {
                 best = cost;
@@ -828,7 +836,7 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
             uint64_t d5[5] = {static_cast<uint64_t>(mi.kb), bdims[1], bdims[2], bdims[3], static_cast<uint64_t>(cpb / mi.kb)};
             uint64_t s5[4] = {static_cast<uint64_t>(cpb) * mi.es, bdims[1] * cpb * mi.es, bdims[1] * bdims[2] * cpb * mi.es,
                               static_cast<uint64_t>(mi.kb) * mi.es};
-            uint32_t b5[5] = {bbox[0], bbox[1], bbox[2], bbox[3], static_cast<uint32_t>(P.bn / mi.kb)};
+            uint32_t b5[5] = {bbox[0], bbox[1], bbox[2], bbox[3], static_cast<uint32_t>((P.pair ? P.bn / 2 : P.bn) / mi.kb)};
             uint32_t e5[5] = {1, 1, 1, 1, 1};
             rc = encode_map(&P.tmB[pl], pb[pl], mi.es, 5, d5, b5, e5, mn_swz, s5);
         } else {

@@ -366,8 +366,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     }
                 } else {  // MODE_WGRAD
                     int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
+                if (kPair) m_tiles = (m_tiles + 1) / 2;  // tile ids name pairs of row tiles
                     int ntile, mt, z;
                     decode_wgrad_tile(P, tile, m_tiles, ntile, mt, z);
+                    if (kPair) mt = 2 * mt + static_cast<int>(cta_rank);
                     int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
                     int kb_begin = z * per;
                     int kb_end = min(kb_begin + per, P.kblocks_total);
@@ -388,6 +390,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         for (int kbi = kb_begin; kbi < kb_end; ++kbi) {
                             int w0 = tw << P.wb_log2, h0 = th << P.hb_log2, n0 = tn << P.nb_log2;
                             uint32_t fb = smem_u32(&full_bar[stage]);
+                            if (kPair) fb = map_to_cta(fb, 0);
                             if (slot == 0) {
                                 if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag,
                                                P.err, ERR_WAIT_EMPTY)) {
@@ -395,11 +398,21 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                                     break;
                                 }
                                 n_in_stage = min(P.ka, left);
-                                mbar_arrive_expect_tx(fb, n_in_stage * tx_bytes);
+                                if (!kPair) mbar_arrive_expect_tx(fb, n_in_stage * tx_bytes);
+                                else if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * n_in_stage * tx_bytes);
                             }
                             --left;
                             uint32_t sa = smem_u32(smem + stage * stage_bytes) + slot * kStageABytes;
                             uint32_t sb = smem_u32(smem + stage * stage_bytes) + b_off + slot * stage_b_bytes;
+                            if (kPair) {  // pairs are only planned for grouped operands
+                                const Tap& tap = P.taps[t0];
+                                if (do_a)
+                                    tma_load_5d_pair(sa, ta, fb, 0, w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0,
+                                                     cib0);
+                                if (do_b)
+                                    tma_load_5d_pair(sb, tb, fb, 0, w0, h0, n0,
+                                                     (ntile * P.bn) / P.kb + static_cast<int>(cta_rank) * (P.bn / 2 / P.kb));
+                            } else
                             if (!do_a) {
                             } else if (P.a_grouped) {
                                 const Tap& tap = P.taps[t0];
@@ -415,7 +428,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                                                 w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0);
                                 }
                             }
-                            if (!do_b) {
+                            if (kPair || !do_b) {
                             } else if (P.b_grouped) {
                                 tma_load_5d(sb, tb, fb, 0, w0, h0, n0, (ntile * P.bn) / P.kb);
                             } else {
@@ -498,6 +511,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 k_iters = P.passes * P.phases[p].tap_count * P.c_blocks;
             } else {
                 int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
+                if (kPair) m_tiles = (m_tiles + 1) / 2;  // tile ids name pairs of row tiles
                 int z = tile / (P.n_tiles * m_tiles);
                 int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
                 int kb_begin = z * per;
@@ -625,8 +639,10 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 }
             } else {
                 int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
+                if (kPair) m_tiles = (m_tiles + 1) / 2;  // tile ids name pairs of row tiles
                 int mt, z;
                 decode_wgrad_tile(P, tile, m_tiles, ntile, mt, z);
+                if (kPair) mt = 2 * mt + static_cast<int>(cta_rank);
                 int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
                 k_iters = max(min(z * per + per, P.kblocks_total) - z * per, 0);
                 int gi = mt * (kTileM / P.kb) + row / P.kb;
