@@ -137,29 +137,33 @@ static Profiler g_prof;
 
 // The instances of the contraction kernel, and the one that serves a given launch.
 typedef void (*UmmaKernel)(const KParams);
+template <int kOut, bool kPair>
+static UmmaKernel fprop_instance(bool f16) {
+    return f16 ? umma_conv_kernel<MODE_FPROP, kOut, true, kPair> : umma_conv_kernel<MODE_FPROP, kOut, false, kPair>;
+}
 static UmmaKernel kernel_for(const KParams& P) {
     if (P.mode == MODE_WGRAD)
         return P.pair ? umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, true> : umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, false>;
+    const bool h = P.out_f16 != 0;
     if (P.pair) {
-        if (P.out_mode == OUT_NHWC_TMA)
-            return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true, true>
-                             : umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false, true>;
-        return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NCHW, true, true> : umma_conv_kernel<MODE_FPROP, OUT_NCHW, false, true>;
+        if (P.out_mode == OUT_NHWC_TMA) return fprop_instance<OUT_NHWC_TMA, true>(h);
+        if (P.out_mode == OUT_NCHW_TMA) return fprop_instance<OUT_NCHW_TMA, true>(h);
+        return fprop_instance<OUT_NCHW, true>(h);
     }
-    if (P.out_mode == OUT_NHWC_TMA)
-        return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true, false>
-                         : umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false, false>;
-    if (P.out_mode == OUT_NHWC)
-        return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NHWC, true, false> : umma_conv_kernel<MODE_FPROP, OUT_NHWC, false, false>;
-    return P.out_f16 ? umma_conv_kernel<MODE_FPROP, OUT_NCHW, true, false> : umma_conv_kernel<MODE_FPROP, OUT_NCHW, false, false>;
+    if (P.out_mode == OUT_NHWC_TMA) return fprop_instance<OUT_NHWC_TMA, false>(h);
+    if (P.out_mode == OUT_NCHW_TMA) return fprop_instance<OUT_NCHW_TMA, false>(h);
+    if (P.out_mode == OUT_NHWC) return fprop_instance<OUT_NHWC, false>(h);
+    return fprop_instance<OUT_NCHW, false>(h);
 }
 static int raise_smem_limit() {
-    UmmaKernel all[12] = {umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, false>, umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, true>,
-                          umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true, false>, umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false, false>,
-                          umma_conv_kernel<MODE_FPROP, OUT_NHWC, true, false>, umma_conv_kernel<MODE_FPROP, OUT_NHWC, false, false>,
-                          umma_conv_kernel<MODE_FPROP, OUT_NCHW, true, false>, umma_conv_kernel<MODE_FPROP, OUT_NCHW, false, false>,
-                          umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, true, true>, umma_conv_kernel<MODE_FPROP, OUT_NHWC_TMA, false, true>,
-                          umma_conv_kernel<MODE_FPROP, OUT_NCHW, true, true>, umma_conv_kernel<MODE_FPROP, OUT_NCHW, false, true>};
+    UmmaKernel all[16] = {umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, false>, umma_conv_kernel<MODE_WGRAD, OUT_NHWC, false, true>,
+                          fprop_instance<OUT_NHWC_TMA, false>(true), fprop_instance<OUT_NHWC_TMA, false>(false),
+                          fprop_instance<OUT_NCHW_TMA, false>(true), fprop_instance<OUT_NCHW_TMA, false>(false),
+                          fprop_instance<OUT_NHWC, false>(true), fprop_instance<OUT_NHWC, false>(false),
+                          fprop_instance<OUT_NCHW, false>(true), fprop_instance<OUT_NCHW, false>(false),
+                          fprop_instance<OUT_NHWC_TMA, true>(true), fprop_instance<OUT_NHWC_TMA, true>(false),
+                          fprop_instance<OUT_NCHW_TMA, true>(true), fprop_instance<OUT_NCHW_TMA, true>(false),
+                          fprop_instance<OUT_NCHW, true>(true), fprop_instance<OUT_NCHW, true>(false)};
     for (UmmaKernel k : all)
         NML_CUDA(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, 232448));
     return NML_OK;
@@ -294,8 +298,10 @@ static int prepare_window(const void* src, int dtype, int layout, int batch, int
 
 // Picks a power-of-two pixel box (w, h, n) with 2^bits pixels that covers the grid with the
 // fewest boxes; ties go to the wider box.  box extents times the element stride stay <= 256.
-static void choose_box(int bits, int gw, int gh, int gn, int s_w, int s_h, int* wl, int* hl, int* nl) {
-    long long best = -1;
+static void choose_box(int bits, int gw, int gh, int gn, int s_w, int s_h, int* wl, int* hl, int* nl,
+                       int prefer_w_log2 = 0) {
+    long long best = -1, best_wide = -1;
+    int ww = 0, wh = 0, wn = 0;
     for (int a = bits; a >= 0; --a) {
         if ((1 << a) * s_w > 256) continue;
         for (int b = bits - a; b >= 0; --b) {
@@ -309,7 +315,20 @@ static void choose_box(int bits, int gw, int gh, int gn, int s_w, int s_h, int* 
                 *hl = b;
                 *nl = c;
             }
+            if (a >= prefer_w_log2 && (best_wide < 0 || tiles < best_wide)) {
+                best_wide = tiles;
+                ww = a;
+                wh = b;
+                wn = c;
+            }
         }
+    }
+    // A box at least 2^prefer_w_log2 pixels wide (whole 128-byte runs for pixel-major stores) is taken
+    // when it costs at most 15 % more tiles.
+    if (prefer_w_log2 > 0 && best_wide > 0 && best_wide * 100 <= best * 115) {
+        *wl = ww;
+        *hl = wh;
+        *nl = wn;
     }
 }
 
@@ -560,7 +579,8 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     P.n_phases = n_phases;
     // M-tile box from the largest phase grid
     const int esw = (f.gather || window) ? 1 : f.s_w, esh = f.gather ? 1 : f.s_h;
-    choose_box(7, P.phases[0].wq, P.phases[0].hq, f.batch, esw, esh, &P.wb_log2, &P.hb_log2, &P.nb_log2);
+    choose_box(7, P.phases[0].wq, P.phases[0].hq, f.batch, esw, esh, &P.wb_log2, &P.hb_log2, &P.nb_log2,
+               (P.out_mode == OUT_NCHW && !f.gather) ? 5 : 0);
     // Tile width: 256 columns run the tensor pipe best, but when that leaves SMs idle (few row tiles,
     // narrow N) a narrower tile wins.  Cost per column relative to a 256-wide tile, measured on B200:
     // 128 -> 1.28, 64 -> 2.24; the makespan is rounds x width x cost.
@@ -604,12 +624,37 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
                 P.out_mode = OUT_NHWC_TMA;
         }
     }
+    // Channel-major (NCHW) output through TMA stores: box = the (w, h) sub-box of the warp's 32 pixels x 64 fp16 / 32 fp32 channels, staged channel-major.  Needs
+    // unit output stride (TMA cannot stride the innermost dimension) and 16-byte aligned rows.
+    if (P.out_mode == OUT_NCHW && tune_env("NML_TUNE_TMASTORE", 1) && P.out_stride_w == 1 && P.out_stride_h == 1) {
+        const int esz = P.out_f16 ? 2 : 4;
+        const int cpi = 128 / esz;
+        const int wbx = 1 << P.wb_log2, hbx = 1 << P.hb_log2;
+        const int bw = std::min(wbx, 32), bh = std::min(hbx, 32 / bw), bnn = 32 / (bw * bh);
+        if (P.bn % cpi == 0 && (bw * esz) % 16 == 0 && (static_cast<size_t>(f.out_w) * esz) % 16 == 0 &&
+            (reinterpret_cast<uintptr_t>(f.out) & 15) == 0) {
+            uint64_t cd[4] = {static_cast<uint64_t>(f.out_w), static_cast<uint64_t>(f.out_h), static_cast<uint64_t>(N),
+                              static_cast<uint64_t>(f.batch)};
+            uint32_t cb[4] = {static_cast<uint32_t>(bw), static_cast<uint32_t>(bh), static_cast<uint32_t>(cpi),
+                              static_cast<uint32_t>(bnn)};
+            uint32_t ce[4] = {1, 1, 1, 1};
+            if (encode_map(&P.tmC, f.out, esz, 4, cd, cb, ce, SWZ_NONE) == NML_OK) {
+                P.out_mode = OUT_NCHW_TMA;
+                int l = 0;
+                while ((1 << l) < bw) ++l;
+                P.cm_bw_log2 = l;
+                l = 0;
+                while ((1 << l) < bh) ++l;
+                P.cm_bh_log2 = l;
+            }
+        }
+    }
     // Pairs of CTAs (cta_group::2) for 256-wide tiles of problems large enough to fill the pairs: a
     // tile id then names two consecutive row tiles of one phase.
     // (short K loops are epilogue-bound, where pairing only halves the number of independent tiles)
     const int k_iters_min = P.passes * P.c_blocks * std::max<int>(1, P.phases[0].tap_count);
     P.pair = (tune_env("NML_TUNE_PAIR", 1) && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) && k_iters_min >= 4 &&
-              (P.out_mode == OUT_NHWC_TMA || P.out_mode == OUT_NCHW) && ds->sms >= 2) ? 1 : 0;
+              (P.out_mode == OUT_NHWC_TMA || P.out_mode == OUT_NCHW_TMA || P.out_mode == OUT_NCHW) && ds->sms >= 2) ? 1 : 0;
     int tiles = 0;
     for (int p = 0; p < n_phases; ++p) {
         Phase& ph = P.phases[p];

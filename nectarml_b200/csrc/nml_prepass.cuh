@@ -32,9 +32,11 @@ __device__ __forceinline__ void store_enc(int enc, void* out0, void* out1, size_
 }
 
 // in  [N][C][HW] (NCHW)  ->  out [N][HW][Cp] (NHWC, channels zero-padded to Cp).
-// Tile of 64 channels x 64 pixels through shared memory; loads coalesce along pixels,
-// stores along channels.  When `colsum` is given, the per-channel sum over all pixels
-// (the bias gradient) is accumulated with one atomic per channel per tile.
+// Tile of 64 channels x 64 pixels through shared memory.  Loads run along pixels (one 256-byte
+// row segment per 16 threads when the rows allow 16-byte loads), stores along channels: 8 threads
+// write the 64 channels of one pixel as 16-byte (fp16) or 2 x 16-byte (tf32 planes) pieces, so a
+// warp store covers four whole pixels.  When `colsum` is given, the per-channel sum over all
+// pixels (the bias gradient) is accumulated with one atomic per channel per tile.
 template <typename TIn>
 __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict__ in, void* out0,
                                                            void* out1, int enc, int C, int Cp, int HW,
@@ -43,12 +45,28 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict
     const int n = blockIdx.z;
     const int c0 = blockIdx.y * 64;
     const int p0 = blockIdx.x * 64;
-    const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;  // 64 x 4
     const TIn* src = in + static_cast<size_t>(n) * C * HW;
-    for (int c = ty; c < 64; c += 4) {
-        float v = 0.f;
-        if (c0 + c < C && p0 + tx < HW) v = load_as_float(src, static_cast<size_t>(c0 + c) * HW + p0 + tx);
-        tile[c][tx] = v;
+    const bool vec_ok = (sizeof(TIn) == 4) && (HW % 4 == 0) && ((reinterpret_cast<uintptr_t>(in) & 15) == 0);
+    if (vec_ok) {
+        const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // 16 x 16: four pixels per thread
+        for (int c = ty; c < 64; c += 16) {
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int p = p0 + 4 * tx;
+            if (c0 + c < C && p < HW)  // HW % 4 == 0, so a started quad is complete
+                v = __ldg(reinterpret_cast<const float4*>(reinterpret_cast<const float*>(src) +
+                                                          static_cast<size_t>(c0 + c) * HW + p));
+            tile[c][4 * tx + 0] = v.x;
+            tile[c][4 * tx + 1] = v.y;
+            tile[c][4 * tx + 2] = v.z;
+            tile[c][4 * tx + 3] = v.w;
+        }
+    } else {
+        const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;  // 64 x 4
+        for (int c = ty; c < 64; c += 4) {
+            float v = 0.f;
+            if (c0 + c < C && p0 + tx < HW) v = load_as_float(src, static_cast<size_t>(c0 + c) * HW + p0 + tx);
+            tile[c][tx] = v;
+        }
     }
     __syncthreads();
     if (colsum != nullptr && threadIdx.x < 64 && c0 + threadIdx.x < C) {
@@ -56,12 +74,40 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict
         for (int p = 0; p < 64; ++p) s += tile[threadIdx.x][(p + threadIdx.x) & 63];
         atomicAdd(colsum + c0 + threadIdx.x, s);
     }
-    // store: channel index fastest
-    for (int p = ty; p < 64; p += 4) {
-        int c = c0 + tx;
-        if (p0 + p < HW && c < Cp) {
-            size_t o = (static_cast<size_t>(n) * HW + p0 + p) * Cp + c;
-            store_enc(enc, out0, out1, o, tile[tx][p]);
+    // store: 8 threads per pixel, 8 channels each
+    const int j = threadIdx.x & 7, pp = threadIdx.x >> 3;  // 8 x 32
+    const int cb = c0 + 8 * j;
+    const bool full8 = (cb + 8 <= Cp) && (Cp % 8 == 0);
+    for (int p = pp; p < 64; p += 32) {
+        if (p0 + p >= HW || cb >= Cp) continue;
+        const size_t o = (static_cast<size_t>(n) * HW + p0 + p) * Cp + cb;
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = tile[8 * j + i][p];
+        if (full8 && enc == ENC_F16) {
+            uint4 pk;
+            __half2 h;
+            h = __floats2half2_rn(v[0], v[1]); pk.x = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(v[2], v[3]); pk.y = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(v[4], v[5]); pk.z = *reinterpret_cast<uint32_t*>(&h);
+            h = __floats2half2_rn(v[6], v[7]); pk.w = *reinterpret_cast<uint32_t*>(&h);
+            *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(out0) + o) = pk;
+        } else if (full8) {
+            float hi[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) hi[i] = to_tf32_rna(v[i]);
+            float4* d0 = reinterpret_cast<float4*>(reinterpret_cast<float*>(out0) + o);
+            d0[0] = make_float4(hi[0], hi[1], hi[2], hi[3]);
+            d0[1] = make_float4(hi[4], hi[5], hi[6], hi[7]);
+            if (enc == ENC_TF32_PAIR) {
+                float4* d1 = reinterpret_cast<float4*>(reinterpret_cast<float*>(out1) + o);
+                d1[0] = make_float4(to_tf32_rna(v[0] - hi[0]), to_tf32_rna(v[1] - hi[1]), to_tf32_rna(v[2] - hi[2]),
+                                    to_tf32_rna(v[3] - hi[3]));
+                d1[1] = make_float4(to_tf32_rna(v[4] - hi[4]), to_tf32_rna(v[5] - hi[5]), to_tf32_rna(v[6] - hi[6]),
+                                    to_tf32_rna(v[7] - hi[7]));
+            }
+        } else {
+            for (int i = 0; i < 8 && cb + i < Cp; ++i) store_enc(enc, out0, out1, o + i, v[i]);
         }
     }
 }

@@ -27,7 +27,8 @@
 namespace nml {
 
 enum { MODE_FPROP = 0, MODE_WGRAD = 1 };
-enum { OUT_NHWC = 0, OUT_NCHW = 1, OUT_NHWC_TMA = 2 };  // _TMA: row-major output written by TMA stores
+enum { OUT_NHWC = 0, OUT_NCHW = 1, OUT_NHWC_TMA = 2, OUT_NCHW_TMA = 3 };  // _TMA: written by TMA stores
+#define NML_IS_TMA_OUT(m) ((m) == OUT_NHWC_TMA || (m) == OUT_NCHW_TMA)
 enum { KIND_F16 = 0, KIND_TF32 = 2 };
 
 // Error codes written to the status word by a kernel that gave up on a wait.
@@ -69,6 +70,7 @@ struct KParams {
     int num_tiles, n_tiles;
     int bn;              // UMMA N of one tile
     int stages;
+    int cm_bw_log2, cm_bh_log2;  // OUT_NCHW_TMA: pixel sub-box (w, h) of one epilogue warp's 32 rows
     int pair;            // 1: launched as clusters of two CTAs sharing 256x256 tiles (cta_group::2)
     int stg_bufs;        // staging buffers per epilogue warp (4 KB each): 2 when shared memory allows, else 1
     int ka;              // K atoms (128-byte-wide operand slices) per stage; narrow tiles take 2 to amortise the
@@ -630,7 +632,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 int ow = ph.pw + P.out_stride_w * iw;
                 int oh = ph.ph + P.out_stride_h * ih;
                 k_iters = ph.tap_count;
-                if (kOutMode != OUT_NCHW) {
+                if (kOutMode != OUT_NCHW && kOutMode != OUT_NCHW_TMA) {
                     row_off = ((static_cast<size_t>(n) * P.out_h + oh) * P.out_w + ow) * P.ld_out;
                     col_stride = 1;
                 } else {
@@ -662,7 +664,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     col_stride = static_cast<size_t>(P.c_patch) * P.n_taps;
                 }
             }
-            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC_TMA && P.bias != nullptr) {
+            if (kMode == MODE_FPROP && NML_IS_TMA_OUT(kOutMode) && P.bias != nullptr) {
                 // this tile's bias values, one copy per warp (no cross-warp barrier to get stuck on)
                 float* btw = bias_tile + (warp - 2) * 256;
                 const int cb0 = ntile * P.bn;
@@ -695,7 +697,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             if (threadIdx.x == 64) NML_STAMP(titer, 3);
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * P.bn;
             const int col_base = ntile * P.bn;
-            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC_TMA) {
+            if (kMode == MODE_FPROP && NML_IS_TMA_OUT(kOutMode)) {
                 // Row-major output through TMA: each warp converts 128-byte row pieces of its 32 rows into a
                 // swizzled 4 KB buffer and one lane hands the buffer to a TMA store, whose box is exactly
                 // those 32 rows; rows and columns outside the tensor are clipped by the hardware.  Two
@@ -743,6 +745,29 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                         if (P.stg_bufs == 2) bulk_wait_group_read<1>(); else bulk_wait_group_read<0>();
                     }
                     __syncwarp();
+                    if (kOutMode == OUT_NCHW_TMA) {
+                        // channel-major output: the staging tile is [image][channel][h][w] of this warp's
+                        // pixel sub-box, so lane (= pixel) l writes channel j at ((dn*cpi + j)*bh + dh)*bw + dw
+                        const int bwl = P.cm_bw_log2, bhl = P.cm_bh_log2;
+                        const int dwp = lane & ((1 << bwl) - 1);
+                        const int dhp = (lane >> bwl) & ((1 << bhl) - 1);
+                        const int dnp = lane >> (bwl + bhl);
+                        const uint32_t esz = kOutF16 ? 2 : 4;
+                        const uint32_t pix = buf_addr + ((((dnp * cpi) << bhl) + dhp) << bwl) * esz + dwp * esz;
+                        const uint32_t cstep = (esz << (bwl + bhl));  // bytes between consecutive channels
+#pragma unroll
+                        for (int j = 0; j < cpi; ++j) {
+                            float xv = __uint_as_float(j < 32 ? r0[j & 31] : r1[j & 31]);
+                            if (has_bias) xv += bt[c0 + j];
+                            if (kOutF16) {
+                                const __half hv = __float2half_rn(xv);
+                                asm volatile("st.shared.b16 [%0], %1;" ::"r"(pix + j * cstep), "h"(*reinterpret_cast<const uint16_t*>(&hv)) : "memory");
+                            } else {
+                                if (P.round_f16) xv = round_through_f16(xv);
+                                asm volatile("st.shared.b32 [%0], %1;" ::"r"(pix + j * cstep), "r"(__float_as_uint(xv)) : "memory");
+                            }
+                        }
+                    } else
 #pragma unroll
                     for (int qq = 0; qq < 8; ++qq) {
                         uint4 pk;
@@ -785,7 +810,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                     fence_proxy_async();  // make the generic-proxy writes visible to the TMA engine
                     __syncwarp();
                     if (lane == 0) {
-                        tma_store_4d(&P.tmC, buf_addr, cg, sw, sh, sn);
+                        if (kOutMode == OUT_NCHW_TMA) tma_store_4d(&P.tmC, buf_addr, sw, sh, cg, sn);
+                        else tma_store_4d(&P.tmC, buf_addr, cg, sw, sh, sn);
                         bulk_commit_group();
                     }
                     ++store_seq;
@@ -965,7 +991,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 else mbar_arrive(smem_u32(&tempty_bar[buf]));
             }
         }
-        if (kOutMode == OUT_NHWC_TMA && lane == 0) bulk_wait_group<0>();  // stores must land before the CTA ends
+        if (NML_IS_TMA_OUT(kOutMode) && lane == 0) bulk_wait_group<0>();  // stores must land before the CTA ends
     }
 
     // ------------------------------------------------------------ teardown --
