@@ -345,13 +345,23 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
     // Shared memory: the operand ring, then the epilogue's staging buffers (two per warp if that does not
     // cost a ring stage, else one), the per-warp bias tiles, and the barriers.
     const int fixed = 1024 + 256 + kBiasTileBytes;
-    int stages2 = (232448 - fixed - 4 * 2 * kStagingBufBytes) / stage_bytes;
-    int stages1 = (232448 - fixed - 4 * 1 * kStagingBufBytes) / stage_bytes;
+    const bool tma_out = (P.mode == MODE_FPROP) && NML_IS_TMA_OUT(P.out_mode);
+    // A second group of four epilogue warps (TMA-store instances only) halves the drain time of a tile;
+    // it pays where the K loop is too short to hide the drain behind the next tile's MMAs.
+    {
+        const int cpi = P.out_f16 ? 64 : 32;
+        int k_slices = 0;  // 64-deep (fp16) K slices per tile, longest phase
+        for (int p = 0; p < P.n_phases; ++p) k_slices = std::max(k_slices, P.passes * P.c_blocks * P.phases[p].tap_count);
+        const bool short_k = k_slices <= tune_env("NML_TUNE_EPI8_K", 8);
+        P.epi_warps = (tma_out && short_k && P.bn / cpi >= 2 && tune_env("NML_TUNE_EPI8", 1)) ? 8 : 4;
+    }
+    int stages2 = (232448 - fixed - P.epi_warps * 2 * kStagingBufBytes) / stage_bytes;
+    int stages1 = (232448 - fixed - P.epi_warps * 1 * kStagingBufBytes) / stage_bytes;
     P.stg_bufs = (stages2 >= std::min(stages1, 8)) ? 2 : 1;
     int stages = std::min(8, P.stg_bufs == 2 ? stages2 : stages1);
     stages = std::max(2, std::min(stages, tune_env("NML_TUNE_STAGES", 8)));
     P.stages = stages;
-    size_t smem = static_cast<size_t>(stages) * stage_bytes + 4 * P.stg_bufs * kStagingBufBytes + fixed;
+    size_t smem = static_cast<size_t>(stages) * stage_bytes + P.epi_warps * P.stg_bufs * kStagingBufBytes + fixed;
     smem = std::max<size_t>(smem, 120 * 1024);  // one CTA per SM: each allocates its own TMEM
     P.err = ds->err;
 #ifdef NML_TRACE
@@ -367,7 +377,7 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
         cudaLaunchConfig_t cfg;
         memset(&cfg, 0, sizeof(cfg));
         cfg.gridDim = dim3(grid);
-        cfg.blockDim = dim3(kThreads);
+        cfg.blockDim = dim3(threads_for(P.mode == MODE_FPROP ? P.out_mode : OUT_NHWC));
         cfg.dynamicSmemBytes = smem;
         cfg.stream = st;
         cudaLaunchAttribute attr;
@@ -379,7 +389,7 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
         cfg.numAttrs = 1;
         NML_CUDA(cudaLaunchKernelEx(&cfg, kernel_for(P), P));
     } else {
-        kernel_for(P)<<<grid, kThreads, smem, st>>>(P);
+        kernel_for(P)<<<grid, threads_for(P.mode == MODE_FPROP ? P.out_mode : OUT_NHWC), smem, st>>>(P);
     }
     NML_CUDA(cudaGetLastError());
     if (rec) NML_CUDA(cudaEventRecord(g_prof.stop[g_prof.n++], st));

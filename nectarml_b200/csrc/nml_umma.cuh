@@ -44,9 +44,12 @@ constexpr int kMaxPhases = 16;
 constexpr int kMaxTaps = 128;
 constexpr int kTileM = 128;
 constexpr int kStageABytes = kTileM * 128;
-constexpr int kThreads = 224;  // warp 0: A loads, warp 1: MMA issue, warps 2-5: epilogue, warp 6: B loads
+constexpr int kThreads = 224;      // warp 0: A loads, warp 1: MMA issue, warps 2-5: epilogue, warp 6: B loads
+constexpr int kThreadsWide = 352;  // TMA-store instances: warps 7-10 are a second epilogue group (used when the
+                                   // K loop is short and the epilogue is the critical path; they need few registers)
+__host__ __device__ constexpr int threads_for(int out_mode) { return (out_mode == 2 || out_mode == 3) ? kThreadsWide : kThreads; }
 constexpr int kStagingBufBytes = 4096;         // one staging buffer: 32 rows x 128 bytes of output
-constexpr int kBiasTileBytes = 4 * 256 * 4;   // per epilogue warp: the current tile's bias values
+constexpr int kBiasTileBytes = 8 * 256 * 4;   // per epilogue warp (up to 8): the current tile's bias values
 
 struct Tap {
     short dh, dw;  // offset of this tap's box from the tile origin, in input pixels
@@ -71,6 +74,7 @@ struct KParams {
     int bn;              // UMMA N of one tile
     int stages;
     int cm_bw_log2, cm_bh_log2;  // OUT_NCHW_TMA: pixel sub-box (w, h) of one epilogue warp's 32 rows
+    int epi_warps;       // 4, or 8 on the TMA-store instances when the epilogue is the critical path
     int pair;            // 1: launched as clusters of two CTAs sharing 256x256 tiles (cta_group::2)
     int stg_bufs;        // staging buffers per epilogue warp (4 KB each): 2 when shared memory allows, else 1
     int ka;              // K atoms (128-byte-wide operand slices) per stage; narrow tiles take 2 to amortise the
@@ -213,7 +217,7 @@ __device__ __noinline__ void store_row_chunk(const KParams& P, const float (&v)[
 // the rank-0 CTA; each CTA loads its own 128 rows of A and its own 128-column half of B (no multicast),
 // which halves the B traffic and the MMA issue cost per SM and leaves room for 6 stages.
 template <int kMode, int kOutMode, bool kOutF16, bool kPair>
-__global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_constant__ KParams P) {
+__global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(const __grid_constant__ KParams P) {
     extern __shared__ uint8_t smem_raw[];
     // stages need 1024-byte alignment for the 128-byte swizzle pattern
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -226,7 +230,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
     const int stage_bytes = P.ka * (kStageABytes + stage_b_bytes);  // [A atoms][B atoms]
     const int b_off = P.ka * kStageABytes;                        // first B atom within a stage
     uint8_t* staging = smem + P.stages * stage_bytes;  // 4 epilogue warps x 4 KB
-    const int staging_bytes = 4 * P.stg_bufs * kStagingBufBytes;
+    const int staging_bytes = P.epi_warps * P.stg_bufs * kStagingBufBytes;
     float* bias_tile = reinterpret_cast<float*>(staging + staging_bytes);
     uint8_t* ctrl = staging + staging_bytes + kBiasTileBytes;
     uint64_t* full_bar = reinterpret_cast<uint64_t*>(ctrl);          // [stages]
@@ -248,7 +252,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&tfull_bar[b]), 1);
-            mbar_init(smem_u32(&tempty_bar[b]), kPair ? 8 : 4);  // the leader also hears the partner's epilogue warps
+            mbar_init(smem_u32(&tempty_bar[b]), (kPair ? 2 : 1) * P.epi_warps);  // the leader also hears the partner's epilogue warps
         }
         *abort_flag = 0;
         fence_mbar_init();
@@ -600,7 +604,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
         }
     }
     // ------------------------------------------------------------ epilogue --
-    else {
+    else if (warp < 6 || P.epi_warps == 8) {
+        const int ew = (warp < 6) ? warp - 2 : warp - 3;  // epilogue warp index 0..7; 4..7 form the second group
         const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
         const int row = quarter * 32 + lane;
         bool ok = true;
@@ -666,7 +671,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
             }
             if (kMode == MODE_FPROP && NML_IS_TMA_OUT(kOutMode) && P.bias != nullptr) {
                 // this tile's bias values, one copy per warp (no cross-warp barrier to get stuck on)
-                float* btw = bias_tile + (warp - 2) * 256;
+                float* btw = bias_tile + ew * 256;
                 const int cb0 = ntile * P.bn;
                 __syncwarp();
                 for (int j = lane; j < P.bn; j += 32) btw[j] = (cb0 + j < P.c_out) ? __ldg(P.bias + cb0 + j) : 0.f;
@@ -703,8 +708,8 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 // those 32 rows; rows and columns outside the tensor are clipped by the hardware.  Two
                 // buffers alternate, so packing the next piece overlaps the store of the previous one.
                 constexpr int cpi = kOutF16 ? 64 : 32;
-                const uint32_t stg0 = smem_u32(staging) + (warp - 2) * P.stg_bufs * kStagingBufBytes;
-                const float* bt = bias_tile + (warp - 2) * 256;
+                const uint32_t stg0 = smem_u32(staging) + ew * P.stg_bufs * kStagingBufBytes;
+                const float* bt = bias_tile + ew * 256;
                 const bool has_bias = (P.bias != nullptr);
                 // store coordinates of this warp's first row
                 int sw, sh, sn;
@@ -729,16 +734,22 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
 #pragma unroll
                     for (int j = 0; j < 32; ++j) r0[j] = r1[j] = 0u;
                 }
-                if (live && col_base < P.c_out) {
-                    tmem_ld_32x32(t_row, r0);
-                    if (cpi == 64) tmem_ld_32x32(t_row + 32, r1);
+                // with two epilogue groups, the first takes the low half of the tile's pieces, the second the rest
+                int c_begin = 0, c_end = P.bn;
+                if (P.epi_warps == 8) {
+                    const int half = ((P.bn / cpi + 1) / 2) * cpi;
+                    if (ew < 4) c_end = min(half, P.bn); else c_begin = half;
+                }
+                if (live && c_begin < c_end && col_base + c_begin < P.c_out) {
+                    tmem_ld_32x32(t_row + c_begin, r0);
+                    if (cpi == 64) tmem_ld_32x32(t_row + c_begin + 32, r1);
                     tmem_ld_wait();
                 }
-                for (int c0 = 0; c0 < P.bn; c0 += cpi) {
+                for (int c0 = c_begin; c0 < c_end; c0 += cpi) {
                     const int cg = col_base + c0;
                     if (cg >= P.c_out) break;  // uniform across the warp
                     const int cn = c0 + cpi;
-                    const bool more = live && cn < P.bn && col_base + cn < P.c_out;
+                    const bool more = live && cn < c_end && col_base + cn < P.c_out;
                     const uint32_t buf_addr = stg0 + ((P.stg_bufs == 2) ? (store_seq & 1) * kStagingBufBytes : 0);
                     // the store that last read this buffer must be done reading it
                     if (lane == 0) {
@@ -826,7 +837,7 @@ __global__ void __launch_bounds__(kThreads, 1) umma_conv_kernel(const __grid_con
                 // added on the way out, where each lane owns the same 16 bytes of every row.
                 const int cpi = kOutF16 ? 64 : 32;
                 const int esz = kOutF16 ? 2 : 4;
-                const uint32_t stg = smem_u32(staging) + (warp - 2) * P.stg_bufs * kStagingBufBytes;
+                const uint32_t stg = smem_u32(staging) + ew * P.stg_bufs * kStagingBufBytes;
                 const bool has_bias = (P.bias != nullptr);
                 const bool aligned = ((static_cast<size_t>(P.ld_out) * esz) & 15) == 0 &&
                                      (reinterpret_cast<uintptr_t>(P.out) & 15) == 0 &&
