@@ -34,6 +34,10 @@ LINEAR_SWEEP = [(rows, d) for d in (512, 1024, 2048) for rows in (4096, 16384)]
 # its small-channel path exists): (c_in, hw, c_out, k, stride, pad)
 RESNET_SWEEP = [(64, 56, 64, 3, 1, 1), (256, 56, 64, 1, 1, 0), (128, 28, 128, 3, 2, 1), (1024, 14, 2048, 1, 2, 0)]
 RESNET_BATCH = 256
+LINEAR_NAME = ("Linear sweep X[B*T,d]@W^T[d,4d]+b, d in {512,1024,2048} x B*T in {4096,16384}, "
+               "forward+dgrad+wgrad+db, fp16 storage / fp32 accumulate")
+RESNET_NAME = ("ResNet-style conv shapes, batch 256 per GPU, NHWC fp16: 3x3 64->64 @56, 1x1 256->64 @56, "
+               "3x3 s2 128->128 @28, 1x1 s2 1024->2048 @14; forward+dgrad+wgrad+db")
 
 
 def measured_peaks():
@@ -172,12 +176,9 @@ def run_gpu(args):
         bytes_resident = sum(t.numel() * t.element_size() for l in layers for t in
                              (l["xd"], l["dyd"], l["wd"], l["y"], l["dx"], l["dw"]))
 
-        def step(from_host: bool):
+        def step():
             pending = []
             for l in layers:
-                if from_host:
-                    l["xd"].copy_(l["x"], non_blocking=True)
-                    l["dyd"].copy_(l["dy"], non_blocking=True)
                 ops.linear_forward(l["xd"], l["wd"], l["bd"], out=l["y"])
                 ops.linear_backward_data(l["dyd"], l["wd"], out=l["dx"])
                 ops.linear_backward_weight(l["xd"], l["dyd"], dw=l["dw"], db=l["db"])
@@ -186,15 +187,44 @@ def run_gpu(args):
                     pending.append(dist.all_reduce(l["db"], async_op=True))
             for p in pending:
                 p.wait()
-            if from_host:
-                for l in layers:
+
+        # End-to-end step: the same calls, with each layer's inputs coming from pinned host memory and its
+        # gradients going back to it.  Copies run on their own streams, ordered against the compute stream
+        # by events, so a layer's transfers overlap the other layers' kernels inside the step; every step
+        # ends with the compute stream waiting for that step's last device-to-host copy.
+        s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+        ev_in = [torch.cuda.Event() for _ in layers]
+        ev_done = [torch.cuda.Event() for _ in layers]
+        ev_out = [torch.cuda.Event() for _ in layers]
+
+        def step_e2e():
+            cur = torch.cuda.current_stream()
+            with torch.cuda.stream(s_in):
+                for i, l in enumerate(layers):
+                    s_in.wait_event(ev_done[i])  # the previous step's kernels have finished reading xd / dyd
+                    l["xd"].copy_(l["x"], non_blocking=True)
+                    l["dyd"].copy_(l["dy"], non_blocking=True)
+                    ev_in[i].record(s_in)
+            for i, l in enumerate(layers):
+                cur.wait_event(ev_in[i])
+                cur.wait_event(ev_out[i])  # the previous step's copy of dw / db has left the device
+                ops.linear_forward(l["xd"], l["wd"], l["bd"], out=l["y"])
+                ops.linear_backward_data(l["dyd"], l["wd"], out=l["dx"])
+                ops.linear_backward_weight(l["xd"], l["dyd"], dw=l["dw"], db=l["db"])
+                if world > 1:
+                    dist.all_reduce(l["dw"])
+                    dist.all_reduce(l["db"])
+                ev_done[i].record(cur)
+                with torch.cuda.stream(s_out):
+                    s_out.wait_event(ev_done[i])
                     l["dw_host"].copy_(l["dw"], non_blocking=True)
                     l["db_host"].copy_(l["db"], non_blocking=True)
+                    ev_out[i].record(s_out)
+            cur.wait_event(ev_out[-1])
 
         h2d = sum(l["x"].numel() * 2 + l["dy"].numel() * 2 for l in layers)
         d2h = sum(l["dw"].numel() * 4 + l["db"].numel() * 4 for l in layers)
-        workload = {"workload": "Linear sweep X[B*T,d]@W^T[d,4d]+b, d in {512,1024,2048} x B*T in {4096,16384}, "
-                                "forward+dgrad+wgrad+db, fp16 storage / fp32 accumulate",
+        workload = {"workload": LINEAR_NAME,
                     "layers": len(layers), "rows_per_gpu": sum(l["rows"] for l in layers)}
     else:
         rng = np.random.default_rng(1237 + rank)
@@ -216,7 +246,7 @@ def run_gpu(args):
         bytes_resident = sum(t.numel() * t.element_size() for l in layers for t in (l["xd"], l["dyd"], l["y"], l["dx"]))
         grads = {}
 
-        def step(from_host: bool):
+        def step():
             pending = []
             for i, l in enumerate(layers):
                 ops.conv_forward(l["g"], l["xd"], l["wd"], None, layout="nhwc", out=l["y"])
@@ -229,8 +259,7 @@ def run_gpu(args):
                 p.wait()
 
         h2d = d2h = 0
-        workload = {"workload": "ResNet-style conv shapes, batch 256 per GPU, NHWC fp16: 3x3 64->64 @56, 1x1 256->64 @56, "
-                                "3x3 s2 128->128 @28, 1x1 s2 1024->2048 @14; forward+dgrad+wgrad+db",
+        workload = {"workload": RESNET_NAME,
                     "layers": len(layers)}
 
     def barrier():
@@ -253,7 +282,7 @@ def run_gpu(args):
         return float(ms.item())
 
     for _ in range(max(args.warmup, 3)):
-        step(False)
+        step()
     ops.device_status()
 
     sampler = ClockSampler(local) if rank == 0 else None
@@ -262,7 +291,7 @@ def run_gpu(args):
         time.sleep(0.25)
     launches0 = ops.launch_count()
     t0 = time.time()
-    ms_total = timed(lambda: step(False), args.steps)
+    ms_total = timed(lambda: step(), args.steps)
     t1 = time.time()
     launches = ops.launch_count() - launches0
     clocks = sampler.stop(t0, t1) if sampler else None
@@ -273,7 +302,7 @@ def run_gpu(args):
     barrier()
     ops.profile_begin(n_rec)
     for _ in range(args.steps):
-        step(False)
+        step()
     per_launch_ms = ops.profile_end(n_rec)
     kern_ms = sum(per_launch_ms)
     kern_flops = sum(flops_per_launch) * (len(per_launch_ms) / max(len(flops_per_launch), 1))
@@ -283,9 +312,12 @@ def run_gpu(args):
     e2e = None
     if args.workload == "linear":
         for _ in range(2):
-            step(True)
+            step_e2e()
         e2e_steps = max(2, min(args.steps, 5))
-        e2e_ms = timed(lambda: step(True), e2e_steps)
+        e2e_ms = timed(step_e2e, e2e_steps)
+        for l in layers:  # the gradients that reached the host are the ones on the device
+            if not torch.equal(l["db_host"], l["db"].cpu()):
+                raise SystemExit("bench.py: end-to-end leg returned stale gradients")
         e2e = {"value": step_flops * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
                "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
 
@@ -388,7 +420,7 @@ def run_reference(args):
         return
     world = int(os.environ.get("WORLD_SIZE", "1"))
     warm = max(args.warmup, 1)
-    per_step_budget = max(0.5, min(6.0, 150.0 / (args.steps + warm)))
+    per_step_budget = args.cpu_budget if args.cpu_budget > 0 else max(0.5, min(6.0, 150.0 / (args.steps + warm)))
     for _ in range(warm):
         cpu_baseline(args.workload, per_step_budget)
     flops = secs = 0.0
@@ -400,13 +432,13 @@ def run_reference(args):
     value = flops / secs / 1e12
     base = {k: base[k] for k in ("unit", "cores", "kind", "sample")}
     base["value"] = value
-    name = ("Linear sweep X[B*T,d]@W^T[d,4d]+b, d in {512,1024,2048} x B*T in {4096,16384}, forward+dgrad+wgrad+db"
-            if args.workload == "linear" else "ResNet-style conv shapes, forward+dgrad+wgrad")
+    name = LINEAR_NAME if args.workload == "linear" else RESNET_NAME
     print(json.dumps({
         "metric": "conv/linear fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": warm, "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 (CPU)", "data": "synthetic", "impl": "reference",
-        "config": {"workload": name, "note": "CPU arithmetic of the reference (NumPy) on a bounded sample per step"},
+        "config": {"workload": name, "parallelism": "host cores of rank 0",
+                   "note": "the reference's CPU arithmetic (NumPy, fp32) on a bounded sample of the workload per step"},
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
@@ -420,6 +452,8 @@ def main():
     ap.add_argument("--impl", default="nectarml_b200", choices=["nectarml_b200", "reference"])
     ap.add_argument("--workload", default="linear", choices=["linear", "resnet"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-budget", type=float, default=0.0,
+                    help="seconds of CPU work per step of the reference arm (default: sized from --steps)")
     ap.add_argument("--only", default="", help="linear workload: restrict the sweep to ROWSxD (for profiling captures)")
     args = ap.parse_args()
     if args.impl == "reference":
