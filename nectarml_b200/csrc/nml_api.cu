@@ -355,13 +355,56 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
         const bool short_k = k_slices <= tune_env("NML_TUNE_EPI8_K", 8);
         P.epi_warps = (tma_out && short_k && P.bn / cpi >= 2 && tune_env("NML_TUNE_EPI8", 1)) ? 8 : 4;
     }
+    size_t smem;
+    if (P.patch) {
+        // [B: resident slices, or a ring of single-slice stages][patch buffers][staging][bias][barriers]
+        P.ka = 1;
+        const int b_slice = P.bn * 128;
+        const int taps = P.phases[0].tap_count;
+        const int res_bytes = P.c_blocks * taps * b_slice;
+        P.stg_bufs = 2;
+        int avail = 232448 - fixed - P.epi_warps * P.stg_bufs * kStagingBufBytes;
+        const bool res_wanted = P.n_tiles == 1 && P.passes == 1 && tune_env("NML_TUNE_BRES", 1);
+        if (res_wanted && res_bytes + 2 * P.patch_bytes > avail) {  // trade staging for residency
+            P.stg_bufs = 1;
+            avail = 232448 - fixed - P.epi_warps * P.stg_bufs * kStagingBufBytes;
+            if (res_bytes + 2 * P.patch_bytes > avail) {
+                P.epi_warps = 4;
+                avail = 232448 - fixed - P.epi_warps * P.stg_bufs * kStagingBufBytes;
+            }
+        }
+        int b_region;
+        if (res_wanted && res_bytes + 2 * P.patch_bytes <= avail) {
+            P.b_resident = 1;
+            P.stages = 1;
+            b_region = res_bytes;
+            P.a_stages = std::min(4, (avail - res_bytes) / P.patch_bytes);
+        } else {
+            P.b_resident = 0;
+            P.a_stages = std::min(3, std::max(2, P.passes * P.c_blocks));
+            P.stages = std::min(8, (avail - P.a_stages * P.patch_bytes) / b_slice);
+            if (P.stages < 3) {  // wide tiles: give the B ring room
+                P.a_stages = 2;
+                P.stg_bufs = 1;
+                avail = 232448 - fixed - P.epi_warps * P.stg_bufs * kStagingBufBytes;
+                P.stages = std::min(8, (avail - P.a_stages * P.patch_bytes) / b_slice);
+            }
+            if (P.stages < 2) return NML_ERR_UNSUPPORTED;
+            b_region = P.stages * b_slice;
+        }
+        P.a_ring_off = static_cast<int>(round_up(b_region, 1024));
+        P.ring_bytes = P.a_ring_off + P.a_stages * P.patch_bytes;
+        smem = static_cast<size_t>(P.ring_bytes) + P.epi_warps * P.stg_bufs * kStagingBufBytes + fixed;
+    } else {
     int stages2 = (232448 - fixed - P.epi_warps * 2 * kStagingBufBytes) / stage_bytes;
     int stages1 = (232448 - fixed - P.epi_warps * 1 * kStagingBufBytes) / stage_bytes;
     P.stg_bufs = (stages2 >= std::min(stages1, 8)) ? 2 : 1;
     int stages = std::min(8, P.stg_bufs == 2 ? stages2 : stages1);
     stages = std::max(2, std::min(stages, tune_env("NML_TUNE_STAGES", 8)));
     P.stages = stages;
-    size_t smem = static_cast<size_t>(stages) * stage_bytes + P.epi_warps * P.stg_bufs * kStagingBufBytes + fixed;
+    P.ring_bytes = stages * stage_bytes;
+    smem = static_cast<size_t>(stages) * stage_bytes + P.epi_warps * P.stg_bufs * kStagingBufBytes + fixed;
+    }
     smem = std::max<size_t>(smem, 120 * 1024);  // one CTA per SM: each allocates its own TMEM
     P.err = ds->err;
 #ifdef NML_TRACE
@@ -591,6 +634,46 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     const int esw = (f.gather || window) ? 1 : f.s_w, esh = f.gather ? 1 : f.s_h;
     choose_box(7, P.phases[0].wq, P.phases[0].hq, f.batch, esw, esh, &P.wb_log2, &P.hb_log2, &P.nb_log2,
                (P.out_mode == OUT_NCHW && !f.gather) ? 5 : 0);
+    bool patch_resident = false;
+    // Patch walk: unit-stride problems with several taps load one haloed patch per channel block instead of
+    // one box per tap (8 x 16 pixel tiles of a single image).  Taken when the fixed tile shape does not
+    // waste much more of the tile than the free-form box does.
+    {
+        const int mode = tune_env("NML_TUNE_PATCH", 1);
+        int dw_min = 0, dw_max = 0, dh_min = 0, dh_max = 0;
+        for (int t = 0; t < n_taps; ++t) {
+            dw_min = t ? std::min<int>(dw_min, P.taps[t].dw) : P.taps[t].dw;
+            dw_max = t ? std::max<int>(dw_max, P.taps[t].dw) : P.taps[t].dw;
+            dh_min = t ? std::min<int>(dh_min, P.taps[t].dh) : P.taps[t].dh;
+            dh_max = t ? std::max<int>(dh_max, P.taps[t].dh) : P.taps[t].dh;
+        }
+        const int pw_ = 8 + dw_max - dw_min, ph_ = 16 + dh_max - dh_min;
+        const int wq = P.phases[0].wq, hq = P.phases[0].hq;
+        const double eff_patch = static_cast<double>(wq) * hq / (1.0 * round_up(wq, 8) * round_up(hq, 16));
+        const double eff_box = static_cast<double>(wq) * hq * f.batch /
+                               (1.0 * round_up(wq, 1 << P.wb_log2) * round_up(hq, 1 << P.hb_log2) * round_up(f.batch, 1 << P.nb_log2));
+        const bool can = !window && n_phases == 1 && n_taps >= 2 && esw == 1 && esh == 1 && P.out_stride_w == 1 &&
+                         P.out_stride_h == 1 && pw_ <= 256 && ph_ <= 256 && pw_ * ph_ * 128 <= 48 * 1024;
+        // B stays resident when every slice fits beside two patch buffers and the smallest epilogue staging;
+        // streaming B tap by tap pays only for the 3xTF32 split (a barrier round trip per 4 short MMAs otherwise)
+        const long long res_need = 1ll * c_blocks * n_taps * round_up(N, 32) * 128 + 2 * round_up(pw_ * ph_ * 128, 1024);
+        const bool res_ok = P.passes == 1 && N <= 256 &&
+                            res_need <= 232448 - (1024 + 256 + kBiasTileBytes) - 4 * kStagingBufBytes;
+        patch_resident = res_ok;
+        if (can && mode && (mode == 2 || (eff_patch >= 0.8 * eff_box && (res_ok || (P.passes == 3 && N <= 128))))) {
+            P.patch = 1;
+            P.patch_w = pw_;
+            P.patch_h = ph_;
+            P.patch_org_w = dw_min;
+            P.patch_org_h = dh_min;
+            P.patch_bytes = static_cast<int>(round_up(pw_ * ph_ * 128, 1024));
+            for (int t = 0; t < n_taps; ++t)
+                P.taps[t].aoff = ((P.taps[t].dh - dh_min) * pw_ + (P.taps[t].dw - dw_min)) * 128 / 16;
+            P.wb_log2 = 3;
+            P.hb_log2 = 4;
+            P.nb_log2 = 0;
+        }
+    }
     // Tile width: 256 columns run the tensor pipe best, but when that leaves SMs idle (few row tiles,
     // narrow N) a narrower tile wins.  Cost per column relative to a 256-wide tile, measured on B200:
     // 128 -> 1.28, 64 -> 2.24; the makespan is rounds x width x cost.
@@ -599,12 +682,12 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         for (int p = 0; p < n_phases; ++p)
             m_tiles_all += 1ll * ceil_div(P.phases[p].wq, 1 << P.wb_log2) * ceil_div(P.phases[p].hq, 1 << P.hb_log2) *
                            ceil_div(f.batch, 1 << P.nb_log2);
-        const int forced = tune_env("NML_TUNE_BN", 0);
-        const int cand[3] = {256, 128, 64};
+        const int forced = (P.patch && patch_resident) ? static_cast<int>(round_up(N, 32)) : tune_env("NML_TUNE_BN", 0);
+        const int cand[4] = {256, 128, 64, forced};
         const double cost[3] = {1.0, 1.28, 2.24};
         double best = -1;
-        for (int i = 0; i < 3; ++i) {
-            if (forced && cand[i] != forced) continue;
+        for (int i = 0; i < 4; ++i) {
+            if (forced ? i != 3 : i == 3) continue;
             int nt = ceil_div(N, cand[i]);
             int bn = static_cast<int>(round_up(ceil_div(N, nt), b_mn_major ? 64 : 32));
             if (bn > 256) continue;
@@ -663,7 +746,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     // tile id then names two consecutive row tiles of one phase.
     // (short K loops are epilogue-bound, where pairing only halves the number of independent tiles)
     const int k_iters_min = P.passes * P.c_blocks * std::max<int>(1, P.phases[0].tap_count);
-    P.pair = (tune_env("NML_TUNE_PAIR", 1) && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) && k_iters_min >= 4 &&
+    P.pair = (tune_env("NML_TUNE_PAIR", 1) && !P.patch && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) && k_iters_min >= 4 &&
               (P.out_mode == OUT_NHWC_TMA || P.out_mode == OUT_NCHW_TMA || P.out_mode == OUT_NCHW) && ds->sms >= 2) ? 1 : 0;
     int tiles = 0;
     for (int p = 0; p < n_phases; ++p) {
@@ -683,6 +766,11 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         uint32_t abox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>((1 << P.wb_log2) * esw),
                             static_cast<uint32_t>((1 << P.hb_log2) * esh), static_cast<uint32_t>(1 << P.nb_log2)};
         uint32_t aes[4] = {1, static_cast<uint32_t>(esw), static_cast<uint32_t>(esh), 1};
+        if (P.patch) {
+            abox[1] = static_cast<uint32_t>(P.patch_w);
+            abox[2] = static_cast<uint32_t>(P.patch_h);
+            abox[3] = 1;
+        }
         if (window) {
             // dims: (64 elements = 8 pixels x 8 channels, output column, padded row, image); consecutive
             // output columns start s_w pixels apart, so the windows overlap

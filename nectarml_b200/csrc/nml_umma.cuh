@@ -54,6 +54,7 @@ constexpr int kBiasTileBytes = 8 * 256 * 4;   // per epilogue warp (up to 8): th
 struct Tap {
     short dh, dw;  // offset of this tap's box from the tile origin, in input pixels
     int wk;        // first K index (fprop) / tap index (wgrad) of this tap in the weight operand
+    int aoff;      // patch walk: where this tap's rows start inside the patch, in 16-byte units
 };
 
 struct Phase {
@@ -82,6 +83,21 @@ struct KParams {
     int a_mn_major, b_mn_major;
     int a_grouped, b_grouped;  // MN-major operand fetched as ONE box whose outermost dimension walks
                                // the 128-byte column groups (needs the channel count to be a multiple of kb)
+    // Patch walk (forward walk, unit stride, several taps): instead of one 128-row box per tap, the A
+    // producer loads ONE box per channel block that covers the tile's 8 x 16 output pixels plus the reach
+    // of every tap, and the MMA of tap (dh, dw) reads its 128 rows straight out of that patch: its
+    // descriptor starts (dh * patch_w + dw) rows in, and 8-row groups are patch_w rows apart.  (The swizzle
+    // is a function of the shared-memory address, so a descriptor may start on any 128-byte row.)
+    // A is then read from L2 about once instead of once per tap.  B slices stream through the stage ring,
+    // or stay resident in shared memory for the whole launch when all of them fit.
+    int patch;           // 1: patch walk
+    int patch_w, patch_h;    // patch extent in pixels
+    int patch_org_w, patch_org_h;  // smallest tap offset (the patch origin relative to the tile origin)
+    int patch_bytes;     // bytes one patch buffer occupies (multiple of 1024)
+    int a_stages;        // patch buffers
+    int b_resident;      // 1: every B slice of the launch is loaded once, at [pass plane][cb][tap] * bn * 128
+    int ring_bytes;      // bytes of the operand ring(s) in front of the staging buffers
+    int a_ring_off;      // patch walk: offset of the patch buffers within the ring region
     int kind;            // KIND_F16 / KIND_TF32
     int passes;          // 1, or 3 for the 3xTF32 split (hi*lo, lo*hi, hi*hi in that order)
     int kb;              // elements per 128-byte row (64 fp16, 32 tf32)
@@ -229,7 +245,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
     const int stage_b_bytes = (kPair ? P.bn / 2 : P.bn) * 128;   // one atom of B (a pair member holds half the columns)
     const int stage_bytes = P.ka * (kStageABytes + stage_b_bytes);  // [A atoms][B atoms]
     const int b_off = P.ka * kStageABytes;                        // first B atom within a stage
-    uint8_t* staging = smem + P.stages * stage_bytes;  // 4 epilogue warps x 4 KB
+    uint8_t* staging = smem + P.ring_bytes;  // epilogue warps x 4 KB
     const int staging_bytes = P.epi_warps * P.stg_bufs * kStagingBufBytes;
     float* bias_tile = reinterpret_cast<float*>(staging + staging_bytes);
     uint8_t* ctrl = staging + staging_bytes + kBiasTileBytes;
@@ -237,7 +253,10 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
     uint64_t* empty_bar = full_bar + 8;                               // [stages]
     uint64_t* tfull_bar = empty_bar + 8;                              // [2]
     uint64_t* tempty_bar = tfull_bar + 2;                             // [2]
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty_bar + 2);
+    uint64_t* afull_bar = tempty_bar + 2;                             // [4] patch walk: patch buffers
+    uint64_t* aempty_bar = afull_bar + 4;                             // [4]
+    uint64_t* bres_bar = aempty_bar + 4;                              // [1] patch walk: resident B has landed
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bres_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -247,13 +266,18 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.stages; ++s) {
-            mbar_init(smem_u32(&full_bar[s]), 2);  // one arrival (with its byte count) per producer warp
+            mbar_init(smem_u32(&full_bar[s]), P.patch ? 1 : 2);  // one arrival (with its byte count) per producer warp
             mbar_init(smem_u32(&empty_bar[s]), 1);
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(smem_u32(&tfull_bar[b]), 1);
             mbar_init(smem_u32(&tempty_bar[b]), (kPair ? 2 : 1) * P.epi_warps);  // the leader also hears the partner's epilogue warps
         }
+        for (int s = 0; s < 4; ++s) {
+            mbar_init(smem_u32(&afull_bar[s]), 1);
+            mbar_init(smem_u32(&aempty_bar[s]), 1);
+        }
+        mbar_init(smem_u32(bres_bar), 1);
         *abort_flag = 0;
         fence_mbar_init();
         tma_prefetch_desc(&P.tmA[0]);
@@ -281,6 +305,70 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
     const int box_bytes = P.kb * 128;  // one MN-major box: kb k-rows of 128 bytes
     const int wb = 1 << P.wb_log2, hb = 1 << P.hb_log2;
 
+    // Patch walk with resident B: the MMA issue loop of the tiles t_first, t_first + t_step, ... of this CTA.
+    // Nothing in it waits for B, so two warps can share the issuing: the MMA warp takes the even tiles
+    // (accumulator 0) and the B producer, idle once the weights have landed, the odd ones (accumulator 1).
+    // One warp's per-tile bookkeeping (barrier waits, commits) then hides behind the other's MMAs.
+    auto patch_resident_issue = [&](int t_first, int t_step) {
+        const Phase& ph = P.phases[0];
+        const uint32_t idesc = make_instr_desc(P.kind, 0, P.b_mn_major, kTileM, P.bn);
+        const bool b32 = P.b_mn_major && P.kind == KIND_TF32;
+        const uint32_t lbo_b = P.b_mn_major ? box_bytes : 16;
+        const uint32_t adv_b = P.b_mn_major ? (((P.kind == KIND_F16) ? 16 : 8) * 128) >> 4 : 2;
+        const uint32_t b_step = static_cast<uint32_t>(stage_b_bytes) >> 4;
+        const uint32_t sbo_a = static_cast<uint32_t>(P.patch_w) * 128u;  // 8-row groups are one patch row apart
+        const bool f16 = (P.kind == KIND_F16);
+        const Tap* tp = &P.taps[ph.tap_begin];
+        const int nt = ph.tap_count;
+        if (!mbar_wait(smem_u32(bres_bar), 0, abort_flag, P.err, ERR_WAIT_FULL)) return;
+        int titer = t_first;
+        for (int tile = tile_first + t_first * tile_step; tile < P.num_tiles; tile += t_step * tile_step, titer += t_step) {
+            const int buf = titer & 1;
+            const uint32_t tpar = (titer >> 1) & 1;
+            if (!mbar_wait(smem_u32(&tempty_bar[buf]), tpar ^ 1, abort_flag, P.err, ERR_WAIT_TMEM_EMPTY)) return;
+            tc_fence_after();
+            if (lane == 0) NML_STAMP(titer, 0);
+            const uint32_t d_tmem = tmem_base + buf * P.bn;
+            uint32_t acc = 0;
+            for (int cb = 0; cb < P.c_blocks; ++cb) {
+                const int pi = titer * P.c_blocks + cb;  // patches are consumed in tile order
+                const int pstage = pi % P.a_stages;
+                const uint32_t pparity = (pi / P.a_stages) & 1;
+                if (!mbar_wait(smem_u32(&afull_bar[pstage]), pparity, abort_flag, P.err, ERR_WAIT_FULL)) return;
+                tc_fence_after();
+                if (cb == 0 && lane == 0) NML_STAMP(titer, 1);
+                if (elect_one()) {
+                    const uint64_t adesc0 = make_smem_desc(smem_u32(smem + P.a_ring_off) + pstage * P.patch_bytes, 16, sbo_a, 2);
+                    uint64_t bdesc = make_smem_desc(smem_u32(smem) + cb * nt * stage_b_bytes, lbo_b, b32 ? 512 : 1024, b32 ? 1 : 2);
+#pragma unroll 1
+                    for (int t = 0; t < nt; ++t) {
+                        const uint64_t adesc = adesc0 + static_cast<uint32_t>(tp[t].aoff);
+                        if (f16) {
+                            umma_f16(d_tmem, adesc, bdesc, idesc, acc);
+                            umma_f16(d_tmem, adesc + 2, bdesc + adv_b, idesc, 1u);
+                            umma_f16(d_tmem, adesc + 4, bdesc + 2 * adv_b, idesc, 1u);
+                            umma_f16(d_tmem, adesc + 6, bdesc + 3 * adv_b, idesc, 1u);
+                        } else {
+                            umma_tf32(d_tmem, adesc, bdesc, idesc, acc);
+                            umma_tf32(d_tmem, adesc + 2, bdesc + adv_b, idesc, 1u);
+                            umma_tf32(d_tmem, adesc + 4, bdesc + 2 * adv_b, idesc, 1u);
+                            umma_tf32(d_tmem, adesc + 6, bdesc + 3 * adv_b, idesc, 1u);
+                        }
+                        acc = 1u;
+                        bdesc += b_step;
+                    }
+                    umma_commit(smem_u32(&aempty_bar[pstage]));
+                    if (cb + 1 == P.c_blocks) {
+                        NML_STAMP(titer, 2);
+                        umma_commit(smem_u32(&tfull_bar[buf]));
+                    }
+                }
+                acc = 1u;
+                __syncwarp();
+            }
+        }
+    };
+
     // ------------------------------------------------------------ producer --
     if (warp == 0 || warp == 6) {
         const bool do_a = (warp == 0), do_b = (warp == 6);
@@ -291,6 +379,109 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             int issued = 0;
             const uint32_t a_bytes = kStageABytes;
             const uint32_t tx_bytes = do_a ? a_bytes : stage_b_bytes;  // this producer's share of one atom
+            // B slice of (tap, channel block, column tile) -> shared memory at sb
+            auto load_b = [&](uint32_t sb, const CUtensorMap* tb, uint32_t fb, const Tap& tap, int cb, int ntile) {
+                if (!P.b_mn_major) {
+                    tma_load_2d(sb, tb, fb, tap.wk + cb * P.kb, ntile * P.bn);
+                } else if (P.b_grouped) {
+                    tma_load_3d(sb, tb, fb, 0, tap.wk + cb * P.kb, (ntile * P.bn) / P.kb);
+                } else {
+                    int nb = P.bn / P.kb;
+                    for (int j = 0; j < nb; ++j)
+                        tma_load_2d(sb + j * box_bytes, tb, fb, ntile * P.bn + j * P.kb, tap.wk + cb * P.kb);
+                }
+            };
+            if (kMode == MODE_FPROP && !kPair && P.patch) {
+                const Phase& ph = P.phases[0];
+                if (do_a) {
+                    const uint32_t a_base = smem_u32(smem + P.a_ring_off);
+                    const uint32_t patch_tx = static_cast<uint32_t>(P.patch_w) * P.patch_h * 128u;
+                    int abuf = 0;
+                    uint32_t apar = 0;
+                    for (int tile = tile_first; ok && tile < P.num_tiles; tile += tile_step) {
+                        const int m = tile / P.n_tiles;
+                        const int tw = m % ph.tiles_w;
+                        const int th = (m / ph.tiles_w) % ph.tiles_h;
+                        const int tn = m / (ph.tiles_w * ph.tiles_h);
+                        const int w0 = (tw << P.wb_log2) + P.patch_org_w;
+                        const int h0 = (th << P.hb_log2) + P.patch_org_h;
+                        for (int pass = 0; ok && pass < P.passes; ++pass) {
+                            const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
+                            for (int cb = 0; cb < P.c_blocks; ++cb) {
+                                if (!mbar_wait(smem_u32(&aempty_bar[abuf]), apar ^ 1, abort_flag, P.err, ERR_WAIT_EMPTY)) {
+                                    ok = false;
+                                    break;
+                                }
+                                const uint32_t fb = smem_u32(&afull_bar[abuf]);
+                                mbar_arrive_expect_tx(fb, patch_tx);
+                                tma_load_4d(a_base + abuf * P.patch_bytes, ta, fb, cb * P.kb, w0, h0, tn);
+                                ++issued;
+                                if (++abuf == P.a_stages) {
+                                    abuf = 0;
+                                    apar ^= 1;
+                                }
+                            }
+                        }
+                    }
+                    if (!ok) {  // give patches already requested a bounded chance to land
+                        int back = issued < P.a_stages ? issued : P.a_stages;
+                        for (int i = 0; i < back; ++i) {
+                            if (--abuf < 0) {
+                                abuf = P.a_stages - 1;
+                                apar ^= 1;
+                            }
+                            uint64_t t0 = globaltimer_ns();
+                            while (!mbar_try_wait(smem_u32(&afull_bar[abuf]), apar)) {
+                                if (globaltimer_ns() - t0 > 2000000ull) {
+                                    atomicCAS(P.err, 0, ERR_WAIT_DRAIN);
+                                    break;
+                                }
+                            }
+                        }
+                    }
+                    ok = true;   // nothing left for the common unwinding below
+                    issued = 0;
+                } else if (P.b_resident) {
+                    // every slice once, for the whole launch (one column tile, one pass plane)
+                    const uint32_t fb = smem_u32(bres_bar);
+                    mbar_arrive_expect_tx(fb, static_cast<uint32_t>(P.c_blocks) * ph.tap_count * stage_b_bytes);
+                    for (int cb = 0; cb < P.c_blocks; ++cb)
+                        for (int t = 0; t < ph.tap_count; ++t)
+                            load_b(smem_u32(smem) + (cb * ph.tap_count + t) * stage_b_bytes, &P.tmB[0], fb,
+                                   P.taps[ph.tap_begin + t], cb, 0);
+                    // the MMA warp waits for these before its first tile; if it gave up, wait here (bounded) so
+                    // that no copy is in flight when the CTA's shared memory goes away
+                    uint64_t t0 = globaltimer_ns();
+                    while (!mbar_try_wait(fb, 0)) {
+                        if (globaltimer_ns() - t0 > 4000000ull) {
+                            if (*abort_flag) atomicCAS(P.err, 0, ERR_WAIT_DRAIN);
+                            break;
+                        }
+                    }
+                } else {
+                    for (int tile = tile_first; ok && tile < P.num_tiles; tile += tile_step) {
+                        const int ntile = tile % P.n_tiles;
+                        for (int pass = 0; ok && pass < P.passes; ++pass) {
+                            const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
+                            for (int cb = 0; ok && cb < P.c_blocks; ++cb)
+                                for (int t = 0; t < ph.tap_count; ++t) {
+                                    if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err, ERR_WAIT_EMPTY)) {
+                                        ok = false;
+                                        break;
+                                    }
+                                    const uint32_t fb = smem_u32(&full_bar[stage]);
+                                    mbar_arrive_expect_tx(fb, stage_b_bytes);
+                                    load_b(smem_u32(smem) + stage * stage_b_bytes, tb, fb, P.taps[ph.tap_begin + t], cb, ntile);
+                                    ++issued;
+                                    if (++stage == P.stages) {
+                                        stage = 0;
+                                        parity ^= 1;
+                                    }
+                                }
+                        }
+                    }
+                }
+            } else
             for (int tile = tile_first; ok && tile < P.num_tiles; tile += tile_step) {
                 if (kMode == MODE_FPROP) {
                     int p = 0;
@@ -343,17 +534,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                             }
                         } else
                         if (do_a) tma_load_4d(sa, ta, fb, cb * P.kb, w0 + tap.dw, h0 + tap.dh, n0);
-                        if (kPair || !do_b) {
-                        } else if (!P.b_mn_major) {
-                            tma_load_2d(sb, tb, fb, tap.wk + cb * P.kb, ntile * P.bn);
-                        } else if (P.b_grouped) {
-                            tma_load_3d(sb, tb, fb, 0, tap.wk + cb * P.kb, (ntile * P.bn) / P.kb);
-                        } else {
-                            int nb = P.bn / P.kb;
-                            for (int j = 0; j < nb; ++j)
-                                tma_load_2d(sb + j * box_bytes, tb, fb, ntile * P.bn + j * P.kb,
-                                            tap.wk + cb * P.kb);
-                        }
+                        if (!kPair && do_b) load_b(sb, tb, fb, tap, cb, ntile);
                         if (++slot == n_in_stage) {
                             slot = 0;
                             ++issued;
@@ -482,6 +663,10 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 }
             }
         }
+        if (kMode == MODE_FPROP && !kPair && P.patch && P.b_resident && warp == 6) {
+            __syncwarp();
+            patch_resident_issue(1, 2);  // the weights are in: help with the odd tiles
+        }
     }
     // ---------------------------------------------------------- MMA issuer --
     else if (warp == 1) {
@@ -505,10 +690,13 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
         const uint32_t b_atom_step = static_cast<uint32_t>(stage_b_bytes) >> 4;
         const uint32_t stage_step = static_cast<uint32_t>(stage_bytes) >> 4;
         const bool f16 = (P.kind == KIND_F16);
-        int stage = 0;
-        uint32_t parity = 0;
+        int stage = 0, pstage = 0;
+        uint32_t parity = 0, pparity = 0;
         bool ok = true;
         int titer = 0;
+        if (kMode == MODE_FPROP && !kPair && P.patch && P.b_resident) {
+            patch_resident_issue(0, 2);
+        } else
         for (int tile = tile_first; ok && (!kPair || leader) && tile < P.num_tiles; tile += tile_step, ++titer) {
             int k_iters;
             if (kMode == MODE_FPROP) {
@@ -534,6 +722,56 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             if (lane == 0) NML_STAMP(titer, 0);
             const uint32_t d_tmem = tmem_base + buf * P.bn;
             uint32_t acc = 0;
+            if (kMode == MODE_FPROP && !kPair && P.patch) {
+                const Phase& ph = P.phases[0];
+                const uint32_t sbo_a = static_cast<uint32_t>(P.patch_w) * 128u;  // 8-row groups are one patch row apart
+                const uint64_t bdesc_ring0 = make_smem_desc(smem_u32(smem), lbo_b, b32 ? 512 : 1024, b32 ? 1 : 2);  // B ring starts the region
+                for (int pass = 0; ok && pass < P.passes; ++pass)
+                    for (int cb = 0; ok && cb < P.c_blocks; ++cb) {
+                        if (!mbar_wait(smem_u32(&afull_bar[pstage]), pparity, abort_flag, P.err, ERR_WAIT_FULL)) {
+                            ok = false;
+                            break;
+                        }
+                        tc_fence_after();
+                        if (pass == 0 && cb == 0 && lane == 0) NML_STAMP(titer, 1);
+                        const uint32_t patch_addr = smem_u32(smem + P.a_ring_off) + pstage * P.patch_bytes;
+                        const uint64_t adesc0 = make_smem_desc(patch_addr, 16, sbo_a, 2);
+                        for (int t = 0; t < ph.tap_count; ++t) {
+                            if (!mbar_wait(smem_u32(&full_bar[stage]), parity, abort_flag, P.err, ERR_WAIT_FULL)) {
+                                ok = false;
+                                break;
+                            }
+                            tc_fence_after();
+                            if (elect_one()) {
+                                const uint64_t adesc = adesc0 + static_cast<uint32_t>(P.taps[ph.tap_begin + t].aoff);
+                                const uint64_t bdesc = bdesc_ring0 + static_cast<uint64_t>(stage * b_atom_step);
+                                if (f16) {
+                                    umma_f16(d_tmem, adesc, bdesc, idesc, acc);
+                                    umma_f16(d_tmem, adesc + 2, bdesc + adv_b, idesc, 1u);
+                                    umma_f16(d_tmem, adesc + 4, bdesc + 2 * adv_b, idesc, 1u);
+                                    umma_f16(d_tmem, adesc + 6, bdesc + 3 * adv_b, idesc, 1u);
+                                } else {
+                                    umma_tf32(d_tmem, adesc, bdesc, idesc, acc);
+                                    umma_tf32(d_tmem, adesc + 2, bdesc + adv_b, idesc, 1u);
+                                    umma_tf32(d_tmem, adesc + 4, bdesc + 2 * adv_b, idesc, 1u);
+                                    umma_tf32(d_tmem, adesc + 6, bdesc + 3 * adv_b, idesc, 1u);
+                                }
+                                umma_commit(smem_u32(&empty_bar[stage]));
+                            }
+                            acc = 1u;
+                            if (++stage == P.stages) {
+                                stage = 0;
+                                parity ^= 1;
+                            }
+                        }
+                        if (!ok) break;
+                        if (elect_one()) umma_commit(smem_u32(&aempty_bar[pstage]));
+                        if (++pstage == P.a_stages) {
+                            pstage = 0;
+                            pparity ^= 1;
+                        }
+                    }
+            } else
             for (int it = 0; it < k_iters; it += P.ka) {
                 const int n_atoms = min(P.ka, k_iters - it);
 #ifdef NML_TRACE
