@@ -32,12 +32,25 @@ sys.path.insert(0, ROOT)
 LINEAR_SWEEP = [(rows, d) for d in (512, 1024, 2048) for rows in (4096, 16384)]
 # ResNet-style conv shapes at batch 256 (7x7 s2 p3 3->64 @224 is left to the parity tests until
 # its small-channel path exists): (c_in, hw, c_out, k, stride, pad)
-RESNET_SWEEP = [(64, 56, 64, 3, 1, 1), (256, 56, 64, 1, 1, 0), (128, 28, 128, 3, 2, 1), (1024, 14, 2048, 1, 2, 0)]
+# (c_in, input h = w, c_out, kernel, stride, padding, transposed)
+RESNET_SWEEP = [(3, 224, 64, 7, 2, 3, False), (64, 56, 64, 3, 1, 1, False), (256, 56, 64, 1, 1, 0, False),
+                (128, 28, 128, 3, 2, 1, False), (1024, 14, 2048, 1, 2, 0, False)]
 RESNET_BATCH = 256
+# the 16 convolutions of the Pix2Pix U-Net generator (4x4, stride 2, padding 1; decoder inputs carry the skip concat)
+PIX2PIX_SWEEP = ([(ci, hw, co, 4, 2, 1, False) for ci, hw, co in
+                  ((3, 256, 64), (64, 128, 128), (128, 64, 256), (256, 32, 512), (512, 16, 512), (512, 8, 512),
+                   (512, 4, 512), (512, 2, 512))] +
+                 [(ci, hw, co, 4, 2, 1, True) for ci, hw, co in
+                  ((512, 1, 512), (1024, 2, 512), (1024, 4, 512), (1024, 8, 512), (1024, 16, 256), (512, 32, 128),
+                   (256, 64, 64), (128, 128, 3))])
+PIX2PIX_BATCH = 64
 LINEAR_NAME = ("Linear sweep X[B*T,d]@W^T[d,4d]+b, d in {512,1024,2048} x B*T in {4096,16384}, "
                "forward+dgrad+wgrad+db, fp16 storage / fp32 accumulate")
-RESNET_NAME = ("ResNet-style conv shapes, batch 256 per GPU, NHWC fp16: 3x3 64->64 @56, 1x1 256->64 @56, "
+RESNET_NAME = ("ResNet-style conv shapes, batch 256 per GPU, NHWC fp16: 7x7 s2 3->64 @224, 3x3 64->64 @56, 1x1 256->64 @56, "
                "3x3 s2 128->128 @28, 1x1 s2 1024->2048 @14; forward+dgrad+wgrad+db")
+PIX2PIX_NAME = ("Pix2Pix U-Net generator convolutions, batch 64 per GPU, NHWC fp16: 8 Conv2d 4x4 s2 p1 "
+                "(3-64-128-256-512-512-512-512-512) + 8 ConvTranspose2d 4x4 s2 p1 with skip-concat inputs; "
+                "forward+dgrad+wgrad+db of every layer (normalisation and activations not included)")
 
 
 def measured_peaks():
@@ -110,8 +123,8 @@ def linear_flops(rows, d):
     return 3 * 2.0 * rows * d * 4 * d  # forward + dgrad + wgrad
 
 
-def conv_flops(batch, c_in, hw, c_out, k, s, p):
-    ho = (hw + 2 * p - k) // s + 1
+def conv_flops(batch, c_in, hw, c_out, k, s, p, transposed=False):
+    ho = hw if transposed else (hw + 2 * p - k) // s + 1  # a transposed layer does its multiplies per INPUT pixel
     return 3 * 2.0 * batch * ho * ho * c_out * c_in * k * k
 
 
@@ -227,21 +240,22 @@ def run_gpu(args):
         workload = {"workload": LINEAR_NAME,
                     "layers": len(layers), "rows_per_gpu": sum(l["rows"] for l in layers)}
     else:
-        rng = np.random.default_rng(1237 + rank)
+        torch.manual_seed(1237 + rank)
+        sweep, batch = (RESNET_SWEEP, RESNET_BATCH) if args.workload == "resnet" else (PIX2PIX_SWEEP, PIX2PIX_BATCH)
         layers = []
-        for (ci, hw, co, k, s, p) in RESNET_SWEEP:
-            g = ConvGeometry(RESNET_BATCH, ci, hw, hw, co, k, k, (s, s), (p, p))
+        for (ci, hw, co, k, s, p, tr) in sweep:
+            g = ConvGeometry(batch, ci, hw, hw, co, k, k, (s, s), (p, p), transposed=tr)
             ho, wo = g.out_hw()
-            std = np.sqrt(2.0 / (ci * k * k))
+            std = np.sqrt(2.0 / (ci * k * k)) if args.workload == "resnet" else 0.02
             layers.append({
-                "g": g,
-                "xd": torch.randn(RESNET_BATCH, hw, hw, ci, device=dev).half(),
-                "dyd": torch.randn(RESNET_BATCH, ho, wo, co, device=dev).half(),
-                "wd": (torch.randn(co, ci, k, k, device=dev) * std).half(),
-                "y": torch.empty(RESNET_BATCH, ho, wo, co, dtype=torch.float16, device=dev),
-                "dx": torch.empty(RESNET_BATCH, hw, hw, ci, dtype=torch.float16, device=dev),
+                "g": g, "name": f"{'convT' if tr else 'conv'} {k}x{k} s{s} {ci}->{co} @{hw}",
+                "xd": torch.randn(batch, hw, hw, ci, device=dev).half(),
+                "dyd": torch.randn(batch, ho, wo, co, device=dev).half(),
+                "wd": (torch.randn(*g.weight_shape(), device=dev) * std).half(),
+                "y": torch.empty(batch, ho, wo, co, dtype=torch.float16, device=dev),
+                "dx": torch.empty(batch, hw, hw, ci, dtype=torch.float16, device=dev),
             })
-            flops_per_launch += [conv_flops(RESNET_BATCH, ci, hw, co, k, s, p) / 3] * 3
+            flops_per_launch += [conv_flops(batch, ci, hw, co, k, s, p, tr) / 3] * 3
         step_flops = sum(flops_per_launch)
         bytes_resident = sum(t.numel() * t.element_size() for l in layers for t in (l["xd"], l["dyd"], l["y"], l["dx"]))
         grads = {}
@@ -259,7 +273,7 @@ def run_gpu(args):
                 p.wait()
 
         h2d = d2h = 0
-        workload = {"workload": RESNET_NAME,
+        workload = {"workload": RESNET_NAME if args.workload == "resnet" else PIX2PIX_NAME,
                     "layers": len(layers)}
 
     def barrier():
@@ -305,6 +319,13 @@ def run_gpu(args):
         step()
     per_launch_ms = ops.profile_end(n_rec)
     kern_ms = sum(per_launch_ms)
+    per_layer = None
+    if args.per_layer and per_launch_ms:
+        n1 = len(flops_per_launch)
+        mean = [sum(per_launch_ms[i::n1]) / len(per_launch_ms[i::n1]) for i in range(n1)]
+        names = [l["name"] if "name" in l else f"linear {l['rows']}x{l['d']}->{4 * l['d']}" for l in layers]
+        per_layer = [{"layer": names[i // 3], "pass": ("fwd", "dgrad", "wgrad")[i % 3], "us": round(mean[i] * 1e3, 1),
+                      "tflops": round(flops_per_launch[i] / (mean[i] * 1e-3) / 1e12, 1)} for i in range(n1)]
     kern_flops = sum(flops_per_launch) * (len(per_launch_ms) / max(len(flops_per_launch), 1))
     achieved = kern_flops / (kern_ms * 1e-3) / 1e12 if kern_ms > 0 else None
 
@@ -338,6 +359,8 @@ def run_gpu(args):
                          "kernel": "umma_conv_kernel", "launches_timed": len(per_launch_ms),
                          "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(args.workload)},
         }
+        if per_layer:
+            out["per_layer"] = per_layer
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(args.workload, budget_s=12.0)
         print(json.dumps(out), flush=True)
@@ -379,7 +402,7 @@ def cpu_linear_sample(budget_s: float):
 def cpu_conv_sample(budget_s: float):
     from oracle import nectar_oracle as orc
     rng = np.random.default_rng(1237)
-    ci, hw, co, k, s, p = RESNET_SWEEP[0]
+    ci, hw, co, k, s, p, _ = RESNET_SWEEP[1]
     x = rng.standard_normal((1, ci, hw, hw), dtype=np.float32)
     w = rng.standard_normal((co, ci, k, k), dtype=np.float32)
     dy = rng.standard_normal((1, co, hw, hw), dtype=np.float32)
@@ -432,7 +455,7 @@ def run_reference(args):
     value = flops / secs / 1e12
     base = {k: base[k] for k in ("unit", "cores", "kind", "sample")}
     base["value"] = value
-    name = LINEAR_NAME if args.workload == "linear" else RESNET_NAME
+    name = {"linear": LINEAR_NAME, "resnet": RESNET_NAME, "pix2pix": PIX2PIX_NAME}[args.workload]
     print(json.dumps({
         "metric": "conv/linear fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": warm, "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
@@ -450,7 +473,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="nectarml_b200", choices=["nectarml_b200", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "resnet"])
+    ap.add_argument("--workload", default="linear", choices=["linear", "resnet", "pix2pix"])
+    ap.add_argument("--per-layer", action="store_true",
+                    help="add the contraction kernel's mean time per layer and pass to the JSON line")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=0.0,
                     help="seconds of CPU work per step of the reference arm (default: sized from --steps)")

@@ -108,6 +108,44 @@ def test_native_fp16_nhwc(name, oracle):
     assert_f32(host(db), db_o, f"{name} db", tol=2e-5)
 
 
+# Unit-stride multi-tap layers whose weights fit in shared memory take the patch walk (one haloed box
+# per channel block, resident weights, two issuing warps); these shapes span several tiles in both
+# image directions, ragged edges, two channel blocks, dilation and a transposed (gather) layer.
+PATCH_SHAPES = {
+    "p_3x3_64_96":   (False, (2, 64, 40, 27, 96, 3, 3, (1, 1), (1, 1), (1, 1), (0, 0)), True, "normal"),
+    "p_3x3_128_32":  (False, (1, 128, 33, 50, 32, 3, 3, (1, 1), (1, 1), (1, 1), (0, 0)), True, "normal"),
+    "p_5x5_dil":     (False, (2, 16, 37, 21, 24, 5, 5, (1, 1), (4, 4), (2, 2), (0, 0)), False, "normal"),
+    "p_rect_nopad":  (False, (3, 40, 19, 45, 64, 2, 4, (1, 1), (0, 0), (1, 1), (0, 0)), True, "normal"),
+    "p_t_3x3_s1":    (True,  (2, 48, 18, 29, 40, 3, 3, (1, 1), (1, 1), (1, 1), (0, 0)), True, "normal"),
+}
+
+
+@pytest.mark.parametrize("name", sorted(PATCH_SHAPES))
+def test_patch_walk_shapes(name, oracle):
+    case = PATCH_SHAPES[name]
+    g = geometry(case)
+    x, w, b, dy = cases.draw_conv(name, case)
+    r = oracle.round_f16
+    y_o, dx_o, dw_o, db_o = oracle_all(oracle, case, r(x), r(w), r(b) if b is not None else None, r(dy))
+    xd, dyd = dev(x, torch.float16, nhwc=True), dev(dy, torch.float16, nhwc=True)
+    wd = dev(w, torch.float16)
+    bd = dev(b, torch.float16) if b is not None else None
+    y = ops.conv_forward(g, xd, wd, bd, layout="nhwc", math="f16")
+    dx = ops.conv_backward_data(g, dyd, wd, layout="nhwc", math="f16")
+    ops.device_status()
+    assert_f16(host(y, nhwc=True), y_o, f"{name} y")
+    assert_f16(host(dx, nhwc=True), dx_o, f"{name} dx")
+    # the same layer in fp32 (3xTF32: patches per pass, weights streamed)
+    y32_o, dx32_o, _, _ = oracle_all(oracle, case, x, w, b, dy)
+    xd32, wd32, dyd32 = dev(x), dev(w), dev(dy)
+    bd32 = dev(b) if b is not None else None
+    y32 = shim_forward(case, xd32, wd32, bd32, F32, False)
+    dx32, _ = shim_backward(case, dyd32, xd32, wd32, F32)
+    ops.device_status()
+    assert_f32(y32, y32_o, f"{name} y fp32")
+    assert_f32(dx32, dx32_o, f"{name} dx fp32")
+
+
 def test_config1_full_size(golden_config1, oracle):
     """BASELINE config 1: Conv2d fp32 N=8 64->64 56x56 3x3 s1 p1, output, dX, dW and db."""
     case = cases.CONFIG1
