@@ -360,8 +360,7 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
         // [B: resident slices, or a ring of single-slice stages][patch buffers][staging][bias][barriers]
         P.ka = 1;
         const int b_slice = P.bn * 128;
-        const int taps = P.phases[0].tap_count;
-        const int res_bytes = P.c_blocks * taps * b_slice;
+        const int res_bytes = P.c_blocks * P.n_taps * b_slice;  // the taps of every phase
         P.stg_bufs = 2;
         int avail = 232448 - fixed - P.epi_warps * P.stg_bufs * kStagingBufBytes;
         const bool res_wanted = P.n_tiles == 1 && P.passes == 1 && tune_env("NML_TUNE_BRES", 1);
@@ -635,40 +634,59 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     choose_box(7, P.phases[0].wq, P.phases[0].hq, f.batch, esw, esh, &P.wb_log2, &P.hb_log2, &P.nb_log2,
                (P.out_mode == OUT_NCHW && !f.gather) ? 5 : 0);
     bool patch_resident = false;
-    // Patch walk: unit-stride problems with several taps load one haloed patch per channel block instead of
+    // Patch walk: unit-stride walks with several taps load one haloed patch per channel block instead of
     // one box per tap (8 x 16 pixel tiles of a single image).  Taken when the fixed tile shape does not
-    // waste much more of the tile than the free-form box does.
+    // waste much more of the tile than the free-form box does.  Every phase of a gather walk has its own
+    // taps and patch origin; the box is sized for the widest phase.
     {
         const int mode = tune_env("NML_TUNE_PATCH", 1);
-        int dw_min = 0, dw_max = 0, dh_min = 0, dh_max = 0;
-        for (int t = 0; t < n_taps; ++t) {
-            dw_min = t ? std::min<int>(dw_min, P.taps[t].dw) : P.taps[t].dw;
-            dw_max = t ? std::max<int>(dw_max, P.taps[t].dw) : P.taps[t].dw;
-            dh_min = t ? std::min<int>(dh_min, P.taps[t].dh) : P.taps[t].dh;
-            dh_max = t ? std::max<int>(dh_max, P.taps[t].dh) : P.taps[t].dh;
+        int range_w = 0, range_h = 0;
+        bool every_phase_has_taps = true;
+        for (int p = 0; p < n_phases; ++p) {
+            Phase& ph = P.phases[p];
+            if (ph.tap_count == 0) {
+                every_phase_has_taps = false;
+                continue;
+            }
+            int dw_min = 0, dw_max = 0, dh_min = 0, dh_max = 0;
+            for (int t = 0; t < ph.tap_count; ++t) {
+                const Tap& tp = P.taps[ph.tap_begin + t];
+                dw_min = t ? std::min<int>(dw_min, tp.dw) : tp.dw;
+                dw_max = t ? std::max<int>(dw_max, tp.dw) : tp.dw;
+                dh_min = t ? std::min<int>(dh_min, tp.dh) : tp.dh;
+                dh_max = t ? std::max<int>(dh_max, tp.dh) : tp.dh;
+            }
+            ph.org_w = static_cast<short>(dw_min);
+            ph.org_h = static_cast<short>(dh_min);
+            range_w = std::max(range_w, dw_max - dw_min);
+            range_h = std::max(range_h, dh_max - dh_min);
         }
-        const int pw_ = 8 + dw_max - dw_min, ph_ = 16 + dh_max - dh_min;
+        const int pw_ = 8 + range_w, ph_ = 16 + range_h;
         const int wq = P.phases[0].wq, hq = P.phases[0].hq;
         const double eff_patch = static_cast<double>(wq) * hq / (1.0 * round_up(wq, 8) * round_up(hq, 16));
         const double eff_box = static_cast<double>(wq) * hq * f.batch /
                                (1.0 * round_up(wq, 1 << P.wb_log2) * round_up(hq, 1 << P.hb_log2) * round_up(f.batch, 1 << P.nb_log2));
-        const bool can = !window && n_phases == 1 && n_taps >= 2 && esw == 1 && esh == 1 && P.out_stride_w == 1 &&
-                         P.out_stride_h == 1 && pw_ <= 256 && ph_ <= 256 && pw_ * ph_ * 128 <= 48 * 1024;
+        const bool can = !window && every_phase_has_taps && n_taps >= 2 && esw == 1 && esh == 1 && pw_ <= 256 && ph_ <= 256 &&
+                         pw_ * ph_ * 128 <= 48 * 1024;
         // B stays resident when every slice fits beside two patch buffers and the smallest epilogue staging;
         // streaming B tap by tap pays only for the 3xTF32 split (a barrier round trip per 4 short MMAs otherwise)
-        const long long res_need = 1ll * c_blocks * n_taps * round_up(N, 32) * 128 + 2 * round_up(pw_ * ph_ * 128, 1024);
+        const int bn_res = (N <= 16 && !b_mn_major) ? 16 : static_cast<int>(round_up(N, 32));
+        const long long res_need = 1ll * c_blocks * n_taps * bn_res * 128 + 2 * round_up(pw_ * ph_ * 128, 1024);
         const bool res_ok = P.passes == 1 && N <= 256 &&
                             res_need <= 232448 - (1024 + 256 + kBiasTileBytes) - 4 * kStagingBufBytes;
-        patch_resident = res_ok;
-        if (can && mode && (mode == 2 || (eff_patch >= 0.8 * eff_box && (res_ok || (P.passes == 3 && N <= 128))))) {
+        const bool streamed_ok = n_phases == 1 && P.passes == 3 && N <= 128;
+        if (can && mode && ((mode == 2 && (res_ok || n_phases == 1)) || (eff_patch >= 0.8 * eff_box && (res_ok || streamed_ok)))) {
+            patch_resident = res_ok;
             P.patch = 1;
             P.patch_w = pw_;
             P.patch_h = ph_;
-            P.patch_org_w = dw_min;
-            P.patch_org_h = dh_min;
             P.patch_bytes = static_cast<int>(round_up(pw_ * ph_ * 128, 1024));
-            for (int t = 0; t < n_taps; ++t)
-                P.taps[t].aoff = ((P.taps[t].dh - dh_min) * pw_ + (P.taps[t].dw - dw_min)) * 128 / 16;
+            for (int p = 0; p < n_phases; ++p)
+                for (int t = 0; t < P.phases[p].tap_count; ++t) {
+                    Tap& tp = P.taps[P.phases[p].tap_begin + t];
+                    tp.aoff = ((tp.dh - P.phases[p].org_h) * pw_ + (tp.dw - P.phases[p].org_w)) * 128 / 16;
+                }
+            P.n_taps = n_taps;
             P.wb_log2 = 3;
             P.hb_log2 = 4;
             P.nb_log2 = 0;
@@ -682,14 +700,15 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         for (int p = 0; p < n_phases; ++p)
             m_tiles_all += 1ll * ceil_div(P.phases[p].wq, 1 << P.wb_log2) * ceil_div(P.phases[p].hq, 1 << P.hb_log2) *
                            ceil_div(f.batch, 1 << P.nb_log2);
-        const int forced = (P.patch && patch_resident) ? static_cast<int>(round_up(N, 32)) : tune_env("NML_TUNE_BN", 0);
+        const int forced = (P.patch && patch_resident) ? ((N <= 16 && !b_mn_major) ? 16 : static_cast<int>(round_up(N, 32)))
+                                                       : tune_env("NML_TUNE_BN", 0);
         const int cand[4] = {256, 128, 64, forced};
         const double cost[3] = {1.0, 1.28, 2.24};
         double best = -1;
         for (int i = 0; i < 4; ++i) {
             if (forced ? i != 3 : i == 3) continue;
             int nt = ceil_div(N, cand[i]);
-            int bn = static_cast<int>(round_up(ceil_div(N, nt), b_mn_major ? 64 : 32));
+            int bn = static_cast<int>(round_up(ceil_div(N, nt), b_mn_major ? 64 : (forced == 16 ? 16 : 32)));
             if (bn > 256) continue;
             double rounds = static_cast<double>(ceil_div(static_cast<int>(std::min<long long>(m_tiles_all * nt, 1 << 30)), ds->sms));
             double t = rounds * bn * (bn > 128 ? cost[0] : bn > 64 ? cost[1] : cost[2]);

@@ -60,6 +60,7 @@ struct Tap {
 struct Phase {
     short ph, pw;        // first output row / column of the phase
     short tap_begin, tap_count;
+    short org_h, org_w;  // patch walk: smallest tap offset of the phase (its patch origin relative to the tile origin)
     int hq, wq;          // extent of the phase grid
     int tiles_h, tiles_w;
     int tile_begin;      // first tile id of this phase
@@ -92,7 +93,6 @@ struct KParams {
     // or stay resident in shared memory for the whole launch when all of them fit.
     int patch;           // 1: patch walk
     int patch_w, patch_h;    // patch extent in pixels
-    int patch_org_w, patch_org_h;  // smallest tap offset (the patch origin relative to the tile origin)
     int patch_bytes;     // bytes one patch buffer occupies (multiple of 1024)
     int a_stages;        // patch buffers
     int b_resident;      // 1: every B slice of the launch is loaded once, at [pass plane][cb][tap] * bn * 128
@@ -261,8 +261,10 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const uint32_t tmem_cols = (2 * P.bn <= 32) ? 32 : (2 * P.bn <= 64) ? 64 : (2 * P.bn <= 128) ? 128
-                               : (2 * P.bn <= 256) ? 256 : 512;
+    // two accumulators; the epilogue reads 32 columns at a time, so a 16-column tile still needs 16 + 32
+    const uint32_t tmem_need = (P.bn < 32) ? P.bn + 32 : 2 * P.bn;
+    const uint32_t tmem_cols = (tmem_need <= 32) ? 32 : (tmem_need <= 64) ? 64 : (tmem_need <= 128) ? 128
+                               : (tmem_need <= 256) ? 256 : 512;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < P.stages; ++s) {
@@ -310,7 +312,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
     // (accumulator 0) and the B producer, idle once the weights have landed, the odd ones (accumulator 1).
     // One warp's per-tile bookkeeping (barrier waits, commits) then hides behind the other's MMAs.
     auto patch_resident_issue = [&](int t_first, int t_step) {
-        const Phase& ph = P.phases[0];
         const uint32_t idesc = make_instr_desc(P.kind, 0, P.b_mn_major, kTileM, P.bn);
         const bool b32 = P.b_mn_major && P.kind == KIND_TF32;
         const uint32_t lbo_b = P.b_mn_major ? box_bytes : 16;
@@ -318,11 +319,14 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
         const uint32_t b_step = static_cast<uint32_t>(stage_b_bytes) >> 4;
         const uint32_t sbo_a = static_cast<uint32_t>(P.patch_w) * 128u;  // 8-row groups are one patch row apart
         const bool f16 = (P.kind == KIND_F16);
-        const Tap* tp = &P.taps[ph.tap_begin];
-        const int nt = ph.tap_count;
         if (!mbar_wait(smem_u32(bres_bar), 0, abort_flag, P.err, ERR_WAIT_FULL)) return;
         int titer = t_first;
+        int p = 0;
         for (int tile = tile_first + t_first * tile_step; tile < P.num_tiles; tile += t_step * tile_step, titer += t_step) {
+            while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
+            const Tap* tp = &P.taps[P.phases[p].tap_begin];
+            const int nt = P.phases[p].tap_count;
+            const int tb0 = P.phases[p].tap_begin;
             const int buf = titer & 1;
             const uint32_t tpar = (titer >> 1) & 1;
             if (!mbar_wait(smem_u32(&tempty_bar[buf]), tpar ^ 1, abort_flag, P.err, ERR_WAIT_TMEM_EMPTY)) return;
@@ -339,7 +343,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 if (cb == 0 && lane == 0) NML_STAMP(titer, 1);
                 if (elect_one()) {
                     const uint64_t adesc0 = make_smem_desc(smem_u32(smem + P.a_ring_off) + pstage * P.patch_bytes, 16, sbo_a, 2);
-                    uint64_t bdesc = make_smem_desc(smem_u32(smem) + cb * nt * stage_b_bytes, lbo_b, b32 ? 512 : 1024, b32 ? 1 : 2);
+                    uint64_t bdesc = make_smem_desc(smem_u32(smem) + (cb * P.n_taps + tb0) * stage_b_bytes, lbo_b, b32 ? 512 : 1024, b32 ? 1 : 2);
 #pragma unroll 1
                     for (int t = 0; t < nt; ++t) {
                         const uint64_t adesc = adesc0 + static_cast<uint32_t>(tp[t].aoff);
@@ -398,13 +402,16 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     const uint32_t patch_tx = static_cast<uint32_t>(P.patch_w) * P.patch_h * 128u;
                     int abuf = 0;
                     uint32_t apar = 0;
+                    int p = 0;
                     for (int tile = tile_first; ok && tile < P.num_tiles; tile += tile_step) {
-                        const int m = tile / P.n_tiles;
-                        const int tw = m % ph.tiles_w;
-                        const int th = (m / ph.tiles_w) % ph.tiles_h;
-                        const int tn = m / (ph.tiles_w * ph.tiles_h);
-                        const int w0 = (tw << P.wb_log2) + P.patch_org_w;
-                        const int h0 = (th << P.hb_log2) + P.patch_org_h;
+                        while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
+                        const Phase& pt = P.phases[p];
+                        const int m = (tile - pt.tile_begin) / P.n_tiles;
+                        const int tw = m % pt.tiles_w;
+                        const int th = (m / pt.tiles_w) % pt.tiles_h;
+                        const int tn = m / (pt.tiles_w * pt.tiles_h);
+                        const int w0 = (tw << P.wb_log2) + pt.org_w;
+                        const int h0 = (th << P.hb_log2) + pt.org_h;
                         for (int pass = 0; ok && pass < P.passes; ++pass) {
                             const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
                             for (int cb = 0; cb < P.c_blocks; ++cb) {
@@ -413,8 +420,10 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                                     break;
                                 }
                                 const uint32_t fb = smem_u32(&afull_bar[abuf]);
+                                if (pass == 0 && cb == 0) NML_STAMP((tile - tile_first) / tile_step, 5);
                                 mbar_arrive_expect_tx(fb, patch_tx);
                                 tma_load_4d(a_base + abuf * P.patch_bytes, ta, fb, cb * P.kb, w0, h0, tn);
+                                if (pass == 0 && cb == 0) NML_STAMP((tile - tile_first) / tile_step, 6);
                                 ++issued;
                                 if (++abuf == P.a_stages) {
                                     abuf = 0;
@@ -444,11 +453,10 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 } else if (P.b_resident) {
                     // every slice once, for the whole launch (one column tile, one pass plane)
                     const uint32_t fb = smem_u32(bres_bar);
-                    mbar_arrive_expect_tx(fb, static_cast<uint32_t>(P.c_blocks) * ph.tap_count * stage_b_bytes);
+                    mbar_arrive_expect_tx(fb, static_cast<uint32_t>(P.c_blocks) * P.n_taps * stage_b_bytes);
                     for (int cb = 0; cb < P.c_blocks; ++cb)
-                        for (int t = 0; t < ph.tap_count; ++t)
-                            load_b(smem_u32(smem) + (cb * ph.tap_count + t) * stage_b_bytes, &P.tmB[0], fb,
-                                   P.taps[ph.tap_begin + t], cb, 0);
+                        for (int t = 0; t < P.n_taps; ++t)  // the taps of every phase
+                            load_b(smem_u32(smem) + (cb * P.n_taps + t) * stage_b_bytes, &P.tmB[0], fb, P.taps[t], cb, 0);
                     // the MMA warp waits for these before its first tile; if it gave up, wait here (bounded) so
                     // that no copy is in flight when the CTA's shared memory goes away
                     uint64_t t0 = globaltimer_ns();
@@ -1065,6 +1073,31 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     }
                     ++store_seq;
                     if (more) tmem_ld_wait();
+                }
+            } else
+            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC && P.c_out <= 8) {
+                // A handful of output channels (image-producing layers, input gradients of stems): each
+                // thread stores its pixel's few values.  Kept short on purpose -- the epilogue warps are
+                // bound by instruction fetch, not by the stores.
+                uint32_t r[8];
+                if (k_iters > 0) {
+                    tmem_ld_32x8(t_row, r);
+                    tmem_ld_wait();
+                }
+                if (row_valid) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        if (j < P.c_out) {
+                            float xv = (k_iters > 0) ? __uint_as_float(r[j]) : 0.f;
+                            if (P.bias != nullptr) xv += __ldg(P.bias + j);
+                            if (kOutF16) {
+                                reinterpret_cast<__half*>(P.out)[row_off + j] = __float2half_rn(xv);
+                            } else {
+                                if (P.round_f16) xv = round_through_f16(xv);
+                                reinterpret_cast<float*>(P.out)[row_off + j] = xv;
+                            }
+                        }
+                    }
                 }
             } else
             if (kMode == MODE_FPROP && kOutMode == OUT_NHWC) {
