@@ -242,6 +242,8 @@ def run_gpu(args):
     else:
         torch.manual_seed(1237 + rank)
         sweep, batch = (RESNET_SWEEP, RESNET_BATCH) if args.workload == "resnet" else (PIX2PIX_SWEEP, PIX2PIX_BATCH)
+        if args.only:  # profiling aid: one layer of the sweep by index, e.g. --workload resnet --only 1
+            sweep = [sweep[int(args.only)]]
         layers = []
         for (ci, hw, co, k, s, p, tr) in sweep:
             g = ConvGeometry(batch, ci, hw, hw, co, k, k, (s, s), (p, p), transposed=tr)
@@ -372,7 +374,7 @@ def run_gpu(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per contraction launch, averaged over one step of the
 # workload, from the ncu capture summarised under profiles/ (None until a capture exists).
-TRAFFIC_BYTES_PER_LAUNCH = {"linear": 196.0e6, "resnet": None}
+TRAFFIC_BYTES_PER_LAUNCH = {"linear": 166.2e6, "resnet": None, "pix2pix": None}
 
 
 # ------------------------------------------------------------ CPU reference arm --
@@ -479,7 +481,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=0.0,
                     help="seconds of CPU work per step of the reference arm (default: sized from --steps)")
-    ap.add_argument("--only", default="", help="linear workload: restrict the sweep to ROWSxD (for profiling captures)")
+    ap.add_argument("--only", default="", help="profiling aid: restrict the linear sweep to ROWSxD, or a conv sweep to the layer with this index")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
