@@ -1,5 +1,5 @@
 // The one contraction kernel of this library: a persistent, warp-specialised
-// implicit-GEMM for sm_100a.  One CTA per SM walks a static list of output tiles.
+// implicit-GEMM for sm_100a.  One CTA per SM (or one cluster of two) walks a static list of output tiles.
 //
 //   warps 0, 6  TMA producers  : tiled cp.async.bulk.tensor loads (never multicast) into a ring of
 //                                128-byte-swizzled shared-memory stages; warp 0 fetches the A
@@ -7,7 +7,8 @@
 //                                few hundred clocks, so one thread cannot feed narrow tiles)
 //   warp 1      MMA issuer     : one thread issues tcgen05.mma, accumulators live in TMEM,
 //                                two TMEM buffers so the epilogue of tile i overlaps tile i+1
-//   warps 2..5  epilogue       : tcgen05.ld -> bias / rounding / cast -> global stores
+//   warps 2..5  epilogue       : tcgen05.ld -> bias / rounding / cast -> TMA or plain global stores
+//   warps 7..10 epilogue       : second group, TMA-store instances only, used on short-K tiles
 //
 // Two tile walks share the pipeline:
 //   MODE_FPROP  rows of the tile are output pixels (n, h, w) taken as one TMA box of the
@@ -16,11 +17,13 @@
 //               zero-filled by TMA).  Covers Conv2d forward, Conv2d input-gradient and
 //               ConvTranspose2d forward (one sub-problem per output phase, no col2im),
 //               ConvTranspose2d input-gradient, and plain GEMMs (Linear forward / dgrad)
-//               seen as a 1x1 convolution over an image of height 1.
+//               seen as a 1x1 convolution over an image of height 1.  Unit-stride walks with
+//               several taps use the patch walk instead (see KParams::patch).
 //   MODE_WGRAD  rows of the tile are (tap, patch channel), columns are the other tensor's
 //               channels, the K loop runs over pixels; both operands are MN-major boxes of the
 //               NHWC tensors.  Partial sums of the split-K slices are added with fp32 atomics.
 //               Covers Conv2d / ConvTranspose2d weight-gradient and Linear weight-gradient.
+// 256-wide tiles of long-K problems run as CTA pairs (cta_group::2, see the kernel's comment).
 #pragma once
 #include "nml_ptx.cuh"
 
