@@ -278,7 +278,7 @@ struct WindowImage {
 };
 static bool window_eligible(int c, int kw, int d_w, int enc) { return c <= 8 && kw <= 8 && d_w == 1 && enc == ENC_F16; }
 static int prepare_window(const void* src, int dtype, int layout, int batch, int c, int h, int w, int p_h, int p_w,
-                          int s_w, int out_w, Bump& ws, cudaStream_t st, WindowImage* img) {
+                          int s_w, int out_w, Bump& ws, cudaStream_t st, WindowImage* img, float* colsum = nullptr) {
     img->hp = h + 2 * p_h;
     img->wp = std::max(w + 2 * p_w, (out_w - 1) * s_w + 8);
     const size_t pixels = static_cast<size_t>(batch) * img->hp * img->wp;
@@ -289,9 +289,9 @@ static int prepare_window(const void* src, int dtype, int layout, int batch, int
     int blocks = static_cast<int>(std::min<size_t>((pixels + 255) / 256, 148 * 32));
     const int nchw = (layout == NML_NCHW) ? 1 : 0;
     if (dtype == NML_F32)
-        { pad_pack_c8_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(src), nchw, static_cast<__half*>(p), batch, c, h, w, p_h, p_w, img->hp, img->wp); ++g_launches; }
+        { pad_pack_c8_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(src), nchw, static_cast<__half*>(p), batch, c, h, w, p_h, p_w, img->hp, img->wp, colsum); ++g_launches; }
     else
-        { pad_pack_c8_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(src), nchw, static_cast<__half*>(p), batch, c, h, w, p_h, p_w, img->hp, img->wp); ++g_launches; }
+        { pad_pack_c8_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(src), nchw, static_cast<__half*>(p), batch, c, h, w, p_h, p_w, img->hp, img->wp, colsum); ++g_launches; }
     NML_CUDA(cudaGetLastError());
     return NML_OK;
 }
@@ -862,12 +862,12 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     int cpa = 0, cpb = 0;
     // Few-channel layer input (RGB stems): patches come as 8-pixel windows of the padded 8-channel image,
     // one kernel row per tap, (kw, c) packed in the 64 patch columns.
-    const bool window = T > 1 && !g.colsum_of_patch && window_eligible(g.patch_c, g.kw, g.d_w, mi.enc);
+    const bool window = T > 1 && window_eligible(g.patch_c, g.kw, g.d_w, mi.enc);
     WindowImage wimg = {nullptr, 0, 0};
     int rc;
     if (window) {
         rc = prepare_window(g.patch, g.dtype, g.layout, g.batch, g.patch_c, g.patch_h, g.patch_w, g.p_h, g.p_w, g.s_w,
-                            g.plain_w, ws, st, &wimg);
+                            g.plain_w, ws, st, &wimg, g.colsum_of_patch ? g.colsum : nullptr);
         pa[0] = wimg.ptr;
         cpa = 8;
     } else {

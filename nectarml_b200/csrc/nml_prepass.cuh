@@ -207,8 +207,9 @@ __global__ void __launch_bounds__(256) repack_weight_kernel(const TIn* __restric
 template <typename TIn>
 __global__ void __launch_bounds__(256) pad_pack_c8_kernel(const TIn* __restrict__ in, int nchw, __half* __restrict__ out,
                                                           int N, int C, int H, int W, int pad_h, int pad_w, int Hp,
-                                                          int Wp) {
+                                                          int Wp, float* colsum) {
     const size_t total = static_cast<size_t>(N) * Hp * Wp;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // per-channel sums of the values written (bias gradient)
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const int wp = static_cast<int>(i % Wp);
@@ -220,13 +221,35 @@ __global__ void __launch_bounds__(256) pad_pack_c8_kernel(const TIn* __restrict_
 #pragma unroll
         for (int c = 0; c < 8; ++c) v[c] = __float2half_rn(0.f);
         if (h >= 0 && h < H && w >= 0 && w < W) {
-            for (int c = 0; c < C; ++c) {
-                size_t src = nchw ? ((static_cast<size_t>(n) * C + c) * H + h) * W + w
-                                  : ((static_cast<size_t>(n) * H + h) * W + w) * C + c;
-                v[c] = __float2half_rn(load_as_float(in, src));
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                if (c < C) {
+                    size_t src = nchw ? ((static_cast<size_t>(n) * C + c) * H + h) * W + w
+                                      : ((static_cast<size_t>(n) * H + h) * W + w) * C + c;
+                    v[c] = __float2half_rn(load_as_float(in, src));
+                    acc[c] += __half2float(v[c]);
+                }
             }
         }
         reinterpret_cast<uint4*>(out)[i] = *reinterpret_cast<const uint4*>(v);
+    }
+    if (colsum != nullptr) {  // uniform across the grid
+        __shared__ float part[8][8];
+        const int lane = threadIdx.x & 31, wy = threadIdx.x >> 5;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+            float x = acc[c];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+            if (lane == 0) part[wy][c] = x;
+        }
+        __syncthreads();
+        if (threadIdx.x < C) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w8 = 0; w8 < 8; ++w8) sum += part[w8][threadIdx.x];
+            atomicAdd(colsum + threadIdx.x, sum);
+        }
     }
 }
 
