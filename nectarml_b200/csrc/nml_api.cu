@@ -380,16 +380,19 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
             P.a_stages = std::min(4, (avail - res_bytes) / P.patch_bytes);
         } else {
             P.b_resident = 0;
+            // B streams tap by tap; narrow tiles take two taps per stage (8 MMAs per barrier round trip)
+            P.ka = std::max(1, std::min(2, tune_env("NML_TUNE_KA", P.bn >= 192 ? 1 : 2)));
+            const int b_stage = P.ka * b_slice;
             P.a_stages = std::min(3, std::max(2, P.passes * P.c_blocks));
-            P.stages = std::min(8, (avail - P.a_stages * P.patch_bytes) / b_slice);
+            P.stages = std::min(8, (avail - P.a_stages * P.patch_bytes) / b_stage);
             if (P.stages < 3) {  // wide tiles: give the B ring room
                 P.a_stages = 2;
                 P.stg_bufs = 1;
                 avail = 232448 - fixed - P.epi_warps * P.stg_bufs * kStagingBufBytes;
-                P.stages = std::min(8, (avail - P.a_stages * P.patch_bytes) / b_slice);
+                P.stages = std::min(8, (avail - P.a_stages * P.patch_bytes) / b_stage);
             }
             if (P.stages < 2) return NML_ERR_UNSUPPORTED;
-            b_region = P.stages * b_slice;
+            b_region = P.stages * b_stage;
         }
         P.a_ring_off = static_cast<int>(round_up(b_region, 1024));
         P.ring_bytes = P.a_ring_off + P.a_stages * P.patch_bytes;
@@ -538,6 +541,11 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
             { to_float_kernel<__half><<<ceil_div(N, 256), 256, 0, st>>>(static_cast<const __half*>(f.bias), b, N); ++g_launches; }
         }
     }
+    // Few output pixels under a long K loop (the 2x2 ... 8x8 layers of a U-Net): room for the fp32 partial
+    // sums of a K-split walk.
+    const size_t out_pixels = static_cast<size_t>(f.batch) * f.out_h * f.out_w;
+    const bool may_split = !window && out_pixels <= 8192 && 1ll * T * c_blocks >= 32 && tune_env("NML_TUNE_FSPLIT", 1);
+    float* split_acc = may_split ? static_cast<float*>(ws.take(out_pixels * N * sizeof(float))) : nullptr;
     if (ws.dry) return NML_OK;
     if (!ws.fits()) return NML_ERR_WORKSPACE;
 
@@ -674,8 +682,8 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         const long long res_need = 1ll * c_blocks * n_taps * bn_res * 128 + 2 * round_up(pw_ * ph_ * 128, 1024);
         const bool res_ok = P.passes == 1 && N <= 256 &&
                             res_need <= 232448 - (1024 + 256 + kBiasTileBytes) - 4 * kStagingBufBytes;
-        const bool streamed_ok = n_phases == 1 && P.passes == 3 && N <= 128;
-        if (can && mode && ((mode == 2 && (res_ok || n_phases == 1)) || (eff_patch >= 0.8 * eff_box && (res_ok || streamed_ok)))) {
+        const bool streamed_ok = N <= 128 && (P.passes == 3 || mode >= 3);
+        if (can && mode && (mode == 2 || (eff_patch >= 0.8 * eff_box && (res_ok || streamed_ok)))) {
             patch_resident = res_ok;
             P.patch = 1;
             P.patch_w = pw_;
@@ -765,7 +773,13 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     // tile id then names two consecutive row tiles of one phase.
     // (short K loops are epilogue-bound, where pairing only halves the number of independent tiles)
     const int k_iters_min = P.passes * P.c_blocks * std::max<int>(1, P.phases[0].tap_count);
-    P.pair = (tune_env("NML_TUNE_PAIR", 1) && !P.patch && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) && k_iters_min >= 4 &&
+    // (a problem with so few tiles that half the SMs would idle is K-split instead, see below)
+    long long tiles_single = 0;
+    for (int p = 0; p < n_phases; ++p)
+        tiles_single += 1ll * ceil_div(P.phases[p].wq, 1 << P.wb_log2) * ceil_div(P.phases[p].hq, 1 << P.hb_log2) *
+                        ceil_div(f.batch, 1 << P.nb_log2) * P.n_tiles;
+    const bool will_split = may_split && !P.patch && tiles_single * 2 <= ds->sms && k_iters_min >= 8;
+    P.pair = (tune_env("NML_TUNE_PAIR", 1) && !P.patch && !will_split && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) && k_iters_min >= 4 &&
               (P.out_mode == OUT_NHWC_TMA || P.out_mode == OUT_NCHW_TMA || P.out_mode == OUT_NCHW) && ds->sms >= 2) ? 1 : 0;
     int tiles = 0;
     for (int p = 0; p < n_phases; ++p) {
@@ -777,6 +791,26 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         tiles += (P.pair ? ceil_div(m_tiles, 2) : m_tiles) * P.n_tiles;
     }
     P.num_tiles = tiles;
+    P.base_tiles = tiles;
+    P.fsplit = 1;
+    if (may_split && !P.pair && !P.patch && tiles * 2 <= ds->sms) {
+        int k_min = k_iters_min;
+        for (int p = 0; p < n_phases; ++p)
+            if (P.phases[p].tap_count > 0) k_min = std::min(k_min, P.passes * P.c_blocks * P.phases[p].tap_count);
+        const int z = std::min(ds->sms / tiles, k_min / 4);  // at least 4 K iterations per slice
+        if (z >= 2) {
+            P.fsplit = z;
+            P.num_tiles = tiles * z;
+            // the walk adds into the scratch; the finishing pass applies bias, rounding, cast and layout
+            NML_CUDA(cudaMemsetAsync(split_acc, 0, out_pixels * N * sizeof(float), st));
+            P.out = split_acc;
+            P.out_mode = OUT_NHWC;
+            P.out_f16 = 0;
+            P.round_f16 = 0;
+            P.bias = nullptr;
+            P.ld_out = N;
+        }
+    }
 
     // tensor maps
     for (int pl = 0; pl < mi.planes; ++pl) {
@@ -822,7 +856,21 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         }
         if (rc) return rc;
     }
-    return launch_kernel(P, ds, st);
+    rc = launch_kernel(P, ds, st);
+    if (rc || P.fsplit <= 1) return rc;
+    {
+        const size_t total = out_pixels * N;
+        const int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 8));
+        const int nchw = (f.out_layout == NML_NCHW && !(f.out_h == 1 && f.out_w == 1)) ? 1 : 0;
+        if (f.out_dtype == NML_F16)
+            { finish_rows_kernel<__half><<<blocks, 256, 0, st>>>(split_acc, bias32, static_cast<__half*>(f.out), out_pixels, N,
+                                                              f.out_h * f.out_w, nchw, 0); ++g_launches; }
+        else
+            { finish_rows_kernel<float><<<blocks, 256, 0, st>>>(split_acc, bias32, static_cast<float*>(f.out), out_pixels, N,
+                                                             f.out_h * f.out_w, nchw, f.round_f16); ++g_launches; }
+        NML_CUDA(cudaGetLastError());
+    }
+    return NML_OK;
 }
 
 // ------------------------------------------------------- wgrad-like problems --

@@ -270,6 +270,29 @@ __global__ void __launch_bounds__(256) repack_weight_c8_kernel(const TIn* __rest
     }
 }
 
+// Partial sums of a K-split forward walk, fp32 [pixels][C] -> the output tensor: bias, optional
+// rounding through fp16, cast, and the caller's layout (nchw: out[n][c][pixel of the image]).
+template <typename TOut>
+__global__ void __launch_bounds__(256) finish_rows_kernel(const float* __restrict__ acc, const float* __restrict__ bias,
+                                                          TOut* __restrict__ out, size_t pixels, int C, int hw, int nchw,
+                                                          int round_f16) {
+    const size_t total = pixels * C;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t p = i / C;
+        const int c = static_cast<int>(i - p * C);
+        float v = acc[i];
+        if (bias != nullptr) v += bias[c];
+        if (round_f16) v = __half2float(__float2half_rn(v));
+        size_t o = i;
+        if (nchw) {
+            const size_t n = p / hw;
+            o = (n * C + c) * hw + (p - n * hw);
+        }
+        out[o] = static_cast<TOut>(v);
+    }
+}
+
 template <typename TIn>
 __global__ void __launch_bounds__(256) to_float_kernel(const TIn* __restrict__ in, float* out, int n) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;

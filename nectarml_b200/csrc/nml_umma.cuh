@@ -94,6 +94,11 @@ struct KParams {
     // is a function of the shared-memory address, so a descriptor may start on any 128-byte row.)
     // A is then read from L2 about once instead of once per tap.  B slices stream through the stage ring,
     // or stay resident in shared memory for the whole launch when all of them fit.
+    // Forward walk, few tiles and a long K loop (U-Net bottleneck layers): the K iterations of a tile are
+    // cut into fsplit slices that run as separate tiles; their partial sums are added with fp32
+    // atomics into a zeroed row-major scratch, which a small pass turns into the output.
+    int fsplit;          // K slices per tile (1 = off)
+    int base_tiles;      // tiles of one slice; tile id = slice * base_tiles + tile
     int patch;           // 1: patch walk
     int patch_w, patch_h;    // patch extent in pixels
     int patch_bytes;     // bytes one patch buffer occupies (multiple of 1024)
@@ -379,7 +384,12 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
     // ------------------------------------------------------------ producer --
     if (warp == 0 || warp == 6) {
         const bool do_a = (warp == 0), do_b = (warp == 6);
-        if (lane == 0) {
+        // Issuing one TMA keeps its thread busy for ~300 clocks, more than the MMAs of a narrow K atom last.
+        // The atoms of a stage are therefore issued by one lane each, in the same instruction (the patch
+        // walk, with one box per tile, is driven by lane 0 alone).
+        const int issue_lanes = P.patch ? 1 : P.ka;
+        const uint32_t issue_mask = (1u << issue_lanes) - 1u;
+        if (lane < issue_lanes) {
             int stage = 0;
             uint32_t parity = 0;
             bool ok = true;
@@ -398,7 +408,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                         tma_load_2d(sb + j * box_bytes, tb, fb, ntile * P.bn + j * P.kb, tap.wk + cb * P.kb);
                 }
             };
-            if (kMode == MODE_FPROP && !kPair && P.patch) {
+            if (kMode == MODE_FPROP && !kPair && P.patch) {  // (issue_lanes == 1 here)
                 const Phase& ph = P.phases[0];
                 if (do_a) {
                     const uint32_t a_base = smem_u32(smem + P.a_ring_off);
@@ -470,19 +480,26 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                         }
                     }
                 } else {
+                    // B streams through the ring, P.ka tap slices per stage
+                    int p = 0;
                     for (int tile = tile_first; ok && tile < P.num_tiles; tile += tile_step) {
-                        const int ntile = tile % P.n_tiles;
+                        while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
+                        const Phase& pt = P.phases[p];
+                        const int ntile = (tile - pt.tile_begin) % P.n_tiles;
                         for (int pass = 0; ok && pass < P.passes; ++pass) {
                             const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
                             for (int cb = 0; ok && cb < P.c_blocks; ++cb)
-                                for (int t = 0; t < ph.tap_count; ++t) {
+                                for (int t = 0; t < pt.tap_count; t += P.ka) {
                                     if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err, ERR_WAIT_EMPTY)) {
                                         ok = false;
                                         break;
                                     }
+                                    const int n = min(P.ka, pt.tap_count - t);
                                     const uint32_t fb = smem_u32(&full_bar[stage]);
-                                    mbar_arrive_expect_tx(fb, stage_b_bytes);
-                                    load_b(smem_u32(smem) + stage * stage_b_bytes, tb, fb, P.taps[ph.tap_begin + t], cb, ntile);
+                                    mbar_arrive_expect_tx(fb, n * stage_b_bytes);
+                                    for (int j = 0; j < n; ++j)
+                                        load_b(smem_u32(smem) + (stage * P.ka + j) * stage_b_bytes, tb, fb,
+                                               P.taps[pt.tap_begin + t + j], cb, ntile);
                                     ++issued;
                                     if (++stage == P.stages) {
                                         stage = 0;
@@ -493,7 +510,12 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     }
                 }
             } else
-            for (int tile = tile_first; ok && tile < P.num_tiles; tile += tile_step) {
+            for (int tile_id = tile_first; ok && tile_id < P.num_tiles; tile_id += tile_step) {
+                int tile = tile_id, kz = 0;
+                if (kMode == MODE_FPROP && P.fsplit > 1) {
+                    kz = tile_id / P.base_tiles;
+                    tile = tile_id - kz * P.base_tiles;
+                }
                 if (kMode == MODE_FPROP) {
                     int p = 0;
                     while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
@@ -509,57 +531,70 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     int h0 = (th << P.hb_log2) * P.a_stride_h;
                     int n0 = tn << P.nb_log2;
                     int k_iters = P.passes * ph.tap_count * P.c_blocks;
+                    int k_first = 0;
+                    if (P.fsplit > 1) {  // this slice's share of the K iterations
+                        const int per = (k_iters + P.fsplit - 1) / P.fsplit;
+                        k_first = min(kz * per, k_iters);
+                        k_iters = min(k_first + per, k_iters) - k_first;
+                    }
 #ifdef NML_TRACE
                     if (P.dbg_skip == 3) k_iters = 0;  // MMA-rate experiment: no loads at all
 #endif
+                    // this lane's position in the K loop, (pass, tap, channel block) of iteration it + lane, kept
+                    // by counting: a division per stage is time the 256-wide tiles' producer does not have
                     int pass = 0, t = 0, cb = 0;
-                    int slot = 0, n_in_stage = 0;
-                    for (int it = 0; it < k_iters; ++it) {
-                        const Tap& tap = P.taps[ph.tap_begin + t];
-                        // 3xTF32 order: hi*lo, lo*hi, then hi*hi -- the small cross terms go in
-                        // while the accumulator is small, so the tensor core's truncating
-                        // accumulation costs them nothing
-                        const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
-                        const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
-                        // in a pair every load signals the LEADER's barrier, which expects both members' bytes
-                        uint32_t fb = smem_u32(&full_bar[stage]);
-                        if (kPair) fb = map_to_cta(fb, 0);
-                        if (slot == 0) {
-                            if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err,
-                                           ERR_WAIT_EMPTY)) {
-                                ok = false;
-                                break;
-                            }
-                            n_in_stage = min(P.ka, k_iters - it);
-                            if (!kPair) mbar_arrive_expect_tx(fb, n_in_stage * tx_bytes);
-                            else if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * n_in_stage * tx_bytes);
-                        }
-                        uint32_t sa = smem_u32(smem + stage * stage_bytes) + slot * kStageABytes;
-                        uint32_t sb = smem_u32(smem + stage * stage_bytes) + b_off + slot * stage_b_bytes;
-                        if (kPair) {
-                            const int ncol = ntile * P.bn + static_cast<int>(cta_rank) * (P.bn / 2);  // this member's half of B
-                            if (do_a) tma_load_4d_pair(sa, ta, fb, cb * P.kb, w0 + tap.dw, h0 + tap.dh, n0);
-                            if (do_b) {
-                                if (!P.b_mn_major) tma_load_2d_pair(sb, tb, fb, tap.wk + cb * P.kb, ncol);
-                                else tma_load_3d_pair(sb, tb, fb, 0, tap.wk + cb * P.kb, ncol / P.kb);
-                            }
-                        } else
-                        if (do_a) tma_load_4d(sa, ta, fb, cb * P.kb, w0 + tap.dw, h0 + tap.dh, n0);
-                        if (!kPair && do_b) load_b(sb, tb, fb, tap, cb, ntile);
-                        if (++slot == n_in_stage) {
-                            slot = 0;
-                            ++issued;
-                            if (++stage == P.stages) {
-                                stage = 0;
-                                parity ^= 1;
-                            }
-                        }
-                        if (++cb == P.c_blocks) {
-                            cb = 0;
+                    auto advance = [&](int steps) {
+                        cb += steps;
+                        while (cb >= P.c_blocks) {
+                            cb -= P.c_blocks;
                             if (++t == ph.tap_count) {
                                 t = 0;
                                 ++pass;
                             }
+                        }
+                    };
+                    advance(k_first + lane);
+                    for (int it = 0; it < k_iters; it += P.ka) {  // one stage per iteration
+                        // in a pair every load signals the LEADER's barrier, which expects both members' bytes
+                        uint32_t fb = smem_u32(&full_bar[stage]);
+                        if (kPair) fb = map_to_cta(fb, 0);
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err, ERR_WAIT_EMPTY)) {
+                            ok = false;
+                            break;
+                        }
+                        const int n_in_stage = min(P.ka, k_iters - it);
+                        if (lane == 0) {
+                            if (!kPair) mbar_arrive_expect_tx(fb, n_in_stage * tx_bytes);
+                            else if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * n_in_stage * tx_bytes);
+                        }
+                        __syncwarp(issue_mask);
+                        if (lane < n_in_stage) {  // this lane's atom: K iteration it + lane = (pass, tap, channel block)
+                            const Tap& tap = P.taps[ph.tap_begin + t];
+                            // 3xTF32 order: hi*lo, lo*hi, then hi*hi -- the small cross terms go in
+                            // while the accumulator is small, so the tensor core's truncating
+                            // accumulation costs them nothing
+                            const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
+                            const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
+                            const uint32_t sa = smem_u32(smem + stage * stage_bytes) + lane * kStageABytes;
+                            const uint32_t sb = smem_u32(smem + stage * stage_bytes) + b_off + lane * stage_b_bytes;
+                            if (kPair) {
+                                const int ncol = ntile * P.bn + static_cast<int>(cta_rank) * (P.bn / 2);  // this member's half of B
+                                if (do_a) tma_load_4d_pair(sa, ta, fb, cb * P.kb, w0 + tap.dw, h0 + tap.dh, n0);
+                                if (do_b) {
+                                    if (!P.b_mn_major) tma_load_2d_pair(sb, tb, fb, tap.wk + cb * P.kb, ncol);
+                                    else tma_load_3d_pair(sb, tb, fb, 0, tap.wk + cb * P.kb, ncol / P.kb);
+                                }
+                            } else if (do_a) {
+                                tma_load_4d(sa, ta, fb, cb * P.kb, w0 + tap.dw, h0 + tap.dh, n0);
+                            } else {
+                                load_b(sb, tb, fb, tap, cb, ntile);
+                            }
+                        }
+                        advance(P.ka);
+                        ++issued;
+                        if (++stage == P.stages) {
+                            stage = 0;
+                            parity ^= 1;
                         }
                     }
                 } else {  // MODE_WGRAD
@@ -573,6 +608,9 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     int kb_end = min(kb_begin + per, P.kblocks_total);
                     int g_per_tile = kTileM / P.kb;
                     int na = g_per_tile, nb = P.bn / P.kb;
+                    if (P.ka == 1) {
+                    // one K block per stage (256-wide tiles, pairs): the single issuing lane has ~500 clocks per
+                    // stage, so its loop carries nothing but counters
                     int left = P.passes * max(kb_end - kb_begin, 0);  // K iterations still to load for this tile
                     int slot = 0, n_in_stage = 0;
                     for (int pass = 0; ok && pass < P.passes; ++pass) {
@@ -651,9 +689,96 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                             }
                         }
                     }
+                    } else {
+                    const int nkb = max(kb_end - kb_begin, 0);
+                    const int k_total = P.passes * nkb;  // K iterations of this tile: (pass, K block)
+                    // groups of this M tile: with a_grouped they share one tap
+                    const int g0 = min(mt * g_per_tile, P.groups_total - 1);
+                    const int t0 = g0 / P.c_blocks;
+                    const int cib0 = g0 - t0 * P.c_blocks;
+                    // this lane's K iteration (it + lane) as (pass, K block -> pixel box), kept by counting
+                    const int tw0 = kb_begin % P.ktiles_w;
+                    const int th0 = (kb_begin / P.ktiles_w) % P.ktiles_h;
+                    const int tn0 = kb_begin / (P.ktiles_w * P.ktiles_h);
+                    int pass = 0, rel = 0, tw = tw0, th = th0, tn = tn0;
+                    auto advance = [&](int steps) {
+                        for (int i = 0; i < steps; ++i) {
+                            if (++rel >= nkb) {
+                                rel = 0;
+                                ++pass;
+                                tw = tw0;
+                                th = th0;
+                                tn = tn0;
+                            } else if (++tw == P.ktiles_w) {
+                                tw = 0;
+                                if (++th == P.ktiles_h) {
+                                    th = 0;
+                                    ++tn;
+                                }
+                            }
+                        }
+                    };
+                    if (nkb > 0) advance(lane);
+                    for (int it = 0; it < k_total; it += P.ka) {  // one stage per iteration
+                        uint32_t fb = smem_u32(&full_bar[stage]);
+                        if (kPair) fb = map_to_cta(fb, 0);
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err, ERR_WAIT_EMPTY)) {
+                            ok = false;
+                            break;
+                        }
+                        const int n_in_stage = min(P.ka, k_total - it);
+                        if (lane == 0) {
+                            if (!kPair) mbar_arrive_expect_tx(fb, n_in_stage * tx_bytes);
+                            else if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * n_in_stage * tx_bytes);
+                        }
+                        __syncwarp(issue_mask);
+                        if (lane < n_in_stage) {
+                            const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
+                            const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
+                            const int w0 = tw << P.wb_log2, h0 = th << P.hb_log2, n0 = tn << P.nb_log2;
+                            const uint32_t sa = smem_u32(smem + stage * stage_bytes) + lane * kStageABytes;
+                            const uint32_t sb = smem_u32(smem + stage * stage_bytes) + b_off + lane * stage_b_bytes;
+                            if (kPair) {  // pairs are only planned for grouped operands
+                                const Tap& tap = P.taps[t0];
+                                if (do_a)
+                                    tma_load_5d_pair(sa, ta, fb, 0, w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0,
+                                                     cib0);
+                                if (do_b)
+                                    tma_load_5d_pair(sb, tb, fb, 0, w0, h0, n0,
+                                                     (ntile * P.bn) / P.kb + static_cast<int>(cta_rank) * (P.bn / 2 / P.kb));
+                            } else if (do_a) {
+                                if (P.a_grouped) {
+                                    const Tap& tap = P.taps[t0];
+                                    tma_load_5d(sa, ta, fb, 0, w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0,
+                                                cib0);
+                                } else {
+                                    for (int g = 0; g < na; ++g) {
+                                        int gi = min(mt * g_per_tile + g, P.groups_total - 1);
+                                        int t = gi / P.c_blocks;
+                                        int cib = gi - t * P.c_blocks;
+                                        const Tap& tap = P.taps[t];
+                                        tma_load_4d(sa + g * box_bytes, ta, fb, cib * P.kb,
+                                                    w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0);
+                                    }
+                                }
+                            } else if (P.b_grouped) {
+                                tma_load_5d(sb, tb, fb, 0, w0, h0, n0, (ntile * P.bn) / P.kb);
+                            } else {
+                                for (int j = 0; j < nb; ++j)
+                                    tma_load_4d(sb + j * box_bytes, tb, fb, ntile * P.bn + j * P.kb, w0, h0, n0);
+                            }
+                        }
+                        advance(P.ka);
+                        ++issued;
+                        if (++stage == P.stages) {
+                            stage = 0;
+                            parity ^= 1;
+                        }
+                    }
+                    }
                 }
             }
-            if (!ok) {
+            if (!ok && lane == 0) {
                 // Unwinding: give copies already issued a bounded chance to land before the
                 // CTA's shared memory goes away.
                 int back = issued < P.stages ? issued : P.stages;
@@ -708,12 +833,22 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
         if (kMode == MODE_FPROP && !kPair && P.patch && P.b_resident) {
             patch_resident_issue(0, 2);
         } else
-        for (int tile = tile_first; ok && (!kPair || leader) && tile < P.num_tiles; tile += tile_step, ++titer) {
+        for (int tile_id = tile_first; ok && (!kPair || leader) && tile_id < P.num_tiles; tile_id += tile_step, ++titer) {
+            int tile = tile_id, kz = 0;
+            if (kMode == MODE_FPROP && P.fsplit > 1) {
+                kz = tile_id / P.base_tiles;
+                tile = tile_id - kz * P.base_tiles;
+            }
             int k_iters;
             if (kMode == MODE_FPROP) {
                 int p = 0;
                 while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
                 k_iters = P.passes * P.phases[p].tap_count * P.c_blocks;
+                if (P.fsplit > 1) {
+                    const int per = (k_iters + P.fsplit - 1) / P.fsplit;
+                    const int k_first = min(kz * per, k_iters);
+                    k_iters = min(k_first + per, k_iters) - k_first;
+                }
             } else {
                 int m_tiles = (P.groups_total * P.kb + kTileM - 1) / kTileM;
                 if (kPair) m_tiles = (m_tiles + 1) / 2;  // tile ids name pairs of row tiles
@@ -734,7 +869,9 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             const uint32_t d_tmem = tmem_base + buf * P.bn;
             uint32_t acc = 0;
             if (kMode == MODE_FPROP && !kPair && P.patch) {
-                const Phase& ph = P.phases[0];
+                int pp = 0;
+                while (pp + 1 < P.n_phases && tile >= P.phases[pp + 1].tile_begin) ++pp;
+                const Phase& ph = P.phases[pp];
                 const uint32_t sbo_a = static_cast<uint32_t>(P.patch_w) * 128u;  // 8-row groups are one patch row apart
                 const uint64_t bdesc_ring0 = make_smem_desc(smem_u32(smem), lbo_b, b32 ? 512 : 1024, b32 ? 1 : 2);  // B ring starts the region
                 for (int pass = 0; ok && pass < P.passes; ++pass)
@@ -747,25 +884,30 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                         if (pass == 0 && cb == 0 && lane == 0) NML_STAMP(titer, 1);
                         const uint32_t patch_addr = smem_u32(smem + P.a_ring_off) + pstage * P.patch_bytes;
                         const uint64_t adesc0 = make_smem_desc(patch_addr, 16, sbo_a, 2);
-                        for (int t = 0; t < ph.tap_count; ++t) {
+                        for (int t = 0; t < ph.tap_count; t += P.ka) {
                             if (!mbar_wait(smem_u32(&full_bar[stage]), parity, abort_flag, P.err, ERR_WAIT_FULL)) {
                                 ok = false;
                                 break;
                             }
                             tc_fence_after();
+                            const int n = min(P.ka, ph.tap_count - t);
                             if (elect_one()) {
-                                const uint64_t adesc = adesc0 + static_cast<uint32_t>(P.taps[ph.tap_begin + t].aoff);
-                                const uint64_t bdesc = bdesc_ring0 + static_cast<uint64_t>(stage * b_atom_step);
-                                if (f16) {
-                                    umma_f16(d_tmem, adesc, bdesc, idesc, acc);
-                                    umma_f16(d_tmem, adesc + 2, bdesc + adv_b, idesc, 1u);
-                                    umma_f16(d_tmem, adesc + 4, bdesc + 2 * adv_b, idesc, 1u);
-                                    umma_f16(d_tmem, adesc + 6, bdesc + 3 * adv_b, idesc, 1u);
-                                } else {
-                                    umma_tf32(d_tmem, adesc, bdesc, idesc, acc);
-                                    umma_tf32(d_tmem, adesc + 2, bdesc + adv_b, idesc, 1u);
-                                    umma_tf32(d_tmem, adesc + 4, bdesc + 2 * adv_b, idesc, 1u);
-                                    umma_tf32(d_tmem, adesc + 6, bdesc + 3 * adv_b, idesc, 1u);
+                                uint64_t bdesc = bdesc_ring0 + static_cast<uint64_t>(stage * P.ka * b_atom_step);
+                                for (int j = 0; j < n; ++j) {
+                                    const uint64_t adesc = adesc0 + static_cast<uint32_t>(P.taps[ph.tap_begin + t + j].aoff);
+                                    if (f16) {
+                                        umma_f16(d_tmem, adesc, bdesc, idesc, acc);
+                                        umma_f16(d_tmem, adesc + 2, bdesc + adv_b, idesc, 1u);
+                                        umma_f16(d_tmem, adesc + 4, bdesc + 2 * adv_b, idesc, 1u);
+                                        umma_f16(d_tmem, adesc + 6, bdesc + 3 * adv_b, idesc, 1u);
+                                    } else {
+                                        umma_tf32(d_tmem, adesc, bdesc, idesc, acc);
+                                        umma_tf32(d_tmem, adesc + 2, bdesc + adv_b, idesc, 1u);
+                                        umma_tf32(d_tmem, adesc + 4, bdesc + 2 * adv_b, idesc, 1u);
+                                        umma_tf32(d_tmem, adesc + 6, bdesc + 3 * adv_b, idesc, 1u);
+                                    }
+                                    acc = 1u;
+                                    bdesc += b_atom_step;
                                 }
                                 umma_commit(smem_u32(&empty_bar[stage]));
                             }
@@ -860,7 +1002,12 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
         bool ok = true;
         int titer = 0;
         uint32_t store_seq = 0;  // TMA-store pieces issued by this warp so far (selects the staging buffer)
-        for (int tile = tile_first; ok && tile < P.num_tiles; tile += tile_step, ++titer) {
+        for (int tile_id = tile_first; ok && tile_id < P.num_tiles; tile_id += tile_step, ++titer) {
+            int tile = tile_id, kz = 0;
+            if (kMode == MODE_FPROP && P.fsplit > 1) {
+                kz = tile_id / P.base_tiles;
+                tile = tile_id - kz * P.base_tiles;
+            }
             const int buf = titer & 1;
             const uint32_t tpar = (titer >> 1) & 1;
             // tile decode
@@ -886,6 +1033,12 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 int ow = ph.pw + P.out_stride_w * iw;
                 int oh = ph.ph + P.out_stride_h * ih;
                 k_iters = ph.tap_count;
+                if (P.fsplit > 1) {  // K iterations of this slice (0: nothing to add)
+                    const int full = P.passes * ph.tap_count * P.c_blocks;
+                    const int per = (full + P.fsplit - 1) / P.fsplit;
+                    const int k_first = min(kz * per, full);
+                    k_iters = min(k_first + per, full) - k_first;
+                }
                 if (kOutMode != OUT_NCHW && kOutMode != OUT_NCHW_TMA) {
                     row_off = ((static_cast<size_t>(n) * P.out_h + oh) * P.out_w + ow) * P.ld_out;
                     col_stride = 1;
@@ -1078,7 +1231,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     if (more) tmem_ld_wait();
                 }
             } else
-            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC && P.c_out <= 8) {
+            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC && P.c_out <= 8 && P.fsplit <= 1) {
                 // A handful of output channels (image-producing layers, input gradients of stems): each
                 // thread stores its pixel's few values.  Kept short on purpose -- the epilogue warps are
                 // bound by instruction fetch, not by the stores.
@@ -1103,7 +1256,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     }
                 }
             } else
-            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC) {
+            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC && P.fsplit <= 1) {
                 // Row-major output.  Each 128-byte piece of a row (64 fp16 / 32 fp32 columns) goes
                 // through a swizzled shared-memory tile so that a warp store writes four full
                 // 128-byte row pieces instead of 32 scattered 16-byte ones.  The TMEM load of the
@@ -1247,7 +1400,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 }
                 const int cg = col_base + c0;
                 const int ncols = min(32, P.c_out - cg);
-                if (kMode == MODE_WGRAD) {
+                if (kMode == MODE_WGRAD || (kOutMode == OUT_NHWC && P.fsplit > 1)) {  // partial sums
                     if (row_valid && k_iters > 0) {
                         float* o = reinterpret_cast<float*>(P.out) + row_off +
                                    static_cast<size_t>(cg) * col_stride;

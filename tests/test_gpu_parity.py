@@ -120,9 +120,19 @@ PATCH_SHAPES = {
 }
 
 
-@pytest.mark.parametrize("name", sorted(PATCH_SHAPES))
+# Few output pixels under a long K loop (U-Net bottleneck layers): the forward walk splits K over
+# CTAs and adds partial sums into an fp32 scratch that a finishing pass turns into the output.
+SPLIT_SHAPES = {
+    "s_conv_k4_s2":  (False, (2, 256, 4, 4, 96, 4, 4, (2, 2), (1, 1), (1, 1), (0, 0)), True, "normal"),
+    "s_convT_k4_s2": (True,  (2, 256, 2, 2, 72, 4, 4, (2, 2), (1, 1), (1, 1), (0, 0)), True, "normal"),
+    "s_conv_3x3":    (False, (1, 320, 6, 5, 40, 3, 3, (1, 1), (0, 0), (1, 1), (0, 0)), False, "normal"),
+}
+WALK_SHAPES = {**PATCH_SHAPES, **SPLIT_SHAPES}
+
+
+@pytest.mark.parametrize("name", sorted(WALK_SHAPES))
 def test_patch_walk_shapes(name, oracle):
-    case = PATCH_SHAPES[name]
+    case = WALK_SHAPES[name]
     g = geometry(case)
     x, w, b, dy = cases.draw_conv(name, case)
     r = oracle.round_f16
