@@ -544,7 +544,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     // Few output pixels under a long K loop (the 2x2 ... 8x8 layers of a U-Net): room for the fp32 partial
     // sums of a K-split walk.
     const size_t out_pixels = static_cast<size_t>(f.batch) * f.out_h * f.out_w;
-    const bool may_split = !window && out_pixels <= 8192 && 1ll * T * c_blocks >= 32 && tune_env("NML_TUNE_FSPLIT", 1);
+    const bool may_split = !window && T >= 4 && out_pixels <= 8192 && 1ll * T * c_blocks >= 32 && tune_env("NML_TUNE_FSPLIT", 1);
     float* split_acc = may_split ? static_cast<float*>(ws.take(out_pixels * N * sizeof(float))) : nullptr;
     if (ws.dry) return NML_OK;
     if (!ws.fits()) return NML_ERR_WORKSPACE;
