@@ -387,7 +387,10 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
         // Issuing one TMA keeps its thread busy for ~300 clocks, more than the MMAs of a narrow K atom last.
         // The atoms of a stage are therefore issued by one lane each, in the same instruction (the patch
         // walk, with one box per tile, is driven by lane 0 alone).
-        const int issue_lanes = P.patch ? 1 : P.ka;
+        // Weight-gradient operands that cannot be fetched as one box per K block get a lane per box.
+        const int boxes_per_atom = (kMode != MODE_WGRAD || kPair) ? 1
+                                   : do_a ? (P.a_grouped ? 1 : kTileM / P.kb) : (P.b_grouped ? 1 : P.bn / P.kb);
+        const int issue_lanes = P.patch ? 1 : P.ka * boxes_per_atom;
         const uint32_t issue_mask = (1u << issue_lanes) - 1u;
         if (lane < issue_lanes) {
             int stage = 0;
@@ -608,8 +611,8 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     int kb_end = min(kb_begin + per, P.kblocks_total);
                     int g_per_tile = kTileM / P.kb;
                     int na = g_per_tile, nb = P.bn / P.kb;
-                    if (P.ka == 1) {
-                    // one K block per stage (256-wide tiles, pairs): the single issuing lane has ~500 clocks per
+                    if (kPair) {
+                    // one K block and one box per stage: the single issuing lane has ~500 clocks per
                     // stage, so its loop carries nothing but counters
                     int left = P.passes * max(kb_end - kb_begin, 0);  // K iterations still to load for this tile
                     int slot = 0, n_in_stage = 0;
@@ -718,7 +721,8 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                             }
                         }
                     };
-                    if (nkb > 0) advance(lane);
+                    const int my_atom = lane / boxes_per_atom, my_box = lane - my_atom * boxes_per_atom;
+                    if (nkb > 0) advance(my_atom);
                     for (int it = 0; it < k_total; it += P.ka) {  // one stage per iteration
                         uint32_t fb = smem_u32(&full_bar[stage]);
                         if (kPair) fb = map_to_cta(fb, 0);
@@ -732,12 +736,12 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                             else if (leader) mbar_arrive_expect_tx(smem_u32(&full_bar[stage]), 2 * n_in_stage * tx_bytes);
                         }
                         __syncwarp(issue_mask);
-                        if (lane < n_in_stage) {
+                        if (my_atom < n_in_stage) {
                             const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
                             const CUtensorMap* tb = &P.tmB[(P.passes == 3 && pass == 0) ? 1 : 0];
                             const int w0 = tw << P.wb_log2, h0 = th << P.hb_log2, n0 = tn << P.nb_log2;
-                            const uint32_t sa = smem_u32(smem + stage * stage_bytes) + lane * kStageABytes;
-                            const uint32_t sb = smem_u32(smem + stage * stage_bytes) + b_off + lane * stage_b_bytes;
+                            const uint32_t sa = smem_u32(smem + stage * stage_bytes) + my_atom * kStageABytes;
+                            const uint32_t sb = smem_u32(smem + stage * stage_bytes) + b_off + my_atom * stage_b_bytes;
                             if (kPair) {  // pairs are only planned for grouped operands
                                 const Tap& tap = P.taps[t0];
                                 if (do_a)
@@ -751,21 +755,19 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                                     const Tap& tap = P.taps[t0];
                                     tma_load_5d(sa, ta, fb, 0, w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0,
                                                 cib0);
-                                } else {
-                                    for (int g = 0; g < na; ++g) {
-                                        int gi = min(mt * g_per_tile + g, P.groups_total - 1);
-                                        int t = gi / P.c_blocks;
-                                        int cib = gi - t * P.c_blocks;
-                                        const Tap& tap = P.taps[t];
-                                        tma_load_4d(sa + g * box_bytes, ta, fb, cib * P.kb,
-                                                    w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0);
-                                    }
+                                } else {  // this lane's 64-channel group of the row tile
+                                    const int g = my_box;
+                                    int gi = min(mt * g_per_tile + g, P.groups_total - 1);
+                                    int t = gi / P.c_blocks;
+                                    int cib = gi - t * P.c_blocks;
+                                    const Tap& tap = P.taps[t];
+                                    tma_load_4d(sa + g * box_bytes, ta, fb, cib * P.kb,
+                                                w0 * P.a_stride_w + tap.dw, h0 * P.a_stride_h + tap.dh, n0);
                                 }
                             } else if (P.b_grouped) {
                                 tma_load_5d(sb, tb, fb, 0, w0, h0, n0, (ntile * P.bn) / P.kb);
-                            } else {
-                                for (int j = 0; j < nb; ++j)
-                                    tma_load_4d(sb + j * box_bytes, tb, fb, ntile * P.bn + j * P.kb, w0, h0, n0);
+                            } else {  // this lane's 64-column group of the column tile
+                                tma_load_4d(sb + my_box * box_bytes, tb, fb, ntile * P.bn + my_box * P.kb, w0, h0, n0);
                             }
                         }
                         advance(P.ka);
