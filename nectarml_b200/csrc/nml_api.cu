@@ -669,12 +669,13 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
             range_w = std::max(range_w, dw_max - dw_min);
             range_h = std::max(range_h, dh_max - dh_min);
         }
-        const int pw_ = 8 + range_w, ph_ = 16 + range_h;
+        // (a row stride of the walk only stretches the patch: consecutive output rows are esh patch rows apart)
+        const int pw_ = 8 + range_w, ph_ = 15 * esh + range_h + 1;
         const int wq = P.phases[0].wq, hq = P.phases[0].hq;
         const double eff_patch = static_cast<double>(wq) * hq / (1.0 * round_up(wq, 8) * round_up(hq, 16));
         const double eff_box = static_cast<double>(wq) * hq * f.batch /
                                (1.0 * round_up(wq, 1 << P.wb_log2) * round_up(hq, 1 << P.hb_log2) * round_up(f.batch, 1 << P.nb_log2));
-        const bool can = !window && every_phase_has_taps && n_taps >= 2 && esw == 1 && esh == 1 && pw_ <= 256 && ph_ <= 256 &&
+        const bool can = every_phase_has_taps && n_taps >= 2 && esw == 1 && pw_ <= 256 && ph_ <= 256 &&
                          pw_ * ph_ * 128 <= 48 * 1024;
         // B stays resident when every slice fits beside two patch buffers and the smallest epilogue staging;
         // streaming B tap by tap pays only for the 3xTF32 split (a barrier round trip per 4 short MMAs otherwise)
@@ -819,10 +820,11 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         uint32_t abox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>((1 << P.wb_log2) * esw),
                             static_cast<uint32_t>((1 << P.hb_log2) * esh), static_cast<uint32_t>(1 << P.nb_log2)};
         uint32_t aes[4] = {1, static_cast<uint32_t>(esw), static_cast<uint32_t>(esh), 1};
-        if (P.patch) {
+        if (P.patch) {  // contiguous rows: the row stride is applied by the MMA descriptors
             abox[1] = static_cast<uint32_t>(P.patch_w);
             abox[2] = static_cast<uint32_t>(P.patch_h);
             abox[3] = 1;
+            aes[1] = aes[2] = 1;
         }
         if (window) {
             // dims: (64 elements = 8 pixels x 8 channels, output column, padded row, image); consecutive

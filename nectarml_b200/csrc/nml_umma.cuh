@@ -325,7 +325,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
         const uint32_t lbo_b = P.b_mn_major ? box_bytes : 16;
         const uint32_t adv_b = P.b_mn_major ? (((P.kind == KIND_F16) ? 16 : 8) * 128) >> 4 : 2;
         const uint32_t b_step = static_cast<uint32_t>(stage_b_bytes) >> 4;
-        const uint32_t sbo_a = static_cast<uint32_t>(P.patch_w) * 128u;  // 8-row groups are one patch row apart
+        const uint32_t sbo_a = static_cast<uint32_t>(P.patch_w * P.a_stride_h) * 128u;  // 8-row groups: one output row = a_stride_h patch rows apart
         const bool f16 = (P.kind == KIND_F16);
         if (!mbar_wait(smem_u32(bres_bar), 0, abort_flag, P.err, ERR_WAIT_FULL)) return;
         int titer = t_first;
@@ -426,8 +426,8 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                         const int tw = m % pt.tiles_w;
                         const int th = (m / pt.tiles_w) % pt.tiles_h;
                         const int tn = m / (pt.tiles_w * pt.tiles_h);
-                        const int w0 = (tw << P.wb_log2) + pt.org_w;
-                        const int h0 = (th << P.hb_log2) + pt.org_h;
+                        const int w0 = (tw << P.wb_log2) * P.a_stride_w + pt.org_w;
+                        const int h0 = (th << P.hb_log2) * P.a_stride_h + pt.org_h;
                         for (int pass = 0; ok && pass < P.passes; ++pass) {
                             const CUtensorMap* ta = &P.tmA[(P.passes == 3 && pass == 1) ? 1 : 0];
                             for (int cb = 0; cb < P.c_blocks; ++cb) {
@@ -874,7 +874,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 int pp = 0;
                 while (pp + 1 < P.n_phases && tile >= P.phases[pp + 1].tile_begin) ++pp;
                 const Phase& ph = P.phases[pp];
-                const uint32_t sbo_a = static_cast<uint32_t>(P.patch_w) * 128u;  // 8-row groups are one patch row apart
+                const uint32_t sbo_a = static_cast<uint32_t>(P.patch_w * P.a_stride_h) * 128u;  // 8-row groups: one output row = a_stride_h patch rows apart
                 const uint64_t bdesc_ring0 = make_smem_desc(smem_u32(smem), lbo_b, b32 ? 512 : 1024, b32 ? 1 : 2);  // B ring starts the region
                 for (int pass = 0; ok && pass < P.passes; ++pass)
                     for (int cb = 0; ok && cb < P.c_blocks; ++cb) {
