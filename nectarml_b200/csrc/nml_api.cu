@@ -455,11 +455,69 @@ struct FpropLike {
     const void* bias;
     int bias_dtype;
     int math, round_f16;
+    // phase-packed gather walk (set by run_fprop_like itself): the real output behind the packed columns
+    int shuf_sh, shuf_sw, shuf_c, shuf_oh, shuf_ow;
 };
 
 static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     MathInfo mi;
     if (!math_info(f.math, &mi)) return NML_ERR_INVALID;
+    // A strided gather with very few output channels (input gradient of an RGB stem, image-producing
+    // transposed layer) would run one mostly empty 16-column pass per output phase.  All phases are
+    // packed into the columns instead: one unit-stride pass over the input with stride_h*stride_w*C
+    // columns, whose epilogue scatters each row to its stride_h x stride_w block of output pixels.
+    if (f.gather && f.k_is_dim0 && !f.shuf_sh && f.d_h == 1 && f.d_w == 1 && f.s_h * f.s_w > 1 &&
+        f.s_h * f.s_w * f.d1 <= 16 && f.out_layout == NML_NHWC && mi.enc == ENC_F16 && f.d1 == f.out_c &&
+        tune_env("NML_TUNE_SHUFFLE", 1)) {
+        const int C = f.d1, Kc = f.d0;
+        int dh_min = 1 << 20, dh_max = -(1 << 20), dw_min = 1 << 20, dw_max = -(1 << 20);
+        for (int ph = 0; ph < f.s_h; ++ph)
+            for (int kh = 0; kh < f.kh; ++kh) {
+                const int nh = ph + f.p_h - kh;
+                if (((nh % f.s_h) + f.s_h) % f.s_h != 0) continue;
+                const int dh = (nh >= 0) ? nh / f.s_h : -((-nh) / f.s_h);
+                dh_min = std::min(dh_min, dh);
+                dh_max = std::max(dh_max, dh);
+            }
+        for (int pw = 0; pw < f.s_w; ++pw)
+            for (int kw = 0; kw < f.kw; ++kw) {
+                const int nw = pw + f.p_w - kw;
+                if (((nw % f.s_w) + f.s_w) % f.s_w != 0) continue;
+                const int dw = (nw >= 0) ? nw / f.s_w : -((-nw) / f.s_w);
+                dw_min = std::min(dw_min, dw);
+                dw_max = std::max(dw_max, dw);
+            }
+        if (dh_min <= dh_max && dw_min <= dw_max && (dh_max - dh_min + 1) * (dw_max - dw_min + 1) <= kMaxTaps) {
+            const int khp = dh_max - dh_min + 1, kwp = dw_max - dw_min + 1;
+            const int np = f.s_h * f.s_w * C;
+            __half* wp = static_cast<__half*>(ws.take(static_cast<size_t>(np) * Kc * khp * kwp * sizeof(__half)));
+            float* bp = f.bias ? static_cast<float*>(ws.take(sizeof(float) * np)) : nullptr;
+            if (!ws.dry) {
+                if (!ws.fits()) return NML_ERR_WORKSPACE;
+                const int total = np * Kc * khp * kwp;
+                const int blocks = std::min(ceil_div(total, 256), 148 * 8);
+#define NML_PACK(TW, TB)                                                                                            \
+    pack_phase_weights_kernel<TW, TB><<<blocks, 256, 0, st>>>(static_cast<const TW*>(f.w), wp,                      \
+                                                              static_cast<const TB*>(f.bias), bp, Kc, C, f.kh, f.kw, \
+                                                              f.s_h, f.s_w, f.p_h, f.p_w, khp, kwp, dh_min, dw_min)
+                if (f.w_dtype == NML_F32) {
+                    if (f.bias_dtype == NML_F16) NML_PACK(float, __half); else NML_PACK(float, float);
+                } else {
+                    if (f.bias_dtype == NML_F16) NML_PACK(__half, __half); else NML_PACK(__half, float);
+                }
+#undef NML_PACK
+                ++g_launches;
+                NML_CUDA(cudaGetLastError());
+            }
+            FpropLike f2 = f;
+            f2.w = wp; f2.w_dtype = NML_F16; f2.d0 = np; f2.d1 = Kc; f2.kh = khp; f2.kw = kwp; f2.k_is_dim0 = 0;
+            f2.w_direct = 0; f2.gather = 0; f2.s_h = f2.s_w = 1; f2.p_h = -dh_min; f2.p_w = -dw_min;
+            f2.out_c = np; f2.out_h = ceil_div(f.out_h, f.s_h); f2.out_w = ceil_div(f.out_w, f.s_w);
+            f2.bias = bp; f2.bias_dtype = NML_F32;
+            f2.shuf_sh = f.s_h; f2.shuf_sw = f.s_w; f2.shuf_c = C; f2.shuf_oh = f.out_h; f2.shuf_ow = f.out_w;
+            return run_fprop_like(f2, ws, st);
+        }
+    }
     const int T = f.kh * f.kw;
     const int K = f.k_is_dim0 ? f.d0 : f.d1;
     const int N = f.k_is_dim0 ? f.d1 : f.d0;
@@ -544,7 +602,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     // Few output pixels under a long K loop (the 2x2 ... 8x8 layers of a U-Net): room for the fp32 partial
     // sums of a K-split walk.
     const size_t out_pixels = static_cast<size_t>(f.batch) * f.out_h * f.out_w;
-    const bool may_split = !window && T >= 4 && out_pixels <= 8192 && 1ll * T * c_blocks >= 32 && tune_env("NML_TUNE_FSPLIT", 1);
+    const bool may_split = !window && !f.shuf_sh && T >= 4 && out_pixels <= 8192 && 1ll * T * c_blocks >= 32 && tune_env("NML_TUNE_FSPLIT", 1);
     float* split_acc = may_split ? static_cast<float*>(ws.take(out_pixels * N * sizeof(float))) : nullptr;
     if (ws.dry) return NML_OK;
     if (!ws.fits()) return NML_ERR_WORKSPACE;
@@ -567,6 +625,11 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     P.out_f16 = (f.out_dtype == NML_F16);
     P.round_f16 = f.round_f16;
     P.c_out = N;
+    P.shuf_sh = f.shuf_sh;
+    P.shuf_sw = f.shuf_sw;
+    P.shuf_c = f.shuf_c;
+    P.shuf_oh = f.shuf_oh;
+    P.shuf_ow = f.shuf_ow;
     P.out_h = f.out_h;
     P.out_w = f.out_w;
     P.ld_out = N;

@@ -293,6 +293,40 @@ __global__ void __launch_bounds__(256) finish_rows_kernel(const float* __restric
     }
 }
 
+// Phase-packed gather walk: the weights [K][C][KH][KW] of a strided gather (input gradient of a
+// convolution, forward of a transposed one; unit dilation) as the weights [N'][K][KH'][KW'] of the
+// unit-stride convolution that computes all stride_h x stride_w output phases at once:
+// n' = (ph * s_w + pw) * C + c, tap (kh', kw') reads the input at offset (kh' + dh_min, kw' + dw_min),
+// which phase ph reaches through kernel row kh = ph + p_h - (kh' + dh_min) * s_h (zero weight if that
+// is no kernel row).  Also replicates the bias per phase.
+template <typename TIn, typename TBias>
+__global__ void __launch_bounds__(256) pack_phase_weights_kernel(const TIn* __restrict__ w, __half* __restrict__ out,
+                                                                 const TBias* __restrict__ bias, float* __restrict__ bias_out,
+                                                                 int K, int C, int KH, int KW, int s_h, int s_w, int p_h,
+                                                                 int p_w, int khp, int kwp, int dh_min, int dw_min) {
+    const int np = s_h * s_w * C;
+    const int total = np * K * khp * kwp;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < total; i += gridDim.x * blockDim.x) {
+        const int kw2 = i % kwp;
+        int r = i / kwp;
+        const int kh2 = r % khp;
+        r /= khp;
+        const int k = r % K;
+        const int n2 = r / K;
+        const int c = n2 % C;
+        const int pw = (n2 / C) % s_w;
+        const int ph = n2 / (C * s_w);
+        const int kh = ph + p_h - (kh2 + dh_min) * s_h;
+        const int kw = pw + p_w - (kw2 + dw_min) * s_w;
+        float v = 0.f;
+        if (kh >= 0 && kh < KH && kw >= 0 && kw < KW)
+            v = load_as_float(w, ((static_cast<size_t>(k) * C + c) * KH + kh) * KW + kw);
+        out[i] = __float2half_rn(v);
+    }
+    if (bias_out != nullptr && blockIdx.x == 0 && threadIdx.x < np)
+        bias_out[threadIdx.x] = (bias != nullptr) ? load_as_float(bias, threadIdx.x % C) : 0.f;
+}
+
 template <typename TIn>
 __global__ void __launch_bounds__(256) to_float_kernel(const TIn* __restrict__ in, float* out, int n) {
     int i = blockIdx.x * blockDim.x + threadIdx.x;

@@ -99,6 +99,12 @@ struct KParams {
     // atomics into a zeroed row-major scratch, which a small pass turns into the output.
     int fsplit;          // K slices per tile (1 = off)
     int base_tiles;      // tiles of one slice; tile id = slice * base_tiles + tile
+    // Phase-packed gather walk (strided input gradients / transposed forwards with very few output
+    // channels): the stride_h x stride_w output phases are packed into the tile's columns, column
+    // j = (ph * shuf_sw + pw) * shuf_c + c, so the walk is ONE unit-stride pass over the input whose row
+    // (n, i, j) scatters to out[n][shuf_sh*i + ph][shuf_sw*j + pw][c] (row-major output only).
+    int shuf_sh, shuf_sw;  // 0 = off
+    int shuf_c, shuf_oh, shuf_ow;
     int patch;           // 1: patch walk
     int patch_w, patch_h;    // patch extent in pixels
     int patch_bytes;     // bytes one patch buffer occupies (multiple of 1024)
@@ -1015,6 +1021,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             // tile decode
             int ntile, k_iters;
             bool row_valid;
+            int pix_n = 0, pix_h = 0, pix_w = 0;  // forward walk: this row's pixel within its phase grid
             size_t row_off = 0;     // NHWC / wgrad: element offset of column 0; NCHW: pixel offset
             size_t col_stride = 1;  // element distance between consecutive columns
             if (kMode == MODE_FPROP) {
@@ -1032,6 +1039,9 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 int ih = (th << P.hb_log2) + ((row >> P.wb_log2) & (hb - 1));
                 int n = (tn << P.nb_log2) + (row >> (P.wb_log2 + P.hb_log2));
                 row_valid = (iw < ph.wq) && (ih < ph.hq) && (n < P.batch);
+                pix_n = n;
+                pix_h = ih;
+                pix_w = iw;
                 int ow = ph.pw + P.out_stride_w * iw;
                 int oh = ph.ph + P.out_stride_h * ih;
                 k_iters = ph.tap_count;
@@ -1231,6 +1241,49 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     }
                     ++store_seq;
                     if (more) tmem_ld_wait();
+                }
+            } else
+            if (kMode == MODE_FPROP && kOutMode == OUT_NHWC && P.shuf_sh > 0) {
+                // Phase-packed columns: this thread's pixel owns shuf_sh rows of shuf_sw * shuf_c consecutive
+                // output values.  Short on purpose, like the few-channel epilogue below.
+                uint32_t r[16];
+                if (k_iters > 0) {
+                    tmem_ld_32x16(t_row, r);
+                    tmem_ld_wait();
+                }
+                if (row_valid) {
+                    const int run = P.shuf_sw * P.shuf_c;
+                    const int ow0 = P.shuf_sw * pix_w;
+                    const int oh0 = P.shuf_sh * pix_h;
+                    // column j = (phs, pw, c), walked with counters (no divisions in the unrolled body)
+                    int phs = 0, q = 0, pw = 0, cc = 0;
+                    size_t o_row = ((static_cast<size_t>(pix_n) * P.shuf_oh + oh0) * P.shuf_ow + ow0) * P.shuf_c;
+                    const size_t o_step = static_cast<size_t>(P.shuf_ow) * P.shuf_c;
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        if (j < P.c_out) {
+                            if (oh0 + phs < P.shuf_oh && ow0 + pw < P.shuf_ow) {
+                                float xv = (k_iters > 0) ? __uint_as_float(r[j]) : 0.f;
+                                if (P.bias != nullptr) xv += __ldg(P.bias + j);
+                                if (kOutF16) {
+                                    reinterpret_cast<__half*>(P.out)[o_row + q] = __float2half_rn(xv);
+                                } else {
+                                    if (P.round_f16) xv = round_through_f16(xv);
+                                    reinterpret_cast<float*>(P.out)[o_row + q] = xv;
+                                }
+                            }
+                            if (++cc == P.shuf_c) {
+                                cc = 0;
+                                ++pw;
+                            }
+                            if (++q == run) {
+                                q = 0;
+                                pw = 0;
+                                ++phs;
+                                o_row += o_step;
+                            }
+                        }
+                    }
                 }
             } else
             if (kMode == MODE_FPROP && kOutMode == OUT_NHWC && P.c_out <= 8 && P.fsplit <= 1) {
