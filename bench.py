@@ -166,7 +166,8 @@ def run_gpu(args):
     flops_per_launch = []  # algorithmic FLOPs of each contraction launch of one step, in launch order
 
     if args.workload == "linear":
-        sweep = LINEAR_SWEEP
+        # largest shapes first: under data parallelism their gradient all-reduce overlaps the smaller shapes' kernels
+        sweep = sorted(LINEAR_SWEEP, key=lambda s_: -s_[0] * s_[1] * s_[1])
         if args.only:  # profiling aid: one shape of the sweep, e.g. --only 16384x1024
             r_, d_ = (int(v) for v in args.only.lower().split("x"))
             sweep = [(r_, d_)]
@@ -420,18 +421,25 @@ def cpu_conv_sample(budget_s: float):
 
 
 def cpu_threads():
+    """Lets the BLAS behind np.matmul use every core this process may run on (launchers such as
+    torchrun export OMP_NUM_THREADS=1) and returns the thread count it ends up with."""
     try:
-        from threadpoolctl import threadpool_info
+        usable = len(os.sched_getaffinity(0))
+    except AttributeError:
+        usable = os.cpu_count() or 1
+    try:
+        from threadpoolctl import threadpool_info, threadpool_limits
+        threadpool_limits(limits=usable)
         n = max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
         return int(n)
     except Exception:
-        return os.cpu_count() or 1
+        return 1
 
 
 def cpu_baseline(workload: str, budget_s: float):
     if workload == "linear":
-        flops, secs, what = cpu_linear_sample(budget_s)
         cores = cpu_threads()
+        flops, secs, what = cpu_linear_sample(budget_s)
     else:
         flops, secs, what = cpu_conv_sample(budget_s)
         cores = 1

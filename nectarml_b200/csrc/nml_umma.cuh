@@ -567,7 +567,9 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                         // in a pair every load signals the LEADER's barrier, which expects both members' bytes
                         uint32_t fb = smem_u32(&full_bar[stage]);
                         if (kPair) fb = map_to_cta(fb, 0);
-                        if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err, ERR_WAIT_EMPTY)) {
+                        // (the issuing lanes leave together: a lane must never wait in __syncwarp for one that gave up)
+                        if (!__all_sync(issue_mask, mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err,
+                                                              ERR_WAIT_EMPTY))) {
                             ok = false;
                             break;
                         }
@@ -732,7 +734,8 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     for (int it = 0; it < k_total; it += P.ka) {  // one stage per iteration
                         uint32_t fb = smem_u32(&full_bar[stage]);
                         if (kPair) fb = map_to_cta(fb, 0);
-                        if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err, ERR_WAIT_EMPTY)) {
+                        if (!__all_sync(issue_mask, mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err,
+                                                              ERR_WAIT_EMPTY))) {
                             ok = false;
                             break;
                         }
