@@ -45,8 +45,6 @@ struct Bump {
     size_t off, cap;
     bool dry;
     DeviceState* ds = nullptr;  // when set, used instead of the lazily allocated per-device state
-    DeviceState* dev = nullptr;  // set by passes that may fork side work (bias-gradient sums)
-    cudaEvent_t join = nullptr;  // recorded on the side stream by such work; the pass waits for it at its end
     void* take(size_t bytes) {
         off = round_up(off, 256);
         void* p = dry ? nullptr : base + off;
@@ -125,10 +123,6 @@ struct DeviceState {
     int* err = nullptr;
     int sms = 0;
     bool attr_set = false;
-    // The bias gradient (a column sum, HBM-bound) runs beside the weight-gradient contraction (tensor-bound)
-    // on this stream, forked from and joined to the caller's stream with events.
-    cudaStream_t side = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
 };
 static DeviceState g_dev[64];
 static std::mutex g_dev_mutex;
@@ -185,9 +179,6 @@ static int device_state(DeviceState** out) {
         NML_CUDA(cudaMalloc(&s.err, sizeof(int)));
         NML_CUDA(cudaMemset(s.err, 0, sizeof(int)));
         NML_CUDA(cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev));
-        NML_CUDA(cudaStreamCreateWithFlags(&s.side, cudaStreamNonBlocking));
-        NML_CUDA(cudaEventCreateWithFlags(&s.ev_fork, cudaEventDisableTiming));
-        NML_CUDA(cudaEventCreateWithFlags(&s.ev_join, cudaEventDisableTiming));
     }
     if (!s.attr_set) {
         int rc_attr = raise_smem_limit();
@@ -228,23 +219,13 @@ static int prepare_activation(const void* src, int dtype, int layout, int batch,
             int col_blocks = ceil_div(c, 256);
             int rows_per_block = static_cast<int>(std::max<size_t>(64, round_up(ceil_div(static_cast<int>(std::min<size_t>(pixels, 1u << 30)), std::max(1, 1184 / col_blocks)), 8)));
             dim3 grid(col_blocks, static_cast<unsigned>((pixels + rows_per_block - 1) / rows_per_block));
-            cudaStream_t cs = st;
-            if (ws.dev && ws.dev->side && tune_env("NML_TUNE_SIDE", 1)) {  // beside the contraction, not in front of it
-                NML_CUDA(cudaEventRecord(ws.dev->ev_fork, st));
-                NML_CUDA(cudaStreamWaitEvent(ws.dev->side, ws.dev->ev_fork, 0));
-                cs = ws.dev->side;
-            }
             if (c % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-                colsum_rows_f16x8_kernel<<<grid, 256, 0, cs>>>(static_cast<const __half*>(src), colsum, pixels, c,
+                colsum_rows_f16x8_kernel<<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
                                                                rows_per_block);
                 ++g_launches;
             } else {
-                { colsum_rows_kernel<__half><<<grid, 256, 0, cs>>>(static_cast<const __half*>(src), colsum, pixels, c,
+                { colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
                                                                  rows_per_block); ++g_launches; }
-            }
-            if (cs != st) {
-                NML_CUDA(cudaEventRecord(ws.dev->ev_join, cs));
-                ws.join = ws.dev->ev_join;
             }
         }
         return NML_OK;
@@ -971,17 +952,7 @@ struct WgradLike {
     int math;
 };
 
-static int run_wgrad_like_impl(const WgradLike& g, Bump& ws, cudaStream_t st);
 static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
-    int rc = run_wgrad_like_impl(g, ws, st);
-    if (ws.join) {  // side work forked by the pass (bias-gradient sum) rejoins the caller's stream on every path
-        cudaError_t e = cudaStreamWaitEvent(st, ws.join, 0);
-        ws.join = nullptr;
-        if (e != cudaSuccess && rc == NML_OK) rc = NML_ERR_CUDA;
-    }
-    return rc;
-}
-static int run_wgrad_like_impl(const WgradLike& g, Bump& ws, cudaStream_t st) {
     MathInfo mi;
     if (!math_info(g.math, &mi)) return NML_ERR_INVALID;
     const int T = g.kh * g.kw;
@@ -993,7 +964,6 @@ static int run_wgrad_like_impl(const WgradLike& g, Bump& ws, cudaStream_t st) {
     if (!ws.dry) {
         int rc = device_state(&ds);
         if (rc) return rc;
-        ws.dev = ds;
         if (g.colsum) {
             int nsum = g.colsum_of_patch ? g.patch_c : g.plain_c;
             NML_CUDA(cudaMemsetAsync(g.colsum, 0, sizeof(float) * nsum, st));
