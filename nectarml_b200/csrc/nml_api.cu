@@ -394,6 +394,7 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
             if (P.stages < 2) return NML_ERR_UNSUPPORTED;
             b_region = P.stages * b_stage;
         }
+        P.issuers = (P.b_resident && P.a_stages >= 2 * P.c_blocks) ? 2 : 1;
         P.a_ring_off = static_cast<int>(round_up(b_region, 1024));
         P.ring_bytes = P.a_ring_off + P.a_stages * P.patch_bytes;
         smem = static_cast<size_t>(P.ring_bytes) + P.epi_warps * P.stg_bufs * kStagingBufBytes + fixed;

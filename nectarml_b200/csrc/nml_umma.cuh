@@ -110,6 +110,7 @@ struct KParams {
     int patch_bytes;     // bytes one patch buffer occupies (multiple of 1024)
     int a_stages;        // patch buffers
     int b_resident;      // 1: every B slice of the launch is loaded once, at [pass plane][cb][tap] * bn * 128
+    int issuers;         // resident patch walk: 2 = the B producer issues the odd tiles (needs a_stages >= 2 * c_blocks)
     int ring_bytes;      // bytes of the operand ring(s) in front of the staging buffers
     int a_ring_off;      // patch walk: offset of the patch buffers within the ring region
     int kind;            // KIND_F16 / KIND_TF32
@@ -325,6 +326,10 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
     // Nothing in it waits for B, so two warps can share the issuing: the MMA warp takes the even tiles
     // (accumulator 0) and the B producer, idle once the weights have landed, the odd ones (accumulator 1).
     // One warp's per-tile bookkeeping (barrier waits, commits) then hides behind the other's MMAs.
+    // A parity wait is only meaningful if the barrier's previous phase is known to be over.  An issuer waits
+    // for a patch only after the epilogue has drained tile t - 2 (the accumulator it reuses), i.e. after every
+    // patch up to that tile's last has landed; with a_stages >= 2 * c_blocks the patch that used the same
+    // buffer before is among those (or is this issuer's own), so the host allows two issuers only then.
     auto patch_resident_issue = [&](int t_first, int t_step) {
         const uint32_t idesc = make_instr_desc(P.kind, 0, P.b_mn_major, kTileM, P.bn);
         const bool b32 = P.b_mn_major && P.kind == KIND_TF32;
@@ -810,7 +815,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 }
             }
         }
-        if (kMode == MODE_FPROP && !kPair && P.patch && P.b_resident && warp == 6) {
+        if (kMode == MODE_FPROP && !kPair && P.patch && P.b_resident && P.issuers == 2 && warp == 6) {
             __syncwarp();
             patch_resident_issue(1, 2);  // the weights are in: help with the odd tiles
         }
@@ -842,7 +847,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
         bool ok = true;
         int titer = 0;
         if (kMode == MODE_FPROP && !kPair && P.patch && P.b_resident) {
-            patch_resident_issue(0, 2);
+            patch_resident_issue(0, P.issuers);
         } else
         for (int tile_id = tile_first; ok && (!kPair || leader) && tile_id < P.num_tiles; tile_id += tile_step, ++titer) {
             int tile = tile_id, kz = 0;

@@ -28,7 +28,7 @@ CONV_CASES = {
     "t_k2_s2":        (True,  (2, 7, 4, 4, 5, 2, 2, (2, 2), (0, 0), (1, 1), (0, 0)), True, "normal"),
 }
 
-# BASELINE config 1: Conv2d fp32, N=8, 64->64, 56x56, 3x3 s1 p1; sampled (the full tensors are 6 MB each).
+# benchmark configuration 1: Conv2d fp32, N=8, 64->64, 56x56, 3x3 s1 p1; sampled (the full tensors are 6 MB each).
 CONFIG1 = (False, (8, 64, 56, 56, 64, 3, 3, (1, 1), (1, 1), (1, 1), (0, 0)), True, "config1")
 CONFIG1_SEED = 1235
 CONFIG1_SAMPLES = 4096

@@ -8,7 +8,7 @@ It loads ``nectarml/cpu/conv/conv2d.py`` from that checkout on its own (the six 
 functions only need NumPy; ``nectarml.typing.float32`` is stubbed) and ``nectarml/cpu/math.py``
 for ``matmul``.  Linear gradients follow nectarml/core/_tensor/numerical.py:896-904 with
 ``cpu.math.matmul`` as the product, because the reference's CPU autograd for matmul raises
-(nectarml/core/_tensor/fake.py:94-97).  ``--config1`` adds the full-size BASELINE config 1
+(nectarml/core/_tensor/fake.py:94-97).  ``--config1`` adds the full-size benchmark configuration 1
 forward, which takes several minutes in the reference's pure-Python loop.
 """
 import importlib.util
@@ -71,7 +71,10 @@ def run_conv_case(ref, name, case, want_forward=True):
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    args = [a for a in sys.argv[1:] if not a.startswith("--")]
+    if not args:
+        raise SystemExit("usage: make_golden.py <path of the reference checkout> [--config1]")
+    root = args[0]
     ref, ref_math = load_reference(root)
     store = {}
     for name, case in cases.CONV_CASES.items():

@@ -1,4 +1,4 @@
-"""Full-size checks at BASELINE shapes (ResNet-style conv sweep at batch 256, Linear projections),
+"""Full-size checks at the benchmark shapes (ResNet-style conv sweep at batch 256, Linear projections),
 where running the CPU oracle on the whole tensor would take hours.  Two size-independent tools:
 
 * sampled outputs: a few thousand output elements are recomputed in float64 on the host straight
@@ -16,7 +16,7 @@ from nectarml_b200.ops import ConvGeometry
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
-# (c_in, hw, c_out, k, stride, pad) at batch 256 -- BASELINE config 3
+# (c_in, hw, c_out, k, stride, pad) at batch 256 -- benchmark configuration 3
 LAYERS = {
     "7x7s2_3_64_224": (3, 224, 64, 7, 2, 3),
     "3x3_64_64_56": (64, 56, 64, 3, 1, 1),
@@ -133,7 +133,7 @@ def test_resnet_shape_full_batch(name):
 
 @pytest.mark.parametrize("rows,d", [(16384, 1024), (16384, 2048)])
 def test_linear_projection_full_size(rows, d):
-    """BASELINE config 2 at its large shapes: sampled rows against float64 and the adjoint identity."""
+    """benchmark configuration 2 at its large shapes: sampled rows against float64 and the adjoint identity."""
     gen = torch.Generator(device=DEV).manual_seed(1236)
     x = torch.randn(rows, d, device=DEV, generator=gen).half()
     w = ((torch.rand(4 * d, d, device=DEV, generator=gen) * 2 - 1) * float(np.sqrt(6.0 / (5 * d)))).half()

@@ -157,7 +157,7 @@ def test_patch_walk_shapes(name, oracle):
 
 
 def test_config1_full_size(golden_config1, oracle):
-    """BASELINE config 1: Conv2d fp32 N=8 64->64 56x56 3x3 s1 p1, output, dX, dW and db."""
+    """benchmark configuration 1: Conv2d fp32 N=8 64->64 56x56 3x3 s1 p1, output, dX, dW and db."""
     case = cases.CONFIG1
     x, w, b, dy = cases.draw_conv("config1", case, cases.CONFIG1_SEED)
     y_o, dx_o, dw_o, db_o = oracle_all(oracle, case, x, w, b, dy)
@@ -204,7 +204,7 @@ def test_linear_fp32_and_fp16(name, golden_small, oracle):
 
 @pytest.mark.parametrize("rows,d", [(4096, 512), (1000, 520)])
 def test_linear_projection_shapes(rows, d, oracle):
-    """BASELINE config 2 family: X[rows, d] @ W^T[d, 4d] + b in fp16 with fp32 accumulation."""
+    """benchmark configuration 2 family: X[rows, d] @ W^T[d, 4d] + b in fp16 with fp32 accumulation."""
     rng = np.random.default_rng(1236)
     x = rng.standard_normal((rows, d), dtype=np.float32)
     bound = np.sqrt(6.0 / (d + 4 * d))

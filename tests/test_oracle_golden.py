@@ -62,7 +62,7 @@ def test_linear_oracle_matches_reference(name, golden_small, oracle):
 
 
 def test_config1_oracle_matches_reference(golden_config1, oracle):
-    """BASELINE config 1 at full size (Conv2d fp32, N=8, 64->64, 56x56, 3x3 s1 p1) against samples
+    """benchmark configuration 1 at full size (Conv2d fp32, N=8, 64->64, 56x56, 3x3 s1 p1) against samples
     of the reference's own outputs."""
     case = cases.CONFIG1
     x, w, b, dy = cases.draw_conv("config1", case, cases.CONFIG1_SEED)
