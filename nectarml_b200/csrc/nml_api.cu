@@ -356,7 +356,17 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
         P.epi_warps = (tma_out && short_k && P.bn / cpi >= 2 && tune_env("NML_TUNE_EPI8", 1)) ? 8 : 4;
     }
     size_t smem;
-    if (P.patch) {
+    if (P.wpatch) {
+        // [stages x (patch, box of the other tensor)][staging (unused by this walk)][bias][barriers]
+        P.ka = 1;
+        P.epi_warps = 4;
+        P.stg_bufs = 1;
+        const int w_stage = P.patch_bytes + P.bn * 128;
+        const int avail = 232448 - fixed - P.epi_warps * P.stg_bufs * kStagingBufBytes;
+        P.stages = std::max(2, std::min(8, avail / w_stage));
+        P.ring_bytes = P.stages * w_stage;
+        smem = static_cast<size_t>(P.ring_bytes) + P.epi_warps * P.stg_bufs * kStagingBufBytes + fixed;
+    } else if (P.patch) {
         // [B: resident slices, or a ring of single-slice stages][patch buffers][staging][bias][barriers]
         P.ka = 1;
         const int b_slice = P.bn * 128;
@@ -1035,6 +1045,40 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
         }
     const int bits = (mi.kb == 64) ? 6 : 5;
     choose_box(bits, g.plain_w, g.plain_h, g.batch, window ? 1 : g.s_w, g.s_h, &P.wb_log2, &P.hb_log2, &P.nb_log2);
+    // Patch walk: one 64-channel group per tap, unit column stride, few enough row tiles for TMEM, 8 x 8 pixel
+    // K blocks that do not waste much of the image, the other tensor fetched as grouped boxes.
+    {
+        const int groups = P.groups_total;
+        const int mt = ceil_div(groups, 2);
+        int dw_min = 0, dw_max = 0, dh_min = 0, dh_max = 0;
+        for (int t = 0; t < P.n_taps; ++t) {
+            dw_min = t ? std::min<int>(dw_min, P.taps[t].dw) : P.taps[t].dw;
+            dw_max = t ? std::max<int>(dw_max, P.taps[t].dw) : P.taps[t].dw;
+            dh_min = t ? std::min<int>(dh_min, P.taps[t].dh) : P.taps[t].dh;
+            dh_max = t ? std::max<int>(dh_max, P.taps[t].dh) : P.taps[t].dh;
+        }
+        const int pw_ = 8 + dw_max - dw_min, ph_ = 7 * g.s_h + dh_max - dh_min + 1;
+        const int bn_w = std::min(256, (512 / std::max(mt, 1)) / 64 * 64);
+        const double eff = static_cast<double>(g.plain_w) * g.plain_h / (1.0 * round_up(g.plain_w, 8) * round_up(g.plain_h, 8));
+        if (tune_env("NML_TUNE_WPATCH", 1) && mi.enc == ENC_F16 && P.c_blocks == 1 && groups >= 2 && mt <= 8 &&
+            (window || g.s_w == 1) && bn_w >= 64 && cpb % 64 == 0 && pw_ <= 256 && ph_ <= 256 &&
+            pw_ * ph_ * 128 <= 40 * 1024 && eff >= 0.7) {
+            P.wpatch = 1;
+            P.w_mtiles = mt;
+            P.bn = std::min(bn_w, static_cast<int>(round_up(g.plain_c, 64)));
+            P.n_tiles = ceil_div(g.plain_c, P.bn);
+            P.patch_w = pw_;
+            P.patch_h = ph_;
+            P.patch_bytes = static_cast<int>(round_up(pw_ * ph_ * 128, 1024));
+            P.phases[0].org_w = static_cast<short>(dw_min);
+            P.phases[0].org_h = static_cast<short>(dh_min);
+            for (int t = 0; t < P.n_taps; ++t)
+                P.taps[t].aoff = ((P.taps[t].dh - dh_min) * pw_ + (P.taps[t].dw - dw_min)) * 128 / 16;
+            P.wb_log2 = 3;
+            P.hb_log2 = 3;
+            P.nb_log2 = 0;
+        }
+    }
     P.ktiles_w = ceil_div(g.plain_w, 1 << P.wb_log2);
     P.ktiles_h = ceil_div(g.plain_h, 1 << P.hb_log2);
     P.kblocks_total = P.ktiles_w * P.ktiles_h * ceil_div(g.batch, 1 << P.nb_log2);
@@ -1042,8 +1086,8 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     const int G_ = kTileM / mi.kb;
     const bool a_grp = !window && (cpa % mi.kb == 0) && (P.c_blocks % G_ == 0);
     const bool b_grp = (cpb % mi.kb == 0);
-    P.pair = (tune_env("NML_TUNE_PAIR", 1) && P.bn == 256 && a_grp && b_grp && ds->sms >= 2) ? 1 : 0;
-    const int m_tiles = P.pair ? ceil_div(ceil_div(P.groups_total * mi.kb, kTileM), 2) : ceil_div(P.groups_total * mi.kb, kTileM);
+    P.pair = (tune_env("NML_TUNE_PAIR", 1) && !P.wpatch && P.bn == 256 && a_grp && b_grp && ds->sms >= 2) ? 1 : 0;
+    const int m_tiles = P.wpatch ? 1 : P.pair ? ceil_div(ceil_div(P.groups_total * mi.kb, kTileM), 2) : ceil_div(P.groups_total * mi.kb, kTileM);
     const int mn_tiles = m_tiles * P.n_tiles;
     // Split K so that the CTAs finish together: the makespan is (rounds of tiles per CTA) x (K
     // blocks per slice, plus a few blocks' worth of prologue / epilogue per tile).  Pick the split
@@ -1064,6 +1108,7 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
             }
         }
     }
+    if (P.wpatch) split = std::max(1, std::min(P.kblocks_total, ds->sms / std::max(1, P.n_tiles)));  // one tile per CTA
     P.split_k = split;
     P.num_tiles = mn_tiles * split;
     // A wave of CTAs re-reads one operand in full; make that the smaller tensor.
@@ -1082,6 +1127,12 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
                             static_cast<uint32_t>((1 << P.hb_log2) * g.s_h), static_cast<uint32_t>(1 << P.nb_log2)};
         uint32_t aes[4] = {1, static_cast<uint32_t>(g.s_w), static_cast<uint32_t>(g.s_h), 1};
         const int G = kTileM / mi.kb;
+        if (P.wpatch) {  // contiguous patch rows; the row stride of the walk lives in the MMA descriptors
+            abox[1] = static_cast<uint32_t>(P.patch_w);
+            abox[2] = static_cast<uint32_t>(P.patch_h);
+            abox[3] = 1;
+            aes[1] = aes[2] = 1;
+        }
         if (window) {
             uint64_t wd[4] = {64, static_cast<uint64_t>(g.plain_w), static_cast<uint64_t>(wimg.hp), static_cast<uint64_t>(g.batch)};
             uint64_t wstr[3] = {static_cast<uint64_t>(g.s_w) * 16, static_cast<uint64_t>(wimg.wp) * 16,
@@ -1089,7 +1140,15 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
             uint32_t wbox[4] = {64, static_cast<uint32_t>(1 << P.wb_log2), static_cast<uint32_t>((1 << P.hb_log2) * g.s_h),
                                 static_cast<uint32_t>(1 << P.nb_log2)};
             uint32_t wes[4] = {1, 1, static_cast<uint32_t>(g.s_h), 1};
+            if (P.wpatch) {
+                wbox[1] = abox[1];
+                wbox[2] = abox[2];
+                wbox[3] = 1;
+                wes[2] = 1;
+            }
             rc = encode_map(&P.tmA[pl], pa[pl], 2, 4, wd, wbox, wes, mn_swz, wstr);
+        } else if (P.wpatch) {
+            rc = encode_map(&P.tmA[pl], pa[pl], mi.es, 4, adims, abox, aes, mn_swz);
         } else if (cpa % mi.kb == 0 && P.c_blocks % G == 0) {
             P.a_grouped = 1;
             uint64_t d5[5] = {static_cast<uint64_t>(mi.kb), adims[1], adims[2], adims[3], static_cast<uint64_t>(cpa / mi.kb)};

@@ -105,6 +105,15 @@ struct KParams {
     // (n, i, j) scatters to out[n][shuf_sh*i + ph][shuf_sw*j + pw][c] (row-major output only).
     int shuf_sh, shuf_sw;  // 0 = off
     int shuf_c, shuf_oh, shuf_ow;
+    // Weight-gradient patch walk (unit column stride, one 64-channel group per tap): a CTA owns a slice of
+    // the K blocks (8 x 8 pixels of one image) and ALL row tiles of the gradient at once.  Per K block it
+    // loads one haloed patch of the tensor the taps are cut from and one box of the other tensor; row tile
+    // i = taps (2i, 2i+1) is an MN-major descriptor into the patch (start = the first tap's rows, the second
+    // tap's 64 columns LBO = their row distance away, 8-pixel groups one patch row * stride_h apart) and
+    // accumulates into its own TMEM columns [i * bn, (i+1) * bn).  Each tensor is then read from L2 about
+    // once instead of once per tap / once per row tile.
+    int wpatch;          // 1: weight-gradient patch walk
+    int w_mtiles;        // row tiles (accumulators), w_mtiles * bn <= 512
     int patch;           // 1: patch walk
     int patch_w, patch_h;    // patch extent in pixels
     int patch_bytes;     // bytes one patch buffer occupies (multiple of 1024)
@@ -277,7 +286,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     // two accumulators; the epilogue reads 32 columns at a time, so a 16-column tile still needs 16 + 32
-    const uint32_t tmem_need = (P.bn < 32) ? P.bn + 32 : 2 * P.bn;
+    const uint32_t tmem_need = P.wpatch ? P.w_mtiles * P.bn : (P.bn < 32) ? P.bn + 32 : 2 * P.bn;
     const uint32_t tmem_cols = (tmem_need <= 32) ? 32 : (tmem_need <= 64) ? 64 : (tmem_need <= 128) ? 128
                                : (tmem_need <= 256) ? 256 : 512;
 
@@ -401,7 +410,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
         // Weight-gradient operands that cannot be fetched as one box per K block get a lane per box.
         const int boxes_per_atom = (kMode != MODE_WGRAD || kPair) ? 1
                                    : do_a ? (P.a_grouped ? 1 : kTileM / P.kb) : (P.b_grouped ? 1 : P.bn / P.kb);
-        const int issue_lanes = P.patch ? 1 : P.ka * boxes_per_atom;
+        const int issue_lanes = (P.patch || P.wpatch) ? 1 : P.ka * boxes_per_atom;
         const uint32_t issue_mask = (1u << issue_lanes) - 1u;
         if (lane < issue_lanes) {
             int stage = 0;
@@ -611,6 +620,44 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                         if (++stage == P.stages) {
                             stage = 0;
                             parity ^= 1;
+                        }
+                    }
+                } else if (!kPair && P.wpatch) {  // MODE_WGRAD, patch walk: stage = [patch][box of the other tensor]
+                    const int ntile = tile % P.n_tiles, z = tile / P.n_tiles;
+                    const int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
+                    const int kb_begin = z * per, kb_end = min(kb_begin + per, P.kblocks_total);
+                    int tw = kb_begin % P.ktiles_w;
+                    int th = (kb_begin / P.ktiles_w) % P.ktiles_h;
+                    int tn = kb_begin / (P.ktiles_w * P.ktiles_h);
+                    const uint32_t w_stage = static_cast<uint32_t>(P.patch_bytes) + stage_b_bytes;
+                    const uint32_t patch_tx = static_cast<uint32_t>(P.patch_w) * P.patch_h * 128u;
+                    for (int kbi = kb_begin; kbi < kb_end; ++kbi) {
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), parity ^ 1, abort_flag, P.err, ERR_WAIT_EMPTY)) {
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t fb = smem_u32(&full_bar[stage]);
+                        const int w0 = tw << 3, h0 = th << 3;
+                        const uint32_t st_addr = smem_u32(smem) + stage * w_stage;
+                        if (do_a) {
+                            mbar_arrive_expect_tx(fb, patch_tx);
+                            tma_load_4d(st_addr, &P.tmA[0], fb, 0, w0 * P.a_stride_w + P.phases[0].org_w,
+                                        h0 * P.a_stride_h + P.phases[0].org_h, tn);
+                        } else {
+                            mbar_arrive_expect_tx(fb, stage_b_bytes);
+                            tma_load_5d(st_addr + P.patch_bytes, &P.tmB[0], fb, 0, w0, h0, tn, (ntile * P.bn) / P.kb);
+                        }
+                        ++issued;
+                        if (++stage == P.stages) {
+                            stage = 0;
+                            parity ^= 1;
+                        }
+                        if (++tw == P.ktiles_w) {
+                            tw = 0;
+                            if (++th == P.ktiles_h) {
+                                th = 0;
+                                ++tn;
+                            }
                         }
                     }
                 } else {  // MODE_WGRAD
@@ -876,6 +923,69 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             }
             const int buf = titer & 1;
             const uint32_t tpar = (titer >> 1) & 1;
+            if (kMode == MODE_WGRAD && !kPair && P.wpatch) {
+                // all row tiles at once, accumulator i in columns [i * bn, (i + 1) * bn); no second TMEM buffer, so
+                // the epilogue of the previous tile (if this CTA has one) must be over
+                const int z = tile / P.n_tiles;
+                const int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
+                const int nkb = max(min(z * per + per, P.kblocks_total) - z * per, 0);
+                if (!mbar_wait(smem_u32(&tempty_bar[0]), (titer & 1) ^ 1, abort_flag, P.err, ERR_WAIT_TMEM_EMPTY)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                if (lane == 0) NML_STAMP(titer, 0);
+                const uint32_t w_stage = static_cast<uint32_t>(P.patch_bytes) + stage_b_bytes;
+                const uint32_t sbo_a = static_cast<uint32_t>(P.patch_w * P.a_stride_h) * 128u;  // next pixel row of the K block
+                // Row tile i = taps (2i, 2i+1): its descriptor relative to stage 0, built once (a 64-column MMA
+                // lasts 48 clocks: the K loop has no time to build descriptors).
+                uint64_t ad[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int t0 = min(2 * i, P.groups_total - 1), t1 = min(2 * i + 1, P.groups_total - 1);
+                    const uint32_t a0 = static_cast<uint32_t>(P.taps[t0].aoff), a1 = static_cast<uint32_t>(P.taps[t1].aoff);
+                    ad[i] = make_smem_desc(smem_u32(smem) + (a0 << 4), (a1 - a0) << 4, sbo_a, 2);
+                }
+                const uint64_t bd0 = make_smem_desc(smem_u32(smem) + P.patch_bytes, box_bytes, 1024, 2);
+                const uint32_t a_step = (2u * sbo_a) >> 4;  // two pixel rows = 16 pixels = one MMA's K
+                const uint32_t stage_step16 = w_stage >> 4;
+                uint32_t accw = 0;
+                for (int kbi = 0; kbi < nkb; ++kbi) {
+                    if (!mbar_wait(smem_u32(&full_bar[stage]), parity, abort_flag, P.err, ERR_WAIT_FULL)) {
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    if (elect_one()) {
+                        const uint64_t so = static_cast<uint64_t>(stage * stage_step16);
+                        const uint64_t bdesc = bd0 + so;
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            if (i < P.w_mtiles) {
+                                const uint64_t adesc = ad[i] + so;
+                                const uint32_t d = tmem_base + i * P.bn;
+                                umma_f16(d, adesc, bdesc, idesc, accw);
+                                umma_f16(d, adesc + a_step, bdesc + adv_b, idesc, 1u);
+                                umma_f16(d, adesc + 2 * a_step, bdesc + 2 * adv_b, idesc, 1u);
+                                umma_f16(d, adesc + 3 * a_step, bdesc + 3 * adv_b, idesc, 1u);
+                            }
+                        }
+                        umma_commit(smem_u32(&empty_bar[stage]));
+                    }
+                    accw = 1u;
+                    if (++stage == P.stages) {
+                        stage = 0;
+                        parity ^= 1;
+                    }
+                }
+                if (!ok) break;
+                if (elect_one()) {
+                    NML_STAMP(titer, 2);
+                    if (nkb > 0) umma_commit(smem_u32(&tfull_bar[0]));
+                    else mbar_arrive(smem_u32(&tfull_bar[0]));
+                }
+                continue;
+            }
             if (!mbar_wait(smem_u32(&tempty_bar[buf]), tpar ^ 1, abort_flag, P.err, ERR_WAIT_TMEM_EMPTY)) {
                 ok = false;
                 break;
@@ -1023,6 +1133,57 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             if (kMode == MODE_FPROP && P.fsplit > 1) {
                 kz = tile_id / P.base_tiles;
                 tile = tile_id - kz * P.base_tiles;
+            }
+            if (kMode == MODE_WGRAD && !kPair && P.wpatch) {
+                // patch walk: every row tile of the gradient sits in TMEM, accumulator i in columns [i*bn, (i+1)*bn)
+                const int w_ntile = tile % P.n_tiles, w_z = tile / P.n_tiles;
+                const int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
+                const int nkb = max(min(w_z * per + per, P.kblocks_total) - w_z * per, 0);
+                if (!mbar_wait(smem_u32(&tfull_bar[0]), titer & 1, abort_flag, P.err, ERR_WAIT_TMEM_FULL)) {
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                if (threadIdx.x == 64) NML_STAMP(titer, 3);
+                const int w_col_base = w_ntile * P.bn;
+#pragma unroll 1
+                for (int i = 0; nkb > 0 && i < P.w_mtiles; ++i) {
+                    const int gi = i * (kTileM / P.kb) + row / P.kb;  // tap (kernel row with kw packing) of this row
+                    const int pc = row % P.kb;
+                    bool w_valid;
+                    size_t w_off, w_stride;
+                    if (P.kw_pack) {
+                        const int kwi = pc >> 3, c = pc & 7;
+                        w_valid = (gi < P.groups_total) && (c < P.c_patch) && (kwi < P.kw_count);
+                        w_off = (static_cast<size_t>(c) * P.n_taps + gi) * P.kw_count + kwi;
+                        w_stride = static_cast<size_t>(P.c_patch) * P.n_taps * P.kw_count;
+                    } else {
+                        w_valid = (gi < P.groups_total) && (pc < P.c_patch);
+                        w_off = static_cast<size_t>(pc) * P.n_taps + gi;
+                        w_stride = static_cast<size_t>(P.c_patch) * P.n_taps;
+                    }
+                    const uint32_t w_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + i * P.bn;
+                    for (int c0 = 0; c0 < P.bn; c0 += 32) {
+                        if (w_col_base + c0 >= P.c_out) break;  // uniform across the warp
+                        uint32_t r[32];
+                        tmem_ld_32x32(w_row + c0, r);
+                        tmem_ld_wait();
+                        const int cg = w_col_base + c0;
+                        const int ncols = min(32, P.c_out - cg);
+                        if (w_valid) {
+                            float* o = reinterpret_cast<float*>(P.out) + w_off + static_cast<size_t>(cg) * w_stride;
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < ncols) atomicAdd(o + j * w_stride, __uint_as_float(r[j]));
+                        }
+                        __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
+                    }
+                }
+                tc_fence_before();
+                __syncwarp();
+                if (threadIdx.x == 64) NML_STAMP(titer, 4);
+                if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[0]));
+                continue;
             }
             const int buf = titer & 1;
             const uint32_t tpar = (titer >> 1) & 1;

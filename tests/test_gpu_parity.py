@@ -156,6 +156,33 @@ def test_patch_walk_shapes(name, oracle):
     assert_f32(dx32, dx32_o, f"{name} dx fp32")
 
 
+# Weight gradients whose taps each hold one 64-channel group (or, for few-channel inputs, one kernel row of
+# packed windows) and whose other tensor has a multiple of 64 channels take the weight-gradient patch walk:
+# all row tiles in TMEM, one haloed patch per 8 x 8 pixel K block.
+WGRAD_PATCH_SHAPES = {
+    "w_3x3_64_64":    (False, (2, 64, 23, 15, 64, 3, 3, (1, 1), (1, 1), (1, 1), (0, 0)), True, "normal"),
+    "w_3x3_dil_128":  (False, (1, 32, 17, 24, 128, 3, 3, (1, 1), (2, 2), (2, 2), (0, 0)), True, "normal"),
+    "w_stem_7x7_s2":  (False, (2, 3, 30, 26, 64, 7, 7, (2, 2), (3, 3), (1, 1), (0, 0)), True, "normal"),
+    "w_rect_s21":     (False, (2, 48, 17, 19, 64, 2, 4, (2, 1), (0, 0), (1, 1), (0, 0)), False, "normal"),
+    "w_convT_to_5":   (True,  (2, 64, 15, 16, 5, 4, 4, (2, 2), (1, 1), (1, 1), (0, 0)), True, "normal"),
+    "w_5x5_192":      (False, (1, 40, 12, 16, 192, 5, 5, (1, 1), (2, 2), (1, 1), (0, 0)), True, "normal"),
+}
+
+
+@pytest.mark.parametrize("name", sorted(WGRAD_PATCH_SHAPES))
+def test_wgrad_patch_walk_shapes(name, oracle):
+    case = WGRAD_PATCH_SHAPES[name]
+    g = geometry(case)
+    x, w, b, dy = cases.draw_conv(name, case)
+    r = oracle.round_f16
+    _, _, dw_o, db_o = oracle_all(oracle, case, r(x), r(w), r(b) if b is not None else None, r(dy))
+    xd, dyd = dev(x, torch.float16, nhwc=True), dev(dy, torch.float16, nhwc=True)
+    dw, db = ops.conv_backward_weight(g, xd, dyd, layout="nhwc", math="f16")
+    ops.device_status()
+    assert_f32(host(dw), dw_o, f"{name} dw", tol=2e-5)
+    assert_f32(host(db), db_o, f"{name} db", tol=2e-5)
+
+
 def test_config1_full_size(golden_config1, oracle):
     """benchmark configuration 1: Conv2d fp32 N=8 64->64 56x56 3x3 s1 p1, output, dX, dW and db."""
     case = cases.CONFIG1
