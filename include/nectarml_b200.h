@@ -211,6 +211,28 @@ int nml_ref_conv_transpose2d_backward_weight(uintptr_t out_grad_ptr, uintptr_t i
                                              int dilation_w, int dtype, uintptr_t* result);
 /* C[..., M, N] = A[..., M, K] * B[K, N] (or batched B), row-major
  * (nectarml/csrc/ops/tensor/matmul.cpp:8-48).  a_shape / b_shape are host arrays. */
+/* 1-D convolutions (`_nectarml.tensor.conv.conv1d` ... `conv_transpose1d_backward_weight`,
+ * nectarml/csrc/python/ops/tensor/conv.h:11-68, called from nectarml/cuda/tensor/conv.py:12-106):
+ * tensors are [B, C, L], weights [C_out, C_in, K] ([C_in, C_out, K] transposed); the same rules on
+ * dtype, streams and ownership as the 2-D entry points (these have no half_precision flag). */
+int nml_ref_conv1d(uintptr_t input_ptr, uintptr_t weight_ptr, uintptr_t bias_ptr, int B, int C_in, int L,
+                   int C_out, int K, int stride, int padding, int dilation, int groups, int dtype,
+                   uintptr_t* result);
+int nml_ref_conv_transpose1d(uintptr_t input_ptr, uintptr_t weight_ptr, uintptr_t bias_ptr, int B, int C_in,
+                             int L, int C_out, int K, int stride, int padding, int dilation,
+                             int output_padding, int groups, int dtype, uintptr_t* result);
+int nml_ref_conv1d_backward_input(uintptr_t out_grad_ptr, uintptr_t weight_ptr, int B, int C_in, int L,
+                                  int C_out, int K, int L_out, int stride, int padding, int dilation,
+                                  int groups, int dtype, uintptr_t* result);
+int nml_ref_conv_transpose1d_backward_input(uintptr_t out_grad_ptr, uintptr_t weight_ptr, int B, int C_in,
+                                            int L, int C_out, int K, int L_out, int stride, int padding,
+                                            int dilation, int groups, int dtype, uintptr_t* result);
+int nml_ref_conv1d_backward_weight(uintptr_t out_grad_ptr, uintptr_t input_ptr, int B, int C_in, int L,
+                                   int C_out, int K, int L_out, int stride, int padding, int dilation,
+                                   int dtype, uintptr_t* result);
+int nml_ref_conv_transpose1d_backward_weight(uintptr_t out_grad_ptr, uintptr_t input_ptr, int B, int C_in,
+                                             int L, int C_out, int K, int L_out, int stride, int padding,
+                                             int dilation, int dtype, uintptr_t* result);
 int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_rank,
                    const int* b_shape, int b_rank, int dtype, uintptr_t* result);
 

@@ -62,6 +62,13 @@ SYMBOLS = {
     # backward_weight: 15 ints + dtype + result
     "nml_ref_conv2d_backward_weight": (_I, _ref_bwd_common + [_I, C.POINTER(_UP)]),
     "nml_ref_conv_transpose2d_backward_weight": (_I, _ref_bwd_common + [_I, C.POINTER(_UP)]),
+    # 1-D: (ptr, ptr, bias) + B, C_in, L, C_out, K, stride, padding, dilation[, output_padding], groups, dtype, result
+    "nml_ref_conv1d": (_I, [_UP, _UP, _UP] + [_I] * 10 + [C.POINTER(_UP)]),
+    "nml_ref_conv_transpose1d": (_I, [_UP, _UP, _UP] + [_I] * 11 + [C.POINTER(_UP)]),
+    "nml_ref_conv1d_backward_input": (_I, [_UP, _UP] + [_I] * 11 + [C.POINTER(_UP)]),
+    "nml_ref_conv_transpose1d_backward_input": (_I, [_UP, _UP] + [_I] * 11 + [C.POINTER(_UP)]),
+    "nml_ref_conv1d_backward_weight": (_I, [_UP, _UP] + [_I] * 10 + [C.POINTER(_UP)]),
+    "nml_ref_conv_transpose1d_backward_weight": (_I, [_UP, _UP] + [_I] * 10 + [C.POINTER(_UP)]),
     "nml_ref_matmul": (_I, [_UP, _UP, C.POINTER(_I), _I, C.POINTER(_I), _I, _I, C.POINTER(_UP)]),
     "nml_ref_free": (_I, [_UP]),
     "nml_debug_copy_to_host": (_I, [_VP, _UP, _SZ]),

@@ -92,6 +92,43 @@ class _Conv:
                      _dtype(dtype))
 
 
+    # 1-D convolutions (nectarml/csrc/python/ops/tensor/conv.h:11-68; callers nectarml/cuda/tensor/conv.py:12-106)
+    @staticmethod
+    def conv1d(input_ptr, weight_ptr, bias_ptr, B, C_in, L, C_out, K, stride, padding, dilation, groups, dtype) -> int:
+        return _call(_lib.load().nml_ref_conv1d, input_ptr, weight_ptr, bias_ptr or 0, B, C_in, L, C_out, K, stride,
+                     padding, dilation, groups, _dtype(dtype))
+
+    @staticmethod
+    def conv_transpose1d(input_ptr, weight_ptr, bias_ptr, B, C_in, L, C_out, K, stride, padding, dilation,
+                         output_padding, groups, dtype) -> int:
+        return _call(_lib.load().nml_ref_conv_transpose1d, input_ptr, weight_ptr, bias_ptr or 0, B, C_in, L, C_out, K,
+                     stride, padding, dilation, output_padding, groups, _dtype(dtype))
+
+    @staticmethod
+    def conv1d_backward_input(out_grad_ptr, weight_ptr, B, C_in, L, C_out, K, L_out, stride, padding, dilation,
+                              groups, dtype) -> int:
+        return _call(_lib.load().nml_ref_conv1d_backward_input, out_grad_ptr, weight_ptr, B, C_in, L, C_out, K, L_out,
+                     stride, padding, dilation, groups, _dtype(dtype))
+
+    @staticmethod
+    def conv_transpose1d_backward_input(out_grad_ptr, weight_ptr, B, C_in, L, C_out, K, L_out, stride, padding,
+                                        dilation, groups, dtype) -> int:
+        return _call(_lib.load().nml_ref_conv_transpose1d_backward_input, out_grad_ptr, weight_ptr, B, C_in, L, C_out,
+                     K, L_out, stride, padding, dilation, groups, _dtype(dtype))
+
+    @staticmethod
+    def conv1d_backward_weight(out_grad_ptr, input_ptr, B, C_in, L, C_out, K, L_out, stride, padding, dilation,
+                               dtype) -> int:
+        return _call(_lib.load().nml_ref_conv1d_backward_weight, out_grad_ptr, input_ptr, B, C_in, L, C_out, K, L_out,
+                     stride, padding, dilation, _dtype(dtype))
+
+    @staticmethod
+    def conv_transpose1d_backward_weight(out_grad_ptr, input_ptr, B, C_in, L, C_out, K, L_out, stride, padding,
+                                         dilation, dtype) -> int:
+        return _call(_lib.load().nml_ref_conv_transpose1d_backward_weight, out_grad_ptr, input_ptr, B, C_in, L, C_out,
+                     K, L_out, stride, padding, dilation, _dtype(dtype))
+
+
 class _Tensor:
     """``_nectarml.tensor``"""
     conv = _Conv()

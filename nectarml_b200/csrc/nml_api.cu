@@ -1669,6 +1669,50 @@ int nml_ref_conv_transpose2d_backward_weight(uintptr_t out_grad_ptr, uintptr_t i
                         W_out, stride_h, stride_w, padding_h, padding_w, dilation_h, dilation_w, dtype, result);
 }
 
+// 1-D convolutions are the same walks over an image of height 1 ([B, C, L] is [B, C, 1, L]).
+int nml_ref_conv1d(uintptr_t input_ptr, uintptr_t weight_ptr, uintptr_t bias_ptr, int B, int C_in, int L, int C_out,
+                   int K, int stride, int padding, int dilation, int groups, int dtype, uintptr_t* result) {
+    return ref_forward(0, input_ptr, weight_ptr, bias_ptr, 0, B, C_in, 1, L, C_out, 1, K, 1, stride, 0, padding, 1,
+                       dilation, 0, 0, groups, dtype, 0, result);
+}
+
+int nml_ref_conv_transpose1d(uintptr_t input_ptr, uintptr_t weight_ptr, uintptr_t bias_ptr, int B, int C_in, int L,
+                             int C_out, int K, int stride, int padding, int dilation, int output_padding, int groups,
+                             int dtype, uintptr_t* result) {
+    return ref_forward(1, input_ptr, weight_ptr, bias_ptr, 0, B, C_in, 1, L, C_out, 1, K, 1, stride, 0, padding, 1,
+                       dilation, 0, output_padding, groups, dtype, 0, result);
+}
+
+int nml_ref_conv1d_backward_input(uintptr_t out_grad_ptr, uintptr_t weight_ptr, int B, int C_in, int L, int C_out,
+                                  int K, int L_out, int stride, int padding, int dilation, int groups, int dtype,
+                                  uintptr_t* result) {
+    if (groups != 1) return NML_ERR_UNSUPPORTED;
+    return ref_backward(0, NML_PASS_BACKWARD_DATA, out_grad_ptr, weight_ptr, B, C_in, 1, L, C_out, 1, K, 1, L_out, 1,
+                        stride, 0, padding, 1, dilation, dtype, result);
+}
+
+int nml_ref_conv_transpose1d_backward_input(uintptr_t out_grad_ptr, uintptr_t weight_ptr, int B, int C_in, int L,
+                                            int C_out, int K, int L_out, int stride, int padding, int dilation,
+                                            int groups, int dtype, uintptr_t* result) {
+    if (groups != 1) return NML_ERR_UNSUPPORTED;
+    return ref_backward(1, NML_PASS_BACKWARD_DATA, out_grad_ptr, weight_ptr, B, C_in, 1, L, C_out, 1, K, 1, L_out, 1,
+                        stride, 0, padding, 1, dilation, dtype, result);
+}
+
+int nml_ref_conv1d_backward_weight(uintptr_t out_grad_ptr, uintptr_t input_ptr, int B, int C_in, int L, int C_out,
+                                   int K, int L_out, int stride, int padding, int dilation, int dtype,
+                                   uintptr_t* result) {
+    return ref_backward(0, NML_PASS_BACKWARD_WEIGHT, out_grad_ptr, input_ptr, B, C_in, 1, L, C_out, 1, K, 1, L_out, 1,
+                        stride, 0, padding, 1, dilation, dtype, result);
+}
+
+int nml_ref_conv_transpose1d_backward_weight(uintptr_t out_grad_ptr, uintptr_t input_ptr, int B, int C_in, int L,
+                                             int C_out, int K, int L_out, int stride, int padding, int dilation,
+                                             int dtype, uintptr_t* result) {
+    return ref_backward(1, NML_PASS_BACKWARD_WEIGHT, out_grad_ptr, input_ptr, B, C_in, 1, L, C_out, 1, K, 1, L_out, 1,
+                        stride, 0, padding, 1, dilation, dtype, result);
+}
+
 int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_rank, const int* b_shape, int b_rank,
                    int dtype, uintptr_t* result) {
     if (!a_shape || !b_shape || a_rank < 2 || b_rank < 2 || !result) return NML_ERR_INVALID;

@@ -131,6 +131,42 @@ def conv_transpose2d_backward_weight(dy, x, w_shape, stride=(1, 1), padding=(0, 
     return dw
 
 
+# 1-D convolutions (nectarml/cpu/conv/conv1d.py:20-215) are the 2-D loops over an image of height 1: the
+# reference's 1-D code accumulates in the same order (bias, then input channel, then kernel position).
+def _up(a):
+    return None if a is None else np.ascontiguousarray(np.asarray(a, np.float32)[:, :, None, :])
+
+
+def conv1d(x, w, bias, stride=1, padding=0, dilation=1):
+    return conv2d(_up(x), _up(w), bias, (1, stride), (0, padding), (1, dilation))[:, :, 0, :]
+
+
+def conv_transpose1d(x, w, bias, stride=1, padding=0, dilation=1, output_padding=0):
+    return conv_transpose2d(_up(x), _up(w), bias, (1, stride), (0, padding), (1, dilation), (0, output_padding))[:, :, 0, :]
+
+
+def conv1d_backward_input(dy, w, x_shape, stride=1, padding=0, dilation=1):
+    B, C, L = x_shape
+    return conv2d_backward_input(_up(dy), _up(w), (B, C, 1, L), (1, stride), (0, padding), (1, dilation))[:, :, 0, :]
+
+
+def conv1d_backward_weight(dy, x, w_shape, stride=1, padding=0, dilation=1):
+    Co, Ci, K = w_shape
+    return conv2d_backward_weight(_up(dy), _up(x), (Co, Ci, 1, K), (1, stride), (0, padding), (1, dilation))[:, :, 0, :]
+
+
+def conv_transpose1d_backward_input(dy, w, x_shape, stride=1, padding=0, dilation=1):
+    B, C, L = x_shape
+    return conv_transpose2d_backward_input(_up(dy), _up(w), (B, C, 1, L), (1, stride), (0, padding),
+                                           (1, dilation))[:, :, 0, :]
+
+
+def conv_transpose1d_backward_weight(dy, x, w_shape, stride=1, padding=0, dilation=1):
+    Ci, Co, K = w_shape
+    return conv_transpose2d_backward_weight(_up(dy), _up(x), (Ci, Co, 1, K), (1, stride), (0, padding),
+                                            (1, dilation))[:, :, 0, :]
+
+
 def bias_grad(dy):
     dy = _f32(dy)
     B, Co, Ho, Wo = dy.shape

@@ -26,6 +26,12 @@ def golden_config1():
 
 
 @pytest.fixture(scope="session")
+def golden_conv1d():
+    import numpy as np
+    return np.load(os.path.join(ROOT, "tests", "golden", "conv1d_cases.npz"))
+
+
+@pytest.fixture(scope="session")
 def oracle():
     from oracle import nectar_oracle
     nectar_oracle.build()

@@ -33,6 +33,29 @@ CONFIG1 = (False, (8, 64, 56, 56, 64, 3, 3, (1, 1), (1, 1), (1, 1), (0, 0)), Tru
 CONFIG1_SEED = 1235
 CONFIG1_SAMPLES = 4096
 
+# 1-D convolutions: name -> (transposed, (B, C_in, L, C_out, K, stride, padding, dilation, output_padding), bias?)
+CONV1D_CASES = {
+    "c1_basic":   (False, (2, 3, 24, 8, 3, 1, 1, 1, 0), True),
+    "c1_stride":  (False, (2, 6, 31, 10, 5, 2, 2, 1, 0), True),
+    "c1_dilated": (False, (1, 5, 40, 7, 3, 1, 3, 3, 0), False),
+    "c1_wide":    (False, (2, 72, 50, 40, 4, 3, 0, 1, 0), True),
+    "c1_t_s2":    (True,  (2, 8, 13, 4, 4, 2, 1, 1, 1), True),
+    "c1_t_s1":    (True,  (1, 5, 17, 6, 3, 1, 1, 2, 0), False),
+}
+
+
+def conv1d_as_2d(case):
+    """The same layer as a CONV_CASES-style tuple over an image of height 1."""
+    transposed, (B, Ci, L, Co, K, s, p, d, op), has_bias = case
+    return (transposed, (B, Ci, 1, L, Co, 1, K, (1, s), (0, p), (1, d), (0, op)), has_bias, "normal")
+
+
+def draw_conv1d(name, case):
+    """x [B, C_in, L], w [C_out, C_in, K] ([C_in, C_out, K] transposed), bias or None, dy [B, C_out, L_out]."""
+    x, w, b, dy = draw_conv(name, conv1d_as_2d(case))
+    return x[:, :, 0, :].copy(), w[:, :, 0, :].copy(), b, dy[:, :, 0, :].copy()
+
+
 LINEAR_CASES = {  # rows, in_features, out_features
     "lin_small": (4, 8, 4),
     "lin_odd": (37, 24, 19),

@@ -76,6 +76,30 @@ def main():
         raise SystemExit("usage: make_golden.py <path of the reference checkout> [--config1]")
     root = args[0]
     ref, ref_math = load_reference(root)
+    if "--conv1d" in sys.argv:
+        # the reference's 1-D functions (nectarml/cpu/conv/conv1d.py:20-215), its own file
+        spec = importlib.util.spec_from_file_location("_ref_conv1d", os.path.join(root, "nectarml/cpu/conv/conv1d.py"))
+        r1 = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(r1)
+        s1 = {}
+        for name, case in cases.CONV1D_CASES.items():
+            transposed, (B, Ci, L, Co, K, st, p, d, op), _ = case
+            x, w, b, dy = cases.draw_conv1d(name, case)
+            Lo = dy.shape[2]
+            if not transposed:
+                y, x_pad = r1.conv1d(x, w, b, B, Ci, Lo, Co, K, st, p, d, 1)
+                dx = r1.conv1d_backward_input(dy, x_pad, w, st, p, d, 1)
+                dw = r1.conv1d_backward_weight(dy, x_pad, w, st, p, d, 1)
+            else:
+                y = r1.conv_transpose1d(x, w, b, B, Ci, L, Co, K, st, p, d, op, 1)
+                dx = r1.conv_transpose1d_backward_input(dy, w, B, Ci, L, Co, K, Lo, st, p, d, 1)
+                dw = r1.conv_transpose1d_backward_weight(dy, x, B, Ci, L, Co, K, Lo, st, p, d, 1)
+            for k, v in (("y", y), ("dx", dx), ("dw", dw), ("db", dy.sum(axis=(0, 2)))):
+                s1[f"{name}__{k}"] = np.asarray(v, np.float32)
+            s1[f"{name}__insum"] = np.array([x.sum(dtype=np.float64), w.sum(dtype=np.float64), dy.sum(dtype=np.float64)])
+            print(name, y.shape, dx.shape, dw.shape)
+        np.savez_compressed(os.path.join(HERE, "conv1d_cases.npz"), **s1)
+        return
     store = {}
     for name, case in cases.CONV_CASES.items():
         (x, w, b, dy), out = run_conv_case(ref, name, case)

@@ -183,6 +183,43 @@ def test_wgrad_patch_walk_shapes(name, oracle):
     assert_f32(host(db), db_o, f"{name} db", tol=2e-5)
 
 
+@pytest.mark.parametrize("name", sorted(cases.CONV1D_CASES))
+def test_reference_shaped_conv1d(name, golden_conv1d, oracle):
+    """`_nectarml.tensor.conv.conv1d` ... `conv_transpose1d_backward_weight` in fp32 (3xTF32) against the
+    oracle and the fixtures produced by the reference's own 1-D functions."""
+    case = cases.CONV1D_CASES[name]
+    transposed, (B, Ci, L, Co, K, s, p, d, op), _ = case
+    x, w, b, dy = cases.draw_conv1d(name, case)
+    Lo = dy.shape[2]
+    if not transposed:
+        y_o = oracle.conv1d(x, w, b, s, p, d)
+        dx_o = oracle.conv1d_backward_input(dy, w, x.shape, s, p, d)
+        dw_o = oracle.conv1d_backward_weight(dy, x, w.shape, s, p, d)
+    else:
+        y_o = oracle.conv_transpose1d(x, w, b, s, p, d, op)
+        dx_o = oracle.conv_transpose1d_backward_input(dy, w, x.shape, s, p, d)
+        dw_o = oracle.conv_transpose1d_backward_weight(dy, x, w.shape, s, p, d)
+    xd, wd, dyd = dev(x), dev(w), dev(dy)
+    bd = dev(b) if b is not None else None
+    bp = bd.data_ptr() if bd is not None else 0
+    if not transposed:
+        y = fetch(conv.conv1d(xd.data_ptr(), wd.data_ptr(), bp, B, Ci, L, Co, K, s, p, d, 1, F32), (B, Co, Lo))
+        dx = fetch(conv.conv1d_backward_input(dyd.data_ptr(), wd.data_ptr(), B, Ci, L, Co, K, Lo, s, p, d, 1, F32), (B, Ci, L))
+        dw = fetch(conv.conv1d_backward_weight(dyd.data_ptr(), xd.data_ptr(), B, Ci, L, Co, K, Lo, s, p, d, F32), (Co, Ci, K))
+    else:
+        y = fetch(conv.conv_transpose1d(xd.data_ptr(), wd.data_ptr(), bp, B, Ci, L, Co, K, s, p, d, op, 1, F32), (B, Co, Lo))
+        dx = fetch(conv.conv_transpose1d_backward_input(dyd.data_ptr(), wd.data_ptr(), B, Ci, L, Co, K, Lo, s, p, d, 1, F32),
+                   (B, Ci, L))
+        dw = fetch(conv.conv_transpose1d_backward_weight(dyd.data_ptr(), xd.data_ptr(), B, Ci, L, Co, K, Lo, s, p, d, F32),
+                   (Ci, Co, K))
+    ops.device_status()
+    for got, orc, key in ((y, y_o, "y"), (dx, dx_o, "dx"), (dw, dw_o, "dw")):
+        assert_f32(got, orc, f"{name} {key} vs oracle")
+        assert_f32(got, golden_conv1d[f"{name}__{key}"], f"{name} {key} vs reference fixture")
+    with pytest.raises(RuntimeError):  # grouped convolution is refused, as the reference asserts on CUDA
+        conv.conv1d(xd.data_ptr(), wd.data_ptr(), bp, B, Ci, L, Co, K, s, p, d, 2, F32)
+
+
 def test_config1_full_size(golden_config1, oracle):
     """benchmark configuration 1: Conv2d fp32 N=8 64->64 56x56 3x3 s1 p1, output, dX, dW and db."""
     case = cases.CONFIG1

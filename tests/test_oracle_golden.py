@@ -50,6 +50,32 @@ def test_conv_oracle_matches_reference(name, golden_small, oracle):
     assert _close(oracle.bias_grad(dy), golden_small[f"{name}__db"])
 
 
+def _oracle_conv1d(oracle, case, x, w, b, dy):
+    transposed, (B, Ci, L, Co, K, s, p, d, op), _ = case
+    if not transposed:
+        return (oracle.conv1d(x, w, b, s, p, d), oracle.conv1d_backward_input(dy, w, x.shape, s, p, d),
+                oracle.conv1d_backward_weight(dy, x, w.shape, s, p, d))
+    return (oracle.conv_transpose1d(x, w, b, s, p, d, op), oracle.conv_transpose1d_backward_input(dy, w, x.shape, s, p, d),
+            oracle.conv_transpose1d_backward_weight(dy, x, w.shape, s, p, d))
+
+
+@pytest.mark.parametrize("name", sorted(cases.CONV1D_CASES))
+def test_conv1d_oracle_matches_reference(name, golden_conv1d, oracle):
+    """The 1-D wrappers of the oracle against the reference's own 1-D functions (nectarml/cpu/conv/conv1d.py)."""
+    case = cases.CONV1D_CASES[name]
+    x, w, b, dy = cases.draw_conv1d(name, case)
+    got = np.array([x.sum(dtype=np.float64), w.sum(dtype=np.float64), dy.sum(dtype=np.float64)])
+    assert np.array_equal(got, golden_conv1d[f"{name}__insum"]), "seeded inputs differ from those the fixtures saw"
+    y, dx, dw = _oracle_conv1d(oracle, case, x, w, b, dy)
+    if not case[0]:
+        # same accumulation order as the reference's scalar loop (bias, input channel, kernel position): bit-exact
+        assert np.array_equal(y, golden_conv1d[f"{name}__y"])
+    assert _close(y, golden_conv1d[f"{name}__y"])
+    assert _close(dx, golden_conv1d[f"{name}__dx"])
+    assert _close(dw, golden_conv1d[f"{name}__dw"])
+    assert _close(dy.sum(axis=(0, 2)), golden_conv1d[f"{name}__db"])
+
+
 @pytest.mark.parametrize("name", sorted(cases.LINEAR_CASES))
 def test_linear_oracle_matches_reference(name, golden_small, oracle):
     x, w, b, dy = cases.draw_linear(name, cases.LINEAR_CASES[name])
