@@ -166,8 +166,9 @@ def run_gpu(args):
     flops_per_launch = []  # algorithmic FLOPs of each contraction launch of one step, in launch order
 
     if args.workload == "linear":
-        # largest shapes first: under data parallelism their gradient all-reduce overlaps the smaller shapes' kernels
-        sweep = sorted(LINEAR_SWEEP, key=lambda s_: -s_[0] * s_[1] * s_[1])
+        # under data parallelism the largest shapes go first, so that their gradient all-reduce overlaps the
+        # smaller shapes' kernels (on one GPU the listed order measured 1-2 % faster)
+        sweep = sorted(LINEAR_SWEEP, key=lambda s_: -s_[0] * s_[1] * s_[1]) if world > 1 else list(LINEAR_SWEEP)
         if args.only:  # profiling aid: one shape of the sweep, e.g. --only 16384x1024
             r_, d_ = (int(v) for v in args.only.lower().split("x"))
             sweep = [(r_, d_)]
