@@ -365,6 +365,10 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
         const int avail = 232448 - fixed - P.epi_warps * P.stg_bufs * kStagingBufBytes;
         P.stages = std::max(2, std::min(8, avail / w_stage));
         P.ring_bytes = P.stages * w_stage;
+        {
+            const long long run = 1ll * P.c_patch * P.n_taps * (P.kw_pack ? P.kw_count : 1);
+            P.w_coalesce = (tune_env("NML_TUNE_WCOAL", 1) && 32 * run * 4 <= P.ring_bytes && P.num_tiles <= ds->sms) ? 1 : 0;
+        }
         smem = static_cast<size_t>(P.ring_bytes) + P.epi_warps * P.stg_bufs * kStagingBufBytes + fixed;
     } else if (P.patch) {
         // [B: resident slices, or a ring of single-slice stages][patch buffers][staging][bias][barriers]

@@ -114,6 +114,8 @@ struct KParams {
     // once instead of once per tap / once per row tile.
     int wpatch;          // 1: weight-gradient patch walk
     int w_mtiles;        // row tiles (accumulators), w_mtiles * bn <= 512
+    int w_coalesce;      // 1: the partial gradient leaves through shared memory as contiguous runs of adds
+                         //    (needs 32 gradient columns, 32 * c_patch * taps floats, to fit in the operand ring)
     int patch;           // 1: patch walk
     int patch_w, patch_h;    // patch extent in pixels
     int patch_bytes;     // bytes one patch buffer occupies (multiple of 1024)
@@ -300,7 +302,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             mbar_init(smem_u32(&tempty_bar[b]), (kPair ? 2 : 1) * P.epi_warps);  // the leader also hears the partner's epilogue warps
         }
         for (int s = 0; s < 4; ++s) {
-            mbar_init(smem_u32(&afull_bar[s]), 1);
+            mbar_init(smem_u32(&afull_bar[s]), P.wpatch ? 4 : 1);  // weight-gradient patch walk: the four epilogue warps meet here
             mbar_init(smem_u32(&aempty_bar[s]), 1);
         }
         mbar_init(smem_u32(bres_bar), 1);
@@ -1146,6 +1148,66 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 tc_fence_after();
                 if (threadIdx.x == 64) NML_STAMP(titer, 3);
                 const int w_col_base = w_ntile * P.bn;
+                if (P.w_coalesce && nkb > 0) {
+                    // A column of the gradient (one channel of the other tensor) is ONE contiguous run of
+                    // c_patch * taps floats in memory, and 32 columns are 32 such runs back to back.  Scattering the
+                    // accumulators' rows straight into them costs a 32-sector atomic per instruction; instead the
+                    // four warps lay 32 columns out in shared memory (the operand ring is idle by now: this CTA has
+                    // no further tile) and add them as contiguous 128-byte pieces.
+                    float* S = reinterpret_cast<float*>(smem);
+                    const size_t run = static_cast<size_t>(P.c_patch) * P.n_taps * (P.kw_pack ? P.kw_count : 1);
+                    uint32_t syncs = 0;
+                    auto meet = [&]() -> bool {  // bounded meeting of the four epilogue warps
+                        __syncwarp();
+                        const uint32_t bar = smem_u32(&afull_bar[syncs & 1]);
+                        if (lane == 0) mbar_arrive(bar);
+                        const bool met = mbar_wait(bar, (syncs >> 1) & 1, abort_flag, P.err, ERR_WAIT_TMEM_FULL);
+                        ++syncs;
+                        return met;
+                    };
+                    fence_proxy_async();
+                    for (int c0 = 0; ok && c0 < P.bn; c0 += 32) {
+                        const int cg = w_col_base + c0;
+                        if (cg >= P.c_out) break;  // uniform across the CTA
+                        const int ncols = min(32, P.c_out - cg);
+#pragma unroll 1
+                        for (int i = 0; i < P.w_mtiles; ++i) {
+                            const int gi = i * (kTileM / P.kb) + row / P.kb;
+                            const int pc = row % P.kb;
+                            bool w_valid;
+                            size_t w_off;
+                            if (P.kw_pack) {
+                                const int kwi = pc >> 3, c = pc & 7;
+                                w_valid = (gi < P.groups_total) && (c < P.c_patch) && (kwi < P.kw_count);
+                                w_off = (static_cast<size_t>(c) * P.n_taps + gi) * P.kw_count + kwi;
+                            } else {
+                                w_valid = (gi < P.groups_total) && (pc < P.c_patch);
+                                w_off = static_cast<size_t>(pc) * P.n_taps + gi;
+                            }
+                            uint32_t r[32];
+                            tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + i * P.bn + c0, r);
+                            tmem_ld_wait();
+                            if (w_valid) {
+#pragma unroll
+                                for (int j = 0; j < 32; ++j)
+                                    if (j < ncols) S[j * run + w_off] = __uint_as_float(r[j]);
+                            }
+                            __syncwarp();
+                        }
+                        if (!meet()) {
+                            ok = false;
+                            break;
+                        }
+                        float* o = reinterpret_cast<float*>(P.out) + static_cast<size_t>(cg) * run;
+                        const size_t total = static_cast<size_t>(ncols) * run;
+                        for (size_t idx = static_cast<size_t>(ew) * 32 + lane; idx < total; idx += 128) atomicAdd(o + idx, S[idx]);
+                        if (!meet()) {  // the next 32 columns overwrite S
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) break;
+                } else
 #pragma unroll 1
                 for (int i = 0; nkb > 0 && i < P.w_mtiles; ++i) {
                     const int gi = i * (kTileM / P.kb) + row / P.kb;  // tap (kernel row with kw packing) of this row
