@@ -116,3 +116,27 @@ def test_product_never_imports_the_oracle():
             if f.endswith((".py", ".cu", ".cuh", ".h")):
                 text = open(os.path.join(dirpath, f)).read()
                 assert "oracle" not in text, f"{f} mentions the oracle"
+
+
+def test_workspace_sizes_of_special_walks(lib):
+    """Workspace requests are computed without a device: the K-split forward walk asks for its fp32 partial
+    sums, the phase-packed gather walk for its packed weights and replicated bias."""
+    n = C.c_size_t()
+    # 4x4 s2 512->512 on a 4x4 image, batch 64: 64 x 2 x 2 output pixels x 512 channels of fp32 partial sums
+    # beside the repacked weights (512 x 16 taps x 512 ch x 2 B)
+    g = ConvGeometry(64, 512, 4, 4, 512, 4, 4, (2, 2), (1, 1))
+    d = g.desc(_lib.NML_F16, "nhwc", _lib.NML_F16, "nhwc", _lib.NML_F16, "f16", False)
+    assert lib.nml_conv_workspace_size(C.byref(d), 0, C.byref(n)) == 0
+    weights, partial = 512 * 16 * 512 * 2, 64 * 2 * 2 * 512 * 4
+    assert weights + partial <= n.value <= weights + partial + 4096
+    # input gradient of a 7x7 s2 3->64 stem: four output phases x 3 channels = 12 packed columns over 16 union
+    # taps of 64 channels (fp16), no bias; then the usual repack of those weights (16 columns of 64-wide K blocks)
+    g = ConvGeometry(4, 3, 32, 32, 64, 7, 7, (2, 2), (3, 3))
+    d = g.desc(_lib.NML_F16, "nhwc", _lib.NML_F16, "nhwc", _lib.NML_F16, "f16", False)
+    assert lib.nml_conv_workspace_size(C.byref(d), 1, C.byref(n)) == 0
+    packed = 12 * 64 * 16 * 2
+    assert 2 * packed <= n.value <= 2 * packed + 4096
+    # the same gradient into an NCHW tensor does not take the packed walk (one pass per phase instead)
+    d = g.desc(_lib.NML_F16, "nhwc", _lib.NML_F16, "nchw", _lib.NML_F16, "f16", False)
+    d.in_layout, d.out_layout = 1, 0  # dY NHWC, dX NCHW
+    assert lib.nml_conv_workspace_size(C.byref(d), 1, C.byref(n)) == 0
