@@ -871,6 +871,19 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     }
     P.num_tiles = tiles;
     P.base_tiles = tiles;
+    {   // division by multiplication in the kernels' tile decode: exact while tile index x divisor < 2^40
+        const unsigned long long one40 = 1ull << 40;
+        long long dmax = P.n_tiles;
+        P.mul_nt = one40 / static_cast<unsigned long long>(P.n_tiles) + 1;
+        for (int p = 0; p < n_phases; ++p) {
+            Phase& ph = P.phases[p];
+            ph.mul_w = one40 / static_cast<unsigned long long>(std::max(1, ph.tiles_w)) + 1;
+            ph.mul_h = one40 / static_cast<unsigned long long>(std::max(1, ph.tiles_h)) + 1;
+            dmax = std::max<long long>(dmax, std::max(ph.tiles_w, ph.tiles_h));
+        }
+        // (a pair doubles the row-tile index before it is divided)
+        P.fastdiv = (2ll * tiles < (1ll << 23) && 2ll * tiles * dmax < (1ll << 40)) ? 1 : 0;
+    }
     P.fsplit = 1;
     if (may_split && !P.pair && !P.patch && tiles * 2 <= ds->sms) {
         int k_min = k_iters_min;

@@ -67,6 +67,7 @@ struct Phase {
     int hq, wq;          // extent of the phase grid
     int tiles_h, tiles_w;
     int tile_begin;      // first tile id of this phase
+    unsigned long long mul_w, mul_h;  // 2^40 / tiles_w + 1, 2^40 / tiles_h + 1 (division by multiplication)
 };
 
 struct KParams {
@@ -76,6 +77,8 @@ struct KParams {
     CUtensorMap tmC;     // OUT_NHWC_TMA: the output, box = the 32 rows x 128 bytes one epilogue warp owns
     int mode, out_mode;
     int num_tiles, n_tiles;
+    unsigned long long mul_nt;  // 2^40 / n_tiles + 1
+    int fastdiv;         // 1: tile ids and divisors are small enough for the multiply-and-shift division to be exact
     int bn;              // UMMA N of one tile
     int stages;
     int cm_bw_log2, cm_bh_log2;  // OUT_NCHW_TMA: pixel sub-box (w, h) of one epilogue warp's 32 rows
@@ -165,6 +168,26 @@ struct KParams {
 #else
 #define NML_STAMP(titer, slot) do {} while (0)
 #endif
+
+// Tile decode runs once per tile in every role, and the epilogue warps in particular are bound by
+// instruction issue: a runtime integer division is ~25 instructions, the multiply-and-shift 4.
+// Exact for x * d < 2^40 (the host checks).
+__device__ __forceinline__ uint32_t fast_div(uint32_t x, unsigned long long mul) {
+    return static_cast<uint32_t>((static_cast<unsigned long long>(x) * mul) >> 40);
+}
+// Forward walk: tile index within its phase -> column tile and the (w, h, n) position of the row tile.
+template <bool kPair>
+__device__ __forceinline__ void decode_fprop_tile(const KParams& P, const Phase& ph, int local, uint32_t cta_rank,
+                                                  int& ntile, int& tw, int& th, int& tn) {
+    uint32_t m = P.fastdiv ? fast_div(local, P.mul_nt) : static_cast<uint32_t>(local) / P.n_tiles;
+    ntile = local - static_cast<int>(m) * P.n_tiles;
+    if (kPair) m = 2 * m + cta_rank;  // the pair's two row tiles
+    const uint32_t q = P.fastdiv ? fast_div(m, ph.mul_w) : m / ph.tiles_w;
+    tw = static_cast<int>(m - q * ph.tiles_w);
+    const uint32_t n = P.fastdiv ? fast_div(q, ph.mul_h) : q / ph.tiles_h;
+    th = static_cast<int>(q - n * ph.tiles_h);
+    tn = static_cast<int>(n);
+}
 
 // Tile id -> (column tile, row tile, K slice) of a weight-gradient launch.
 __device__ __forceinline__ void decode_wgrad_tile(const KParams& P, int tile, int m_tiles, int& ntile, int& mt, int& z) {
@@ -444,10 +467,8 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     for (int tile = tile_first; ok && tile < P.num_tiles; tile += tile_step) {
                         while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
                         const Phase& pt = P.phases[p];
-                        const int m = (tile - pt.tile_begin) / P.n_tiles;
-                        const int tw = m % pt.tiles_w;
-                        const int th = (m / pt.tiles_w) % pt.tiles_h;
-                        const int tn = m / (pt.tiles_w * pt.tiles_h);
+                        int nt_unused, tw, th, tn;
+                        decode_fprop_tile<false>(P, pt, tile - pt.tile_begin, 0u, nt_unused, tw, th, tn);
                         const int w0 = (tw << P.wb_log2) * P.a_stride_w + pt.org_w;
                         const int h0 = (th << P.hb_log2) * P.a_stride_h + pt.org_h;
                         for (int pass = 0; ok && pass < P.passes; ++pass) {
@@ -546,12 +567,8 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
                     const Phase& ph = P.phases[p];
                     int local = tile - ph.tile_begin;
-                    int ntile = local % P.n_tiles;
-                    int m = local / P.n_tiles;
-                    if (kPair) m = 2 * m + static_cast<int>(cta_rank);  // the pair's two row tiles
-                    int tw = m % ph.tiles_w;
-                    int th = (m / ph.tiles_w) % ph.tiles_h;
-                    int tn = m / (ph.tiles_w * ph.tiles_h);
+                    int ntile, tw, th, tn;
+                    decode_fprop_tile<kPair>(P, ph, local, cta_rank, ntile, tw, th, tn);
                     int w0 = (tw << P.wb_log2) * P.a_stride_w;
                     int h0 = (th << P.hb_log2) * P.a_stride_h;
                     int n0 = tn << P.nb_log2;
@@ -1260,12 +1277,8 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
                 const Phase& ph = P.phases[p];
                 int local = tile - ph.tile_begin;
-                ntile = local % P.n_tiles;
-                int m = local / P.n_tiles;
-                    if (kPair) m = 2 * m + static_cast<int>(cta_rank);  // the pair's two row tiles
-                int tw = m % ph.tiles_w;
-                int th = (m / ph.tiles_w) % ph.tiles_h;
-                int tn = m / (ph.tiles_w * ph.tiles_h);
+                int tw, th, tn;
+                decode_fprop_tile<kPair>(P, ph, local, cta_rank, ntile, tw, th, tn);
                 int iw = (tw << P.wb_log2) + (row & (wb - 1));
                 int ih = (th << P.hb_log2) + ((row >> P.wb_log2) & (hb - 1));
                 int n = (tn << P.nb_log2) + (row >> (P.wb_log2 + P.hb_log2));
@@ -1363,11 +1376,8 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
                     const Phase& ph = P.phases[p];
                     int local = tile - ph.tile_begin;
-                    int m = local / P.n_tiles;
-                    if (kPair) m = 2 * m + static_cast<int>(cta_rank);  // the pair's two row tiles
-                    int tw = m % ph.tiles_w;
-                    int th = (m / ph.tiles_w) % ph.tiles_h;
-                    int tn = m / (ph.tiles_w * ph.tiles_h);
+                    int nt_unused, tw, th, tn;
+                    decode_fprop_tile<kPair>(P, ph, local, cta_rank, nt_unused, tw, th, tn);
                     const int row0 = quarter * 32;
                     sw = ph.pw + P.out_stride_w * ((tw << P.wb_log2) + (row0 & (wb - 1)));
                     sh = ph.ph + P.out_stride_h * ((th << P.hb_log2) + ((row0 >> P.wb_log2) & (hb - 1)));
