@@ -1147,6 +1147,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
         bool ok = true;
         int titer = 0;
         uint32_t store_seq = 0;  // TMA-store pieces issued by this warp so far (selects the staging buffer)
+        int bias_ntile = -1;     // column tile whose bias values sit in this warp's shared-memory copy
         for (int tile_id = tile_first; ok && tile_id < P.num_tiles; tile_id += tile_step, ++titer) {
             int tile = tile_id, kz = 0;
             if (kMode == MODE_FPROP && P.fsplit > 1) {
@@ -1329,11 +1330,24 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             }
             if (kMode == MODE_FPROP && NML_IS_TMA_OUT(kOutMode) && P.bias != nullptr) {
                 // this tile's bias values, one copy per warp (no cross-warp barrier to get stuck on)
-                float* btw = bias_tile + ew * 256;
-                const int cb0 = ntile * P.bn;
-                __syncwarp();
-                for (int j = lane; j < P.bn; j += 32) btw[j] = (cb0 + j < P.c_out) ? __ldg(P.bias + cb0 + j) : 0.f;
-                __syncwarp();
+                // (skipped when the column tile is the one this warp loaded last; all eight loads of a lane are
+                // issued before the first is used, so the fill costs one memory latency, not eight)
+                if (ntile != bias_ntile) {
+                    bias_ntile = ntile;
+                    float* btw = bias_tile + ew * 256;
+                    const int cb0 = ntile * P.bn;
+                    float bv[8];
+#pragma unroll
+                    for (int u = 0; u < 8; ++u) {
+                        const int j = lane + 32 * u;
+                        bv[u] = (j < P.bn && cb0 + j < P.c_out) ? __ldg(P.bias + cb0 + j) : 0.f;
+                    }
+                    __syncwarp();
+#pragma unroll
+                    for (int u = 0; u < 8; ++u)
+                        if (lane + 32 * u < P.bn) btw[lane + 32 * u] = bv[u];
+                    __syncwarp();
+                }
             }
             // Row-major epilogue: this lane's bias slice for the first 128-byte piece is fetched before
             // the wait, and each later slice one piece ahead, so the load latency never shows.
