@@ -434,8 +434,7 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
     const bool rec = g_prof.on && g_prof.n < g_prof.cap;
     if (rec) NML_CUDA(cudaEventRecord(g_prof.start[g_prof.n], st));
     if (P.pair) {
-        cudaLaunchConfig_t cfg;
-        memset(&cfg, 0, sizeof(cfg));
+        cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid);
         cfg.blockDim = dim3(threads_for(P.mode == MODE_FPROP ? P.out_mode : OUT_NHWC));
         cfg.dynamicSmemBytes = smem;

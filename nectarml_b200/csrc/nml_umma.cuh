@@ -457,7 +457,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 }
             };
             if (kMode == MODE_FPROP && !kPair && P.patch) {  // (issue_lanes == 1 here)
-                const Phase& ph = P.phases[0];
                 if (do_a) {
                     const uint32_t a_base = smem_u32(smem + P.a_ring_off);
                     const uint32_t patch_tx = static_cast<uint32_t>(P.patch_w) * P.patch_h * 128u;
