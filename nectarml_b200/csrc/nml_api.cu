@@ -72,8 +72,17 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// Tuning overrides for experiments (unset in normal use): NML_TUNE_STAGES caps the ring depth,
-// NML_TUNE_BN caps the tile width, NML_TUNE_L2PROMO picks the TMA L2 promotion (0..3).
+// Tuning overrides for experiments and A/B measurements (unset in normal use; every default is the
+// measured-best setting):
+//   NML_TUNE_STAGES   cap on the ring depth            NML_TUNE_BN        forced tile width (64 / 128 / 256)
+//   NML_TUNE_KA       K atoms per stage (1 or 2)       NML_TUNE_L2PROMO   TMA L2 promotion (0..3)
+//   NML_TUNE_PAIR     0: no CTA pairs                  NML_TUNE_TMASTORE  0: no TMA-store epilogues
+//   NML_TUNE_EPI8     0: never a second epilogue group NML_TUNE_EPI8_K    K slices up to which it is used
+//   NML_TUNE_PATCH    0: no forward patch walk, 2: wherever it is legal, 3: also with streamed weights
+//   NML_TUNE_BRES     0: patch walk streams its weights NML_TUNE_SHUFFLE  0: no phase-packed gather walk
+//   NML_TUNE_FSPLIT   0: no K split of the forward walk
+//   NML_TUNE_WPATCH   0: no weight-gradient patch walk NML_TUNE_WCOAL     0: its gradient leaves by scattered atomics
+// (NML_DBG_* exist only in builds with -DNML_TRACE.)
 static int tune_env(const char* name, int dflt) {
     const char* v = getenv(name);
     return (v && *v) ? atoi(v) : dflt;
