@@ -437,6 +437,20 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                                    : do_a ? (P.a_grouped ? 1 : kTileM / P.kb) : (P.b_grouped ? 1 : P.bn / P.kb);
         const int issue_lanes = (P.patch || P.wpatch) ? 1 : P.ka * boxes_per_atom;
         const uint32_t issue_mask = (1u << issue_lanes) - 1u;
+        if (kMode == MODE_FPROP && !kPair && P.patch && P.b_resident && do_b) {
+            // Resident weights: every slice once, for the whole launch (one column tile, one pass plane, K-major
+            // repacked weights).  The slices are spread over the lanes of the warp, so the dozens of TMA issues at
+            // the start of the kernel cost one thread's worth of them, not their sum.
+            const uint32_t fb = smem_u32(bres_bar);
+            const int slices = P.c_blocks * P.n_taps;
+            if (lane == 0) mbar_arrive_expect_tx(fb, static_cast<uint32_t>(slices) * stage_b_bytes);
+            __syncwarp();
+            for (int i = lane; i < slices; i += 32) {
+                const int cb = i / P.n_taps, t = i - cb * P.n_taps;  // slot order [cb][tap of every phase]
+                tma_load_2d(smem_u32(smem) + i * stage_b_bytes, &P.tmB[0], fb, P.taps[t].wk + cb * P.kb, 0);
+            }
+            __syncwarp();
+        }
         if (lane < issue_lanes) {
             int stage = 0;
             uint32_t parity = 0;
@@ -509,12 +523,8 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     ok = true;   // nothing left for the common unwinding below
                     issued = 0;
                 } else if (P.b_resident) {
-                    // every slice once, for the whole launch (one column tile, one pass plane)
+                    // (the slices were requested above, by the whole warp)
                     const uint32_t fb = smem_u32(bres_bar);
-                    mbar_arrive_expect_tx(fb, static_cast<uint32_t>(P.c_blocks) * P.n_taps * stage_b_bytes);
-                    for (int cb = 0; cb < P.c_blocks; ++cb)
-                        for (int t = 0; t < P.n_taps; ++t)  // the taps of every phase
-                            load_b(smem_u32(smem) + (cb * P.n_taps + t) * stage_b_bytes, &P.tmB[0], fb, P.taps[t], cb, 0);
                     // the MMA warp waits for these before its first tile; if it gave up, wait here (bounded) so
                     // that no copy is in flight when the CTA's shared memory goes away
                     uint64_t t0 = globaltimer_ns();
