@@ -151,6 +151,7 @@ __global__ void __launch_bounds__(256) colsum_rows_f16x8_kernel(const __half* __
     size_t r1 = r0 + rows_per_block < R ? r0 + rows_per_block : R;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
     if (c0 < C) {
+#pragma unroll 4  // several 16-byte loads in flight per thread: the pass is HBM-bound
         for (size_t r = r0 + wy; r < r1; r += 8) {
             uint4 v = __ldg(reinterpret_cast<const uint4*>(in + r * C + c0));
             const __half2* h = reinterpret_cast<const __half2*>(&v);
