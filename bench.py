@@ -376,7 +376,7 @@ def run_gpu(args):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per contraction launch, averaged over one step of the
 # workload, from the ncu capture summarised under profiles/ (None until a capture exists).
-TRAFFIC_BYTES_PER_LAUNCH = {"linear": 164.9e6, "resnet": None, "pix2pix": None}
+TRAFFIC_BYTES_PER_LAUNCH = {"linear": 164.5e6, "resnet": None, "pix2pix": None}
 
 
 # ------------------------------------------------------------ CPU reference arm --
