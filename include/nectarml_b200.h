@@ -5,7 +5,8 @@
  * Two layers of entry points:
  *
  *  (1) nml_conv_* / nml_linear_*  -- descriptor based, caller-owned outputs and workspace,
- *      explicit stream, no allocation, no synchronisation, int status return.
+ *      explicit stream, no allocation, no synchronisation, int status return.  The one exception
+ *      is the first call on each device, which does what nml_init() does (see there).
  *  (2) nml_ref_*                  -- the flat signatures of the reference's host ops
  *      (device pointers as integers + shape ints in, freshly cudaMalloc'ed result out), so a
  *      binding of the reference's `_nectarml.tensor.conv.*` / `_nectarml.tensor.matmul`
@@ -87,6 +88,14 @@ enum { NML_PASS_FORWARD = 0, NML_PASS_BACKWARD_DATA = 1, NML_PASS_BACKWARD_WEIGH
 
 const char* nml_status_string(int status);
 
+/* One-time set-up of the CURRENT device: looks up the device-side status word (it lives in the
+ * library image, nothing is allocated), clears it with a synchronous cudaMemset, loads every
+ * kernel of the library and raises the contraction kernel's dynamic shared-memory limit.  Every
+ * entry point does this by itself on its first call on a device; call nml_init() explicitly
+ * when that first call would otherwise fall inside a CUDA stream capture or a latency-critical
+ * section.  Thread-safe; later calls return immediately. */
+int nml_init(void);
+
 /* Output size of the layer described by d (height, width). Returns a status. */
 int nml_conv_output_size(const nml_conv_desc* d, int* h_out, int* w_out);
 
@@ -131,7 +140,9 @@ int nml_conv_backward_data(const nml_conv_desc* d, const void* dy, const void* w
                            void* workspace, size_t workspace_bytes, void* stream);
 
 /* Weight gradient (overwrites dw, fp32, weight-shaped) and, when db != NULL, the bias gradient
- * db[c] = sum over batch and pixels of dy (fp32).  Replaces run_conv2d_backward_weight /
+ * db[c] = sum over batch and pixels of dy (fp32).  dw is bitwise repeatable from run to run: K
+ * slices store partial sums into planes of the workspace that a second kernel adds in a fixed
+ * order (no atomics); so are y and dx of every forward / input-gradient walk.  Replaces run_conv2d_backward_weight /
  * run_conv_transpose2d_backward_weight (conv2d.cpp:276-335, 337-395) and the three chained
  * reductions of `out_grad.sum(dim=(0,2,3))` (nectarml/cuda/tensor/conv.py:175-176). */
 int nml_conv_backward_weight(const nml_conv_desc* d, const void* x, const void* dy, float* dw,
@@ -151,7 +162,8 @@ int nml_linear_backward_weight(const nml_linear_desc* d, const void* x, const vo
                                float* db, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Synchronises the current device and returns NML_OK, or NML_ERR_DEVICE with *code set to the
- * wait that timed out inside a kernel since the last call (and clears it).  The asynchronous
+ * wait that timed out inside a kernel since the last call (and clears it; nml_status_string then
+ * names the wait).  The asynchronous
  * entry points above never block, so this is how a caller learns of a device-side give-up. */
 int nml_device_status(int* code);
 
@@ -209,8 +221,6 @@ int nml_ref_conv_transpose2d_backward_weight(uintptr_t out_grad_ptr, uintptr_t i
                                              int H_out, int W_out, int stride_h, int stride_w,
                                              int padding_h, int padding_w, int dilation_h,
                                              int dilation_w, int dtype, uintptr_t* result);
-/* C[..., M, N] = A[..., M, K] * B[K, N] (or batched B), row-major
- * (nectarml/csrc/ops/tensor/matmul.cpp:8-48).  a_shape / b_shape are host arrays. */
 /* 1-D convolutions (`_nectarml.tensor.conv.conv1d` ... `conv_transpose1d_backward_weight`,
  * nectarml/csrc/python/ops/tensor/conv.h:11-68, called from nectarml/cuda/tensor/conv.py:12-106):
  * tensors are [B, C, L], weights [C_out, C_in, K] ([C_in, C_out, K] transposed); the same rules on
@@ -233,6 +243,10 @@ int nml_ref_conv1d_backward_weight(uintptr_t out_grad_ptr, uintptr_t input_ptr, 
 int nml_ref_conv_transpose1d_backward_weight(uintptr_t out_grad_ptr, uintptr_t input_ptr, int B, int C_in,
                                              int L, int C_out, int K, int L_out, int stride, int padding,
                                              int dilation, int dtype, uintptr_t* result);
+/* C[..., M, N] = A[..., M, K] * B[K, N] (or batched B), row-major
+ * (nectarml/csrc/ops/tensor/matmul.cpp:8-48).  a_shape / b_shape are host arrays.  A 2-D B is
+ * shared by every batch entry of A (the reference advances B per batch entry even then,
+ * matmul.cpp:27,39, and reads past its end). */
 int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_rank,
                    const int* b_shape, int b_rank, int dtype, uintptr_t* result);
 
@@ -248,6 +262,22 @@ int nml_debug_tma_box(const void* tensor, int elem_bytes, const int dims[4], con
                       const int elem_strides[4], const int coords[4], void* out, size_t out_bytes,
                       void* stream);
 
+
+/* Give-up path, exercised without a fault: one warp waits with the library's bounded wait on an
+ * mbarrier nothing arrives on; after limit_ns (at most 1e8) the wait runs out, the kernel records
+ * the wait code in the status word (use_static_word != 0: the word nml_conv_forward_static's
+ * kernels report into) and returns.  nml_device_status / the d == NULL form of
+ * nml_conv_forward_static then report NML_ERR_DEVICE once. */
+int nml_debug_wait_timeout(unsigned long long limit_ns, int use_static_word, void* stream);
+
+/* The same through the contraction kernel itself: a small fp16 Linear forward whose activation
+ * boxes are encoded half as tall as the kernel expects, so no pipeline stage ever receives all
+ * its bytes; the MMA warp's wait runs out after limit_ns, every role unwinds through its bounded
+ * waits, TMEM is freed and the kernel returns (y is left unwritten).  rows <= 4096,
+ * in_features <= 1024, out_features <= 128, fp16 tensors only. */
+int nml_debug_stalled_linear_forward(const nml_linear_desc* d, const void* x, const void* w, void* y,
+                                     void* workspace, size_t workspace_bytes,
+                                     unsigned long long limit_ns, void* stream);
 
 /* Blocking device-to-host copy of a result pointer, as the reference's tensor read-back does
  * (nectarml/csrc/ops/system/device/device.cpp:39-64).  Lets a test read what nml_ref_* returned

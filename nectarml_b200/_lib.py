@@ -48,6 +48,7 @@ SYMBOLS = {
     "nml_linear_forward": (_I, [C.POINTER(LinearDesc), _VP, _VP, _VP, _VP, _VP, _SZ, _VP]),
     "nml_linear_backward_data": (_I, [C.POINTER(LinearDesc), _VP, _VP, _VP, _VP, _SZ, _VP]),
     "nml_linear_backward_weight": (_I, [C.POINTER(LinearDesc), _VP, _VP, _VP, _VP, _VP, _SZ, _VP]),
+    "nml_init": (_I, []),
     "nml_device_status": (_I, [C.POINTER(_I)]),
     "nml_launch_count": (C.c_longlong, []),
     "nml_profile_begin": (_I, [_I]),
@@ -72,6 +73,8 @@ SYMBOLS = {
     "nml_ref_matmul": (_I, [_UP, _UP, C.POINTER(_I), _I, C.POINTER(_I), _I, _I, C.POINTER(_UP)]),
     "nml_ref_free": (_I, [_UP]),
     "nml_debug_copy_to_host": (_I, [_VP, _UP, _SZ]),
+    "nml_debug_wait_timeout": (_I, [C.c_ulonglong, _I, _VP]),
+    "nml_debug_stalled_linear_forward": (_I, [C.POINTER(LinearDesc), _VP, _VP, _VP, _VP, _SZ, C.c_ulonglong, _VP]),
     "nml_debug_tma_box": (_I, [_VP, _I, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), C.POINTER(_I),
                                _VP, _SZ, _VP]),
 }

@@ -9,6 +9,7 @@
 #include <string.h>
 
 #include <algorithm>
+#include <atomic>
 #include <mutex>
 #include <vector>
 
@@ -30,6 +31,7 @@ namespace nml {
 
 static thread_local char g_last_error[256] = {0};
 static thread_local char g_last_scratch_error[256] = {0};
+static thread_local char g_last_device_error[96] = {0};
 static void set_last_cuda_error(cudaError_t e, const char* what) {
     snprintf(g_last_error, sizeof(g_last_error), "%s: %s", what, cudaGetErrorString(e));
 }
@@ -72,8 +74,8 @@ static EncodeTiledFn get_encode_fn() {
     return fn;
 }
 
-// Tuning overrides for experiments and A/B measurements (unset in normal use; every default is the
-// measured-best setting):
+// Tuning overrides for experiments and A/B measurements, read from the environment ONCE, when the
+// library is first used (unset in normal use; every default is the measured-best setting):
 //   NML_TUNE_STAGES   cap on the ring depth            NML_TUNE_BN        forced tile width (64 / 128 / 256)
 //   NML_TUNE_KA       K atoms per stage (1 or 2)       NML_TUNE_L2PROMO   TMA L2 promotion (0..3)
 //   NML_TUNE_PAIR     0: no CTA pairs                  NML_TUNE_TMASTORE  0: no TMA-store epilogues
@@ -81,11 +83,34 @@ static EncodeTiledFn get_encode_fn() {
 //   NML_TUNE_PATCH    0: no forward patch walk, 2: wherever it is legal, 3: also with streamed weights
 //   NML_TUNE_BRES     0: patch walk streams its weights NML_TUNE_SHUFFLE  0: no phase-packed gather walk
 //   NML_TUNE_FSPLIT   0: no K split of the forward walk
-//   NML_TUNE_WPATCH   0: no weight-gradient patch walk NML_TUNE_WCOAL     0: its gradient leaves by scattered atomics
-// (NML_DBG_* exist only in builds with -DNML_TRACE.)
-static int tune_env(const char* name, int dflt) {
-    const char* v = getenv(name);
-    return (v && *v) ? atoi(v) : dflt;
+//   NML_TUNE_WPATCH   0: no weight-gradient patch walk NML_TUNE_WCOAL     0: its gradient leaves by scattered stores
+struct Tune {
+    int stages, bn, ka, l2promo, pair, tmastore, epi8, epi8_k, patch, bres, shuffle, fsplit, wpatch, wcoal;
+};
+static const Tune& tune() {
+    static Tune t;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        auto env = [](const char* name, int dflt) {
+            const char* v = getenv(name);
+            return (v && *v) ? atoi(v) : dflt;
+        };
+        t.stages = env("NML_TUNE_STAGES", 8);
+        t.bn = env("NML_TUNE_BN", 0);
+        t.ka = env("NML_TUNE_KA", 0);  // 0: chosen per launch
+        t.l2promo = env("NML_TUNE_L2PROMO", 3);
+        t.pair = env("NML_TUNE_PAIR", 1);
+        t.tmastore = env("NML_TUNE_TMASTORE", 1);
+        t.epi8 = env("NML_TUNE_EPI8", 1);
+        t.epi8_k = env("NML_TUNE_EPI8_K", 8);
+        t.patch = env("NML_TUNE_PATCH", 1);
+        t.bres = env("NML_TUNE_BRES", 1);
+        t.shuffle = env("NML_TUNE_SHUFFLE", 1);
+        t.fsplit = env("NML_TUNE_FSPLIT", 1);
+        t.wpatch = env("NML_TUNE_WPATCH", 1);
+        t.wcoal = env("NML_TUNE_WCOAL", 1);
+    });
+    return t;
 }
 
 enum { SWZ_NONE = 0, SWZ_128B = 1, SWZ_128B_ATOM32 = 2 };
@@ -114,7 +139,7 @@ static int encode_map(CUtensorMap* tm, const void* ptr, int elem_bytes, int rank
                     swizzle == SWZ_128B ? CU_TENSOR_MAP_SWIZZLE_128B
                     : swizzle == SWZ_128B_ATOM32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
                                                  : CU_TENSOR_MAP_SWIZZLE_NONE,
-                    static_cast<CUtensorMapL2promotion>(tune_env("NML_TUNE_L2PROMO", 3)),
+                    static_cast<CUtensorMapL2promotion>(tune().l2promo),
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         snprintf(g_last_error, sizeof(g_last_error),
@@ -134,11 +159,17 @@ struct DeviceState {
     bool attr_set = false;
 };
 static DeviceState g_dev[64];
-static std::mutex g_dev_mutex;
-static long long g_launches = 0;
+static std::mutex g_dev_mutex;   // guards g_dev, g_static, g_prof and g_ref_ws
+static std::atomic<long long> g_launches{0};
+// Where kernels report an abandoned wait.  The words live in the library image, so set-up needs no
+// allocation: their device addresses come from cudaGetSymbolAddress, once per device.
+static __device__ int g_status_word;
+// Per-launch overrides used by the nml_debug_* entry points only (0 / false in normal use).
+static thread_local unsigned long long g_dbg_wait_limit_ns = 0;
+static thread_local bool g_dbg_short_a_box = false;
 
 struct Profiler {
-    bool on = false;
+    std::atomic<bool> on{false};
     int cap = 0, n = 0;
     std::vector<cudaEvent_t> start, stop;
 };
@@ -178,24 +209,68 @@ static int raise_smem_limit() {
     return NML_OK;
 }
 
+// Loads every helper kernel of the library (with lazy module loading a kernel is otherwise loaded by
+// its first launch, which may allocate and must not happen inside a stream capture).
+static int load_helper_kernels() {
+    const void* fns[] = {
+        (const void*)nchw_to_nhwc_kernel<float>, (const void*)nchw_to_nhwc_kernel<__half>,
+        (const void*)convert_rows_kernel<float>, (const void*)convert_rows_kernel<__half>,
+        (const void*)colsum_rows_kernel<float>, (const void*)colsum_rows_kernel<__half>,
+        (const void*)colsum_rows_f16x8_kernel,
+        (const void*)repack_weight_kernel<float>, (const void*)repack_weight_kernel<__half>,
+        (const void*)pad_pack_c8_kernel<float>, (const void*)pad_pack_c8_kernel<__half>,
+        (const void*)repack_weight_c8_kernel<float>, (const void*)repack_weight_c8_kernel<__half>,
+        (const void*)finish_rows_kernel<float>, (const void*)finish_rows_kernel<__half>,
+        (const void*)pack_phase_weights_kernel<float, float>, (const void*)pack_phase_weights_kernel<float, __half>,
+        (const void*)pack_phase_weights_kernel<__half, float>, (const void*)pack_phase_weights_kernel<__half, __half>,
+        (const void*)to_float_kernel<__half>, (const void*)colsum_finish_kernel,
+        (const void*)wgrad_reduce_rows4_kernel, (const void*)wgrad_reduce_kernel,
+    };
+    for (const void* f : fns) {
+        cudaFuncAttributes a;
+        NML_CUDA(cudaFuncGetAttributes(&a, f));
+    }
+    return NML_OK;
+}
+
+// One-time set-up of the current device (first use, or nml_init): looks up the status word, loads the
+// kernels and raises their shared-memory limit.  Allocates nothing; the cudaMemset is synchronous.
 static int device_state(DeviceState** out) {
     int dev = 0;
     NML_CUDA(cudaGetDevice(&dev));
     if (dev < 0 || dev >= 64) return NML_ERR_INVALID;
     std::lock_guard<std::mutex> lock(g_dev_mutex);
     DeviceState& s = g_dev[dev];
-    if (!s.err) {
-        NML_CUDA(cudaMalloc(&s.err, sizeof(int)));
-        NML_CUDA(cudaMemset(s.err, 0, sizeof(int)));
-        NML_CUDA(cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev));
-    }
     if (!s.attr_set) {
+        void* status = nullptr;
+        NML_CUDA(cudaGetSymbolAddress(&status, g_status_word));
+        NML_CUDA(cudaMemset(status, 0, sizeof(int)));
+        NML_CUDA(cudaDeviceGetAttribute(&s.sms, cudaDevAttrMultiProcessorCount, dev));
         int rc_attr = raise_smem_limit();
         if (rc_attr) return rc_attr;
+        rc_attr = load_helper_kernels();
+        if (rc_attr) return rc_attr;
+        s.err = static_cast<int*>(status);
         s.attr_set = true;
     }
     *out = &s;
     return NML_OK;
+}
+
+// SM count the planner assumes: the current device's, or a B200's 148 where no device is present
+// (workspace-size queries work on a machine without a GPU).
+static int planning_sms() {
+    static std::atomic<int> cached{0};
+    int v = cached.load();
+    if (v > 0) return v;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        sms <= 0) {
+        (void)cudaGetLastError();
+        return 148;
+    }
+    cached.store(sms);
+    return sms;
 }
 
 struct MathInfo {
@@ -210,8 +285,42 @@ static bool math_info(int math, MathInfo* m) {
     return false;
 }
 
+// Bias gradient = column sums of dY, in two stages so that the result is bitwise repeatable: the pass
+// that reads dY writes rows of partial sums ([P][stride], one row per block), colsum_finish_kernel adds
+// the rows in a fixed order.  Both scratch matrices come from the workspace.
+struct ColsumScratch {
+    float* partial = nullptr;
+    float* second = nullptr;
+    int P = 0, stride = 0;
+};
+static ColsumScratch colsum_scratch(Bump& ws, size_t P, int stride) {
+    ColsumScratch c;
+    c.P = static_cast<int>(P);
+    c.stride = stride;
+    c.partial = static_cast<float*>(ws.take(P * stride * sizeof(float)));
+    if (P > 256) c.second = static_cast<float*>(ws.take(((P + 255) / 256) * stride * sizeof(float)));
+    return c;
+}
+static int colsum_finish(const ColsumScratch& cs, int C, float* out, cudaStream_t st) {
+    const float* src = cs.partial;
+    int P = cs.P, stride = cs.stride;
+    for (;;) {
+        const int S = ceil_div(P, 256);
+        float* dst = (S == 1) ? out : (src == cs.partial ? cs.second : cs.partial);
+        colsum_finish_kernel<<<dim3(ceil_div(C, 32), S), dim3(32, 8), 0, st>>>(src, P, stride, C, dst, cs.stride, 256);
+        ++g_launches;
+        if (S == 1) break;
+        src = dst;
+        P = S;
+        stride = cs.stride;
+    }
+    NML_CUDA(cudaGetLastError());
+    return NML_OK;
+}
+
 // Converts an activation tensor into the NHWC operand encoding of `mi` unless it already is one.
-// planes[0..1] receive the operand pointers, *cp the padded channel count.
+// planes[0..1] receive the operand pointers, *cp the padded channel count.  With `colsum` the
+// per-channel sums of the tensor (the bias gradient) are produced in the same pass where there is one.
 static int prepare_activation(const void* src, int dtype, int layout, int batch, int c, int h, int w,
                               const MathInfo& mi, Bump& ws, cudaStream_t st, const void* planes[2], int* cp,
                               float* colsum) {
@@ -219,23 +328,30 @@ static int prepare_activation(const void* src, int dtype, int layout, int batch,
     const bool direct = (mi.enc == ENC_F16) && dtype == NML_F16 && (c % align == 0) &&
                         (layout == NML_NHWC || (h == 1 && w == 1) || c == 1);
     const size_t pixels = static_cast<size_t>(batch) * h * w;
+    // row-major column sums: enough row blocks to fill the GPU, few enough that the second stage stays negligible
+    const int col_blocks = ceil_div(c, 256);
+    const int rows_per_block = static_cast<int>(std::max<size_t>(64, round_up(ceil_div(static_cast<int>(std::min<size_t>(pixels, 1u << 30)), std::max(1, 1184 / col_blocks)), 8)));
+    const size_t row_blocks = (pixels + rows_per_block - 1) / rows_per_block;
+    auto rows_colsum = [&](const ColsumScratch& cs) -> int {
+        dim3 grid(col_blocks, static_cast<unsigned>(row_blocks));
+        if (dtype == NML_F16 && c % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0)
+            colsum_rows_f16x8_kernel<<<grid, 256, 0, st>>>(static_cast<const __half*>(src), cs.partial, pixels, c, rows_per_block);
+        else if (dtype == NML_F16)
+            colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), cs.partial, pixels, c, rows_per_block);
+        else
+            colsum_rows_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), cs.partial, pixels, c, rows_per_block);
+        ++g_launches;
+        return colsum_finish(cs, c, colsum, st);
+    };
     if (direct) {
         planes[0] = src;
         planes[1] = nullptr;
         *cp = c;
-        if (colsum && !ws.dry) {
-            // enough row blocks to fill the GPU, few enough that the atomics stay negligible
-            int col_blocks = ceil_div(c, 256);
-            int rows_per_block = static_cast<int>(std::max<size_t>(64, round_up(ceil_div(static_cast<int>(std::min<size_t>(pixels, 1u << 30)), std::max(1, 1184 / col_blocks)), 8)));
-            dim3 grid(col_blocks, static_cast<unsigned>((pixels + rows_per_block - 1) / rows_per_block));
-            if (c % 8 == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
-                colsum_rows_f16x8_kernel<<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
-                                                               rows_per_block);
-                ++g_launches;
-            } else {
-                { colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
-                                                                 rows_per_block); ++g_launches; }
-            }
+        if (colsum) {
+            ColsumScratch cs = colsum_scratch(ws, row_blocks, c);
+            if (ws.dry) return NML_OK;
+            if (!ws.fits()) return NML_ERR_WORKSPACE;
+            return rows_colsum(cs);
         }
         return NML_OK;
     }
@@ -245,16 +361,23 @@ static int prepare_activation(const void* src, int dtype, int layout, int batch,
     void* p1 = (mi.planes == 2) ? ws.take(pixels * Cp * mi.es) : nullptr;
     planes[0] = p0;
     planes[1] = p1;
+    const bool transposing = layout == NML_NCHW && !(h == 1 && w == 1);
+    ColsumScratch cs;
+    if (colsum) cs = transposing ? colsum_scratch(ws, static_cast<size_t>(batch) * ceil_div(h * w, 64), c) : colsum_scratch(ws, row_blocks, c);
     if (ws.dry) return NML_OK;
     if (!ws.fits()) return NML_ERR_WORKSPACE;
-    if (layout == NML_NCHW && !(h == 1 && w == 1)) {
+    if (transposing) {
         dim3 grid(ceil_div(h * w, 64), ceil_div(Cp, 64), batch);
         if (dtype == NML_F32)
             { nchw_to_nhwc_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), p0, p1, mi.enc, c, Cp,
-                                                            h * w, colsum); ++g_launches; }
+                                                            h * w, cs.partial); ++g_launches; }
         else
             { nchw_to_nhwc_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), p0, p1, mi.enc, c,
-                                                             Cp, h * w, colsum); ++g_launches; }
+                                                             Cp, h * w, cs.partial); ++g_launches; }
+        if (colsum) {
+            int rc = colsum_finish(cs, c, colsum, st);
+            if (rc) return rc;
+        }
     } else {
         size_t total = pixels * Cp;
         int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 16));
@@ -265,14 +388,8 @@ static int prepare_activation(const void* src, int dtype, int layout, int batch,
             { convert_rows_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(src), p0, p1, mi.enc,
                                                                pixels, c, Cp); ++g_launches; }
         if (colsum) {
-            int rows_per_block = 256;
-            dim3 grid(ceil_div(c, 256), static_cast<unsigned>((pixels + rows_per_block - 1) / rows_per_block));
-            if (dtype == NML_F32)
-                { colsum_rows_kernel<float><<<grid, 256, 0, st>>>(static_cast<const float*>(src), colsum, pixels, c,
-                                                                rows_per_block); ++g_launches; }
-            else
-                { colsum_rows_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(src), colsum, pixels, c,
-                                                                 rows_per_block); ++g_launches; }
+            int rc = rows_colsum(cs);
+            if (rc) return rc;
         }
     }
     NML_CUDA(cudaGetLastError());
@@ -293,15 +410,18 @@ static int prepare_window(const void* src, int dtype, int layout, int batch, int
     const size_t pixels = static_cast<size_t>(batch) * img->hp * img->wp;
     void* p = ws.take(pixels * 16);
     img->ptr = p;
+    int blocks = static_cast<int>(std::min<size_t>((pixels + 255) / 256, 148 * 32));
+    ColsumScratch cs;
+    if (colsum) cs = colsum_scratch(ws, blocks, 8);  // one row of 8 channel sums per block
     if (ws.dry) return NML_OK;
     if (!ws.fits()) return NML_ERR_WORKSPACE;
-    int blocks = static_cast<int>(std::min<size_t>((pixels + 255) / 256, 148 * 32));
     const int nchw = (layout == NML_NCHW) ? 1 : 0;
     if (dtype == NML_F32)
-        { pad_pack_c8_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(src), nchw, static_cast<__half*>(p), batch, c, h, w, p_h, p_w, img->hp, img->wp, colsum); ++g_launches; }
+        { pad_pack_c8_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(src), nchw, static_cast<__half*>(p), batch, c, h, w, p_h, p_w, img->hp, img->wp, cs.partial); ++g_launches; }
     else
-        { pad_pack_c8_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(src), nchw, static_cast<__half*>(p), batch, c, h, w, p_h, p_w, img->hp, img->wp, colsum); ++g_launches; }
+        { pad_pack_c8_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(src), nchw, static_cast<__half*>(p), batch, c, h, w, p_h, p_w, img->hp, img->wp, cs.partial); ++g_launches; }
     NML_CUDA(cudaGetLastError());
+    if (colsum) return colsum_finish(cs, c, colsum, st);
     return NML_OK;
 }
 
@@ -341,15 +461,20 @@ static void choose_box(int bits, int gw, int gh, int gn, int s_w, int s_h, int* 
     }
 }
 
-#ifdef NML_TRACE
-static long long* g_trace_buf = nullptr;
-extern "C" void nml_trace_set(long long* p) { g_trace_buf = p; }
-#endif
 
-static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
+// Closes the timing bracket of a recorded launch (see nml_profile_begin).
+static int profile_stop(int slot, cudaStream_t st) {
+    if (slot >= 0) NML_CUDA(cudaEventRecord(g_prof.stop[slot], st));
+    return NML_OK;
+}
+
+// Launches the contraction kernel.  When `open_slot` is given and the launch is being timed, the
+// bracket is left open (slot index returned there) so that the caller can include the kernel's
+// second-stage reduction; the caller then closes it with profile_stop.
+static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st, int* open_slot = nullptr) {
     // Narrow tiles finish a 64-deep K slice in well under the barrier round trip of a stage, so they
     // take two slices per stage (8 MMAs per round trip); 256-wide tiles already fill 512 clocks.
-    P.ka = P.pair ? 1 : std::max(1, std::min(2, tune_env("NML_TUNE_KA", P.bn >= 192 ? 1 : 2)));
+    P.ka = P.pair ? 1 : std::max(1, std::min(2, tune().ka ? tune().ka : (P.bn >= 192 ? 1 : 2)));
     const int stage_bytes = P.ka * (kStageABytes + (P.pair ? P.bn / 2 : P.bn) * 128);
     // Shared memory: the operand ring, then the epilogue's staging buffers (two per warp if that does not
     // cost a ring stage, else one), the per-warp bias tiles, and the barriers.
@@ -361,8 +486,8 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
         const int cpi = P.out_f16 ? 64 : 32;
         int k_slices = 0;  // 64-deep (fp16) K slices per tile, longest phase
         for (int p = 0; p < P.n_phases; ++p) k_slices = std::max(k_slices, P.passes * P.c_blocks * P.phases[p].tap_count);
-        const bool short_k = k_slices <= tune_env("NML_TUNE_EPI8_K", 8);
-        P.epi_warps = (tma_out && short_k && P.bn / cpi >= 2 && tune_env("NML_TUNE_EPI8", 1)) ? 8 : 4;
+        const bool short_k = k_slices <= tune().epi8_k;
+        P.epi_warps = (tma_out && short_k && P.bn / cpi >= 2 && tune().epi8) ? 8 : 4;
     }
     size_t smem;
     if (P.wpatch) {
@@ -376,7 +501,7 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
         P.ring_bytes = P.stages * w_stage;
         {
             const long long run = 1ll * P.c_patch * P.n_taps * (P.kw_pack ? P.kw_count : 1);
-            P.w_coalesce = (tune_env("NML_TUNE_WCOAL", 1) && 32 * run * 4 <= P.ring_bytes && P.num_tiles <= ds->sms) ? 1 : 0;
+            P.w_coalesce = (tune().wcoal && 32 * run * 4 <= P.ring_bytes && P.num_tiles <= ds->sms) ? 1 : 0;
         }
         smem = static_cast<size_t>(P.ring_bytes) + P.epi_warps * P.stg_bufs * kStagingBufBytes + fixed;
     } else if (P.patch) {
@@ -386,7 +511,7 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
         const int res_bytes = P.c_blocks * P.n_taps * b_slice;  // the taps of every phase
         P.stg_bufs = 2;
         int avail = 232448 - fixed - P.epi_warps * P.stg_bufs * kStagingBufBytes;
-        const bool res_wanted = P.n_tiles == 1 && P.passes == 1 && tune_env("NML_TUNE_BRES", 1);
+        const bool res_wanted = P.n_tiles == 1 && P.passes == 1 && tune().bres;
         if (res_wanted && res_bytes + 2 * P.patch_bytes > avail) {  // trade staging for residency
             P.stg_bufs = 1;
             avail = 232448 - fixed - P.epi_warps * P.stg_bufs * kStagingBufBytes;
@@ -404,7 +529,7 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
         } else {
             P.b_resident = 0;
             // B streams tap by tap; narrow tiles take two taps per stage (8 MMAs per barrier round trip)
-            P.ka = std::max(1, std::min(2, tune_env("NML_TUNE_KA", P.bn >= 192 ? 1 : 2)));
+            P.ka = std::max(1, std::min(2, tune().ka ? tune().ka : (P.bn >= 192 ? 1 : 2)));
             const int b_stage = P.ka * b_slice;
             P.a_stages = std::min(3, std::max(2, P.passes * P.c_blocks));
             P.stages = std::min(8, (avail - P.a_stages * P.patch_bytes) / b_stage);
@@ -426,22 +551,23 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
     int stages1 = (232448 - fixed - P.epi_warps * 1 * kStagingBufBytes) / stage_bytes;
     P.stg_bufs = (stages2 >= std::min(stages1, 8)) ? 2 : 1;
     int stages = std::min(8, P.stg_bufs == 2 ? stages2 : stages1);
-    stages = std::max(2, std::min(stages, tune_env("NML_TUNE_STAGES", 8)));
+    stages = std::max(2, std::min(stages, tune().stages));
     P.stages = stages;
     P.ring_bytes = stages * stage_bytes;
     smem = static_cast<size_t>(stages) * stage_bytes + P.epi_warps * P.stg_bufs * kStagingBufBytes + fixed;
     }
     smem = std::max<size_t>(smem, 120 * 1024);  // one CTA per SM: each allocates its own TMEM
     P.err = ds->err;
-#ifdef NML_TRACE
-    P.trace = g_trace_buf;
-    P.dbg_skip = tune_env("NML_DBG_SKIP", 0);
-    P.dbg_alt = tune_env("NML_DBG_ALT", 0);
-#endif
     int grid = P.pair ? 2 * std::min(P.num_tiles, ds->sms / 2) : std::min(P.num_tiles, ds->sms);
     if (grid <= 0) return NML_OK;
-    const bool rec = g_prof.on && g_prof.n < g_prof.cap;
-    if (rec) NML_CUDA(cudaEventRecord(g_prof.start[g_prof.n], st));
+    P.wait_limit_ns = g_dbg_wait_limit_ns;
+    int rec_slot = -1;
+    if (g_prof.on.load(std::memory_order_relaxed)) {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        if (g_prof.on.load() && g_prof.n < g_prof.cap) rec_slot = g_prof.n++;
+    }
+    const bool rec = rec_slot >= 0;
+    if (rec) NML_CUDA(cudaEventRecord(g_prof.start[rec_slot], st));
     if (P.pair) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid);
@@ -460,7 +586,8 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st) {
         kernel_for(P)<<<grid, threads_for(P.mode == MODE_FPROP ? P.out_mode : OUT_NHWC), smem, st>>>(P);
     }
     NML_CUDA(cudaGetLastError());
-    if (rec) NML_CUDA(cudaEventRecord(g_prof.stop[g_prof.n++], st));
+    if (open_slot) *open_slot = rec_slot;
+    else if (rec) NML_CUDA(cudaEventRecord(g_prof.stop[rec_slot], st));
     ++g_launches;
     return NML_OK;
 }
@@ -491,7 +618,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     // columns, whose epilogue scatters each row to its stride_h x stride_w block of output pixels.
     if (f.gather && f.k_is_dim0 && !f.shuf_sh && f.d_h == 1 && f.d_w == 1 && f.s_h * f.s_w > 1 &&
         f.s_h * f.s_w * f.d1 <= 16 && f.out_layout == NML_NHWC && mi.enc == ENC_F16 && f.d1 == f.out_c &&
-        tune_env("NML_TUNE_SHUFFLE", 1)) {
+        tune().shuffle) {
         const int C = f.d1, Kc = f.d0;
         int dh_min = 1 << 20, dh_max = -(1 << 20), dw_min = 1 << 20, dw_max = -(1 << 20);
         for (int ph = 0; ph < f.s_h; ++ph)
@@ -625,8 +752,16 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     // Few output pixels under a long K loop (the 2x2 ... 8x8 layers of a U-Net): room for the fp32 partial
     // sums of a K-split walk.
     const size_t out_pixels = static_cast<size_t>(f.batch) * f.out_h * f.out_w;
-    const bool may_split = !window && !f.shuf_sh && T >= 4 && out_pixels <= 8192 && 1ll * T * c_blocks >= 32 && tune_env("NML_TUNE_FSPLIT", 1);
-    float* split_acc = may_split ? static_cast<float*>(ws.take(out_pixels * N * sizeof(float))) : nullptr;
+    const bool may_split = !window && !f.shuf_sh && T >= 4 && out_pixels <= 8192 && 1ll * T * c_blocks >= 32 && tune().fsplit;
+    // one fp32 plane per K slice; the bound on the slice count below holds for every plan made further down
+    // (tiles >= tiles_lb, at least 4 K iterations per slice)
+    int z_cap = 1;
+    if (may_split) {
+        const long long tiles_lb = 1ll * ((out_pixels + 127) / 128) * ceil_div(N, 256);
+        const int sms = ds ? ds->sms : planning_sms();
+        z_cap = static_cast<int>(std::max<long long>(1, std::min<long long>(sms / tiles_lb, 1ll * (mi.planes == 2 ? 3 : 1) * T * c_blocks / 4)));
+    }
+    float* split_acc = may_split ? static_cast<float*>(ws.take(static_cast<size_t>(z_cap) * out_pixels * N * sizeof(float))) : nullptr;
     if (ws.dry) return NML_OK;
     if (!ws.fits()) return NML_ERR_WORKSPACE;
 
@@ -733,7 +868,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     // waste much more of the tile than the free-form box does.  Every phase of a gather walk has its own
     // taps and patch origin; the box is sized for the widest phase.
     {
-        const int mode = tune_env("NML_TUNE_PATCH", 1);
+        const int mode = tune().patch;
         int range_w = 0, range_h = 0;
         bool every_phase_has_taps = true;
         for (int p = 0; p < n_phases; ++p) {
@@ -796,7 +931,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
             m_tiles_all += 1ll * ceil_div(P.phases[p].wq, 1 << P.wb_log2) * ceil_div(P.phases[p].hq, 1 << P.hb_log2) *
                            ceil_div(f.batch, 1 << P.nb_log2);
         const int forced = (P.patch && patch_resident) ? ((N <= 16 && !b_mn_major) ? 16 : static_cast<int>(round_up(N, 32)))
-                                                       : tune_env("NML_TUNE_BN", 0);
+                                                       : tune().bn;
         const int cand[4] = {256, 128, 64, forced};
         const double cost[3] = {1.0, 1.28, 2.24};
         double best = -1;
@@ -816,7 +951,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     }
     // Row-major output through TMA stores when the geometry allows: the box is the 32 consecutive tile
     // rows one epilogue warp owns (a sub-box of the tile's pixel box), 128 bytes of columns wide.
-    if (P.out_mode == OUT_NHWC && tune_env("NML_TUNE_TMASTORE", 1)) {
+    if (P.out_mode == OUT_NHWC && tune().tmastore) {
         const int esz = P.out_f16 ? 2 : 4;
         const int cpi = 128 / esz;
         if (P.bn % cpi == 0 && (static_cast<size_t>(N) * esz) % 16 == 0 && (reinterpret_cast<uintptr_t>(f.out) & 15) == 0) {
@@ -833,7 +968,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     }
     // Channel-major (NCHW) output through TMA stores: box = the (w, h) sub-box of the warp's 32 pixels x 64 fp16 / 32 fp32 channels, staged channel-major.  Needs
     // unit output stride (TMA cannot stride the innermost dimension) and 16-byte aligned rows.
-    if (P.out_mode == OUT_NCHW && tune_env("NML_TUNE_TMASTORE", 1) && P.out_stride_w == 1 && P.out_stride_h == 1) {
+    if (P.out_mode == OUT_NCHW && tune().tmastore && P.out_stride_w == 1 && P.out_stride_h == 1) {
         const int esz = P.out_f16 ? 2 : 4;
         const int cpi = 128 / esz;
         const int wbx = 1 << P.wb_log2, hbx = 1 << P.hb_log2;
@@ -866,7 +1001,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         tiles_single += 1ll * ceil_div(P.phases[p].wq, 1 << P.wb_log2) * ceil_div(P.phases[p].hq, 1 << P.hb_log2) *
                         ceil_div(f.batch, 1 << P.nb_log2) * P.n_tiles;
     const bool will_split = may_split && !P.patch && tiles_single * 2 <= ds->sms && k_iters_min >= 8;
-    P.pair = (tune_env("NML_TUNE_PAIR", 1) && !P.patch && !will_split && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) && k_iters_min >= 4 &&
+    P.pair = (tune().pair && !P.patch && !will_split && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) && k_iters_min >= 4 &&
               (P.out_mode == OUT_NHWC_TMA || P.out_mode == OUT_NCHW_TMA || P.out_mode == OUT_NCHW) && ds->sms >= 2) ? 1 : 0;
     int tiles = 0;
     for (int p = 0; p < n_phases; ++p) {
@@ -897,12 +1032,13 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         int k_min = k_iters_min;
         for (int p = 0; p < n_phases; ++p)
             if (P.phases[p].tap_count > 0) k_min = std::min(k_min, P.passes * P.c_blocks * P.phases[p].tap_count);
-        const int z = std::min(ds->sms / tiles, k_min / 4);  // at least 4 K iterations per slice
+        const int z = std::min(z_cap, std::min(ds->sms / tiles, k_min / 4));  // at least 4 K iterations per slice
         if (z >= 2) {
             P.fsplit = z;
             P.num_tiles = tiles * z;
-            // the walk adds into the scratch; the finishing pass applies bias, rounding, cast and layout
-            NML_CUDA(cudaMemsetAsync(split_acc, 0, out_pixels * N * sizeof(float), st));
+            // slice z stores into plane z of the scratch; the finishing pass adds the planes in order and
+            // applies bias, rounding, cast and layout
+            P.plane_elems = out_pixels * N;
             P.out = split_acc;
             P.out_mode = OUT_NHWC;
             P.out_f16 = 0;
@@ -957,21 +1093,33 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         }
         if (rc) return rc;
     }
-    rc = launch_kernel(P, ds, st);
-    if (rc || P.fsplit <= 1) return rc;
+    if (g_dbg_short_a_box) {
+        // nml_debug_stalled_linear_forward only: A boxes half as tall as the kernel expects, so no stage
+        // ever receives all its bytes and the bounded waits run out
+        uint64_t adims[4] = {static_cast<uint64_t>(Cp), static_cast<uint64_t>(f.a_w), static_cast<uint64_t>(f.a_h),
+                             static_cast<uint64_t>(f.batch)};
+        uint32_t abox[4] = {static_cast<uint32_t>(mi.kb), static_cast<uint32_t>((1 << P.wb_log2) / 2), 1, 1};
+        uint32_t aes[4] = {1, 1, 1, 1};
+        rc = encode_map(&P.tmA[0], a_planes[0], mi.es, 4, adims, abox, aes, SWZ_128B);
+        if (rc) return rc;
+    }
+    int slot = -1;
+    rc = launch_kernel(P, ds, st, &slot);
+    if (rc) return rc;
+    if (P.fsplit <= 1) return profile_stop(slot, st);
     {
         const size_t total = out_pixels * N;
         const int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 8));
         const int nchw = (f.out_layout == NML_NCHW && !(f.out_h == 1 && f.out_w == 1)) ? 1 : 0;
         if (f.out_dtype == NML_F16)
-            { finish_rows_kernel<__half><<<blocks, 256, 0, st>>>(split_acc, bias32, static_cast<__half*>(f.out), out_pixels, N,
+            { finish_rows_kernel<__half><<<blocks, 256, 0, st>>>(split_acc, P.fsplit, bias32, static_cast<__half*>(f.out), out_pixels, N,
                                                               f.out_h * f.out_w, nchw, 0); ++g_launches; }
         else
-            { finish_rows_kernel<float><<<blocks, 256, 0, st>>>(split_acc, bias32, static_cast<float*>(f.out), out_pixels, N,
+            { finish_rows_kernel<float><<<blocks, 256, 0, st>>>(split_acc, P.fsplit, bias32, static_cast<float*>(f.out), out_pixels, N,
                                                              f.out_h * f.out_w, nchw, f.round_f16); ++g_launches; }
         NML_CUDA(cudaGetLastError());
     }
-    return NML_OK;
+    return profile_stop(slot, st);
 }
 
 // ------------------------------------------------------- wgrad-like problems --
@@ -1000,12 +1148,8 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     if (!ws.dry) {
         int rc = device_state(&ds);
         if (rc) return rc;
-        if (g.colsum) {
-            int nsum = g.colsum_of_patch ? g.patch_c : g.plain_c;
-            NML_CUDA(cudaMemsetAsync(g.colsum, 0, sizeof(float) * nsum, st));
-        }
-        NML_CUDA(cudaMemsetAsync(g.dw, 0, sizeof(float) * static_cast<size_t>(g.plain_c) * g.patch_c * T, st));
     }
+    const int sms = ds ? ds->sms : planning_sms();
     const void* pa[2] = {nullptr, nullptr};
     const void* pb[2];
     int cpa = 0, cpb = 0;
@@ -1027,8 +1171,6 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     rc = prepare_activation(g.plain, g.dtype, g.layout, g.batch, g.plain_c, g.plain_h, g.plain_w, mi, ws, st, pb, &cpb,
                             g.colsum_of_patch ? nullptr : g.colsum);
     if (rc) return rc;
-    if (ws.dry) return NML_OK;
-    if (!ws.fits()) return NML_ERR_WORKSPACE;
 
     KParams P;
     memset(&P, 0, sizeof(P));
@@ -1049,7 +1191,6 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     P.n_tiles = ceil_div(g.plain_c, 256);
     P.bn = static_cast<int>(round_up(ceil_div(g.plain_c, P.n_tiles), 64));
     P.c_out = g.plain_c;
-    P.out = g.dw;
     P.a_stride_h = g.s_h;
     P.a_stride_w = window ? 1 : g.s_w;
     P.out_stride_h = P.out_stride_w = 1;
@@ -1085,7 +1226,7 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
         const int pw_ = 8 + dw_max - dw_min, ph_ = 7 * g.s_h + dh_max - dh_min + 1;
         const int bn_w = std::min(256, (512 / std::max(mt, 1)) / 64 * 64);
         const double eff = static_cast<double>(g.plain_w) * g.plain_h / (1.0 * round_up(g.plain_w, 8) * round_up(g.plain_h, 8));
-        if (tune_env("NML_TUNE_WPATCH", 1) && mi.enc == ENC_F16 && P.c_blocks == 1 && groups >= 2 && mt <= 8 &&
+        if (tune().wpatch && mi.enc == ENC_F16 && P.c_blocks == 1 && groups >= 2 && mt <= 8 &&
             (window || g.s_w == 1) && bn_w >= 64 && cpb % 64 == 0 && pw_ <= 256 && ph_ <= 256 &&
             pw_ * ph_ * 128 <= 40 * 1024 && eff >= 0.7) {
             P.wpatch = 1;
@@ -1111,7 +1252,7 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     const int G_ = kTileM / mi.kb;
     const bool a_grp = !window && (cpa % mi.kb == 0) && (P.c_blocks % G_ == 0);
     const bool b_grp = (cpb % mi.kb == 0);
-    P.pair = (tune_env("NML_TUNE_PAIR", 1) && !P.wpatch && P.bn == 256 && a_grp && b_grp && ds->sms >= 2) ? 1 : 0;
+    P.pair = (tune().pair && !P.wpatch && P.bn == 256 && a_grp && b_grp && sms >= 2) ? 1 : 0;
     const int m_tiles = P.wpatch ? 1 : P.pair ? ceil_div(ceil_div(P.groups_total * mi.kb, kTileM), 2) : ceil_div(P.groups_total * mi.kb, kTileM);
     const int mn_tiles = m_tiles * P.n_tiles;
     // Split K so that the CTAs finish together: the makespan is (rounds of tiles per CTA) x (K
@@ -1125,7 +1266,7 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
             int per_sp = ceil_div(P.kblocks_total, sp);
             int real = ceil_div(P.kblocks_total, per_sp);  // every slice gets at least one K block
             if (real != sp) continue;
-            long long rounds = ceil_div(mn_tiles * sp, P.pair ? ds->sms / 2 : ds->sms);
+            long long rounds = ceil_div(mn_tiles * sp, P.pair ? sms / 2 : sms);
             long long cost = rounds * (per_sp + 4);
             if (best < 0 || cost < best) {
                 best = cost;
@@ -1133,9 +1274,24 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
             }
         }
     }
-    if (P.wpatch) split = std::max(1, std::min(P.kblocks_total, ds->sms / std::max(1, P.n_tiles)));  // one tile per CTA
+    if (P.wpatch) {  // one tile per CTA, no empty slice
+        split = std::max(1, std::min(P.kblocks_total, sms / std::max(1, P.n_tiles)));
+        split = ceil_div(P.kblocks_total, ceil_div(P.kblocks_total, split));
+    }
     P.split_k = split;
     P.num_tiles = mn_tiles * split;
+    // One K slice writes dW itself.  Several slices store their partial sums into one fp32 plane each
+    // (like dW for the patch walk, else [plain channel][rows of the tile walk]); wgrad_reduce_* then adds
+    // the planes in slice order and writes dW once -- no zero-fill, no atomics, bitwise repeatable.
+    const size_t dw_elems = static_cast<size_t>(g.plain_c) * g.patch_c * T;
+    const int plane_rows = P.wpatch ? 0 : m_tiles * (P.pair ? 2 : 1) * kTileM;
+    const size_t plane_elems = (split <= 1) ? 0 : P.wpatch ? round_up(dw_elems, 4) : static_cast<size_t>(g.plain_c) * plane_rows;
+    float* planes = (split > 1) ? static_cast<float*>(ws.take(static_cast<size_t>(split) * plane_elems * sizeof(float))) : nullptr;
+    if (ws.dry) return NML_OK;
+    if (!ws.fits()) return NML_ERR_WORKSPACE;
+    P.out = (split > 1) ? planes : g.dw;
+    P.plane_elems = plane_elems;
+    P.ld_plane = plane_rows;
     // A wave of CTAs re-reads one operand in full; make that the smaller tensor.
     {
         const double patch_bytes = static_cast<double>(g.batch) * g.patch_h * g.patch_w * cpa * mi.es;
@@ -1204,7 +1360,28 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
         }
         if (rc) return rc;
     }
-    return launch_kernel(P, ds, st);
+    int slot = -1;
+    rc = launch_kernel(P, ds, st, &slot);
+    if (rc) return rc;
+    if (split > 1) {
+        const bool vec_ok = (reinterpret_cast<uintptr_t>(g.dw) & 15) == 0;
+        if (P.wpatch && vec_ok && dw_elems % 4 == 0) {
+            const int blocks = static_cast<int>(std::min<size_t>((dw_elems / 4 + 255) / 256, 148 * 8));
+            wgrad_reduce_rows4_kernel<<<blocks, 256, 0, st>>>(planes, g.dw, split, plane_elems, 1, static_cast<int>(dw_elems / 4), 0);
+        } else if (!P.wpatch && !P.kw_pack && T == 1 && vec_ok && g.patch_c % 4 == 0) {
+            const size_t total4 = dw_elems / 4;
+            const int blocks = static_cast<int>(std::min<size_t>((total4 + 255) / 256, 148 * 16));
+            wgrad_reduce_rows4_kernel<<<blocks, 256, 0, st>>>(planes, g.dw, split, plane_elems, g.plain_c, g.patch_c / 4, plane_rows);
+        } else {
+            const int layout = P.wpatch ? 0 : P.kw_pack ? 2 : 1;
+            const int blocks = static_cast<int>(std::min<size_t>((dw_elems + 255) / 256, 148 * 16));
+            wgrad_reduce_kernel<<<blocks, 256, 0, st>>>(planes, g.dw, split, plane_elems, dw_elems, layout, g.patch_c, P.n_taps,
+                                                        P.kw_count, P.c_blocks, mi.kb, plane_rows);
+        }
+        ++g_launches;
+        NML_CUDA(cudaGetLastError());
+    }
+    return profile_stop(slot, st);
 }
 
 // --------------------------------------------------------- layer -> problems --
@@ -1228,6 +1405,7 @@ static bool conv_out_size(const nml_conv_desc* d, int* ho, int* wo) {
 static int conv_pass(const nml_conv_desc* d, int pass, const void* in0, const void* in1, const void* bias, void* out,
                      float* db, Bump& ws, cudaStream_t st) {
     int ho, wo;
+    g_last_scratch_error[0] = 0;  // a workspace error reported from here on is not the static entry point's
     if (!conv_out_size(d, &ho, &wo)) return NML_ERR_INVALID;
     const bool tr = d->transposed != 0;
     if (pass == NML_PASS_BACKWARD_WEIGHT) {
@@ -1280,6 +1458,7 @@ static int conv_pass(const nml_conv_desc* d, int pass, const void* in0, const vo
 static int linear_pass(const nml_linear_desc* d, int pass, const void* in0, const void* in1, const void* bias,
                        void* out, float* db, Bump& ws, cudaStream_t st) {
     if (!d || d->rows <= 0 || d->in_features <= 0 || d->out_features <= 0) return NML_ERR_INVALID;
+    g_last_scratch_error[0] = 0;
     if (pass == NML_PASS_BACKWARD_WEIGHT) {
         WgradLike g;
         memset(&g, 0, sizeof(g));
@@ -1320,6 +1499,7 @@ static RefWorkspace g_ref_ws[64];
 static int ref_workspace(size_t need, void** out) {
     int dev = 0;
     NML_CUDA(cudaGetDevice(&dev));
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
     RefWorkspace& w = g_ref_ws[dev];
     if (need > w.bytes) {
         if (w.ptr) {
@@ -1340,10 +1520,10 @@ __global__ void tma_box_probe_kernel(const __grid_constant__ CUtensorMap tm, int
                                      uint32_t bytes, uint8_t* out, int* err) {
     extern __shared__ __align__(1024) uint8_t box_smem[];
     __shared__ __align__(8) uint64_t bar;
-    __shared__ int abort_flag;
+    __shared__ __align__(8) int abort_flag[4];
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&bar), 1);
-        abort_flag = 0;
+        abort_state_init(abort_flag, 0);
         fence_mbar_init();
     }
     __syncthreads();
@@ -1351,9 +1531,25 @@ __global__ void tma_box_probe_kernel(const __grid_constant__ CUtensorMap tm, int
         mbar_arrive_expect_tx(smem_u32(&bar), bytes);
         tma_load_4d(smem_u32(box_smem), &tm, smem_u32(&bar), c0, c1, c2, c3);
     }
-    bool ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, err, ERR_WAIT_FULL);
+    bool ok = mbar_wait(smem_u32(&bar), 0, abort_flag, err, ERR_WAIT_FULL);
     if (ok)
         for (uint32_t i = threadIdx.x; i < bytes; i += blockDim.x) out[i] = box_smem[i];
+}
+
+// One warp waits, with the library's bounded wait, on an mbarrier that nothing ever arrives on.  The
+// wait runs out after limit_ns, records ERR_WAIT_FULL in *err and the kernel returns: the give-up path
+// of every kernel here, exercised without a fault, a trap or an unbounded spin.
+__global__ void wait_limit_probe_kernel(unsigned long long limit_ns, int* err, int* gave_up) {
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ __align__(8) int abort_flag[4];
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_state_init(abort_flag, limit_ns);
+        fence_mbar_init();
+    }
+    __syncthreads();
+    const bool ok = mbar_wait(smem_u32(&bar), 0, abort_flag, err, ERR_WAIT_FULL);
+    if (threadIdx.x == 0 && gave_up) *gave_up = ok ? 0 : 1;
 }
 
 }  // namespace nml
@@ -1370,7 +1566,7 @@ const char* nml_status_string(int status) {
         case NML_ERR_WORKSPACE: return g_last_scratch_error[0] ? g_last_scratch_error : "workspace too small";
         case NML_ERR_CUDA: return g_last_error[0] ? g_last_error : "CUDA error";
         case NML_ERR_UNSUPPORTED: return "unsupported configuration";
-        case NML_ERR_DEVICE: return "a kernel abandoned a bounded wait";
+        case NML_ERR_DEVICE: return g_last_device_error[0] ? g_last_device_error : "a kernel abandoned a bounded wait";
     }
     return "unknown status";
 }
@@ -1439,22 +1635,35 @@ int nml_linear_backward_weight(const nml_linear_desc* d, const void* x, const vo
     return linear_pass(d, NML_PASS_BACKWARD_WEIGHT, x, dy, nullptr, dw, db, ws, static_cast<cudaStream_t>(stream));
 }
 
+int nml_init(void) {
+    DeviceState* ds = nullptr;
+    return device_state(&ds);
+}
+
+// Reads and clears one status word; the code of an abandoned wait goes into *code and into the
+// message nml_status_string returns for NML_ERR_DEVICE.
+static int read_status_word(int* word, int* code) {
+    NML_CUDA(cudaDeviceSynchronize());
+    int v = 0;
+    NML_CUDA(cudaMemcpy(&v, word, sizeof(int), cudaMemcpyDeviceToHost));
+    if (code) *code = v;
+    if (v == 0) return NML_OK;
+    NML_CUDA(cudaMemset(word, 0, sizeof(int)));
+    snprintf(g_last_device_error, sizeof(g_last_device_error), "a kernel abandoned bounded wait %d (%s)", v,
+             v == ERR_WAIT_EMPTY ? "producer: free stage" : v == ERR_WAIT_FULL ? "operands to land"
+             : v == ERR_WAIT_TMEM_EMPTY ? "accumulator to drain" : v == ERR_WAIT_TMEM_FULL ? "accumulator to fill"
+             : v == ERR_WAIT_DRAIN ? "copies in flight at unwinding" : "unknown");
+    return NML_ERR_DEVICE;
+}
+
 int nml_device_status(int* code) {
     DeviceState* ds = nullptr;
     int rc = device_state(&ds);
     if (rc) return rc;
-    NML_CUDA(cudaDeviceSynchronize());
-    int v = 0;
-    NML_CUDA(cudaMemcpy(&v, ds->err, sizeof(int), cudaMemcpyDeviceToHost));
-    if (code) *code = v;
-    if (v != 0) {
-        NML_CUDA(cudaMemset(ds->err, 0, sizeof(int)));
-        return NML_ERR_DEVICE;
-    }
-    return NML_OK;
+    return read_status_word(ds->err, code);
 }
 
-long long nml_launch_count(void) { return g_launches; }
+long long nml_launch_count(void) { return g_launches.load(); }
 
 int nml_profile_begin(int max_records) {
     if (max_records <= 0 || max_records > 1 << 16) return NML_ERR_INVALID;
@@ -1465,6 +1674,7 @@ int nml_profile_begin(int max_records) {
         g_prof.start.push_back(a);
         g_prof.stop.push_back(b);
     }
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
     g_prof.cap = max_records;
     g_prof.n = 0;
     g_prof.on = true;
@@ -1486,7 +1696,7 @@ int nml_profile_end(float* ms_out, int capacity, int* count) {
 // kStaticScratchBytes of every GPU that loads this library are held until the process exits.
 constexpr size_t kStaticScratchBytes = 64ull << 20;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
-static __device__ int g_static_status;  // where kernels launched by this entry point report a give-up
+static __device__ int g_static_status;  // where kernels launched by this entry point report a give-up (see g_status_word)
 
 struct StaticState {
     bool ready = false;
@@ -1512,6 +1722,8 @@ static int static_state(StaticState** out) {
         NML_CUDA(cudaDeviceGetAttribute(&s.ds.sms, cudaDevAttrMultiProcessorCount, dev));
         int rc_attr = raise_smem_limit();
         if (rc_attr) return rc_attr;
+        rc_attr = load_helper_kernels();  // so that no later call is the first use (= the loading) of a kernel
+        if (rc_attr) return rc_attr;
         s.scratch = scratch;
         s.ds.err = static_cast<int*>(status);
         s.ds.attr_set = true;
@@ -1527,13 +1739,7 @@ int nml_conv_forward_static(const nml_conv_desc* d, const void* x, const void* w
     if (!d) {  // query form: wait for the device, report and clear a recorded give-up
         int rc = static_state(&ss);
         if (rc) return rc;
-        NML_CUDA(cudaDeviceSynchronize());
-        int v = 0;
-        NML_CUDA(cudaMemcpy(&v, ss->ds.err, sizeof(int), cudaMemcpyDeviceToHost));
-        if (v == 0) return NML_OK;
-        NML_CUDA(cudaMemset(ss->ds.err, 0, sizeof(int)));
-        snprintf(g_last_error, sizeof(g_last_error), "a kernel abandoned bounded wait %d", v);
-        return NML_ERR_DEVICE;
+        return read_status_word(ss->ds.err, nullptr);  // the code is in nml_status_string(NML_ERR_DEVICE)
     }
     if (!x || !w || !y) return NML_ERR_INVALID;
     Bump dry{nullptr, 0, 0, true};
@@ -1814,6 +2020,42 @@ int nml_debug_tma_box(const void* tensor, int elem_bytes, const int dims[4], con
         ds->err);
     NML_CUDA(cudaGetLastError());
     return NML_OK;
+}
+
+int nml_debug_wait_timeout(unsigned long long limit_ns, int use_static_word, void* stream) {
+    if (limit_ns == 0 || limit_ns > 100000000ull) return NML_ERR_INVALID;  // at most 0.1 s
+    int* word = nullptr;
+    if (use_static_word) {
+        StaticState* ss = nullptr;
+        int rc = static_state(&ss);
+        if (rc) return rc;
+        word = ss->ds.err;
+    } else {
+        DeviceState* ds = nullptr;
+        int rc = device_state(&ds);
+        if (rc) return rc;
+        word = ds->err;
+    }
+    wait_limit_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(limit_ns, word, nullptr);
+    NML_CUDA(cudaGetLastError());
+    return NML_OK;
+}
+
+int nml_debug_stalled_linear_forward(const nml_linear_desc* d, const void* x, const void* w, void* y, void* workspace,
+                                     size_t workspace_bytes, unsigned long long limit_ns, void* stream) {
+    if (!d || !x || !w || !y || limit_ns == 0 || limit_ns > 100000000ull) return NML_ERR_INVALID;
+    // only the plain stage-ring walk of a small fp16 layer (one CTA per tile, no pairs): every wait in it is
+    // bounded and no MMA is ever issued
+    if (d->math != NML_MATH_F16 || d->in_dtype != NML_F16 || d->w_dtype != NML_F16 || d->rows > 4096 ||
+        d->in_features > 1024 || d->out_features > 128 || d->in_features % 8 || d->out_features % 8)
+        return NML_ERR_UNSUPPORTED;
+    Bump ws{static_cast<uint8_t*>(workspace), 0, workspace ? workspace_bytes : 0, false};
+    g_dbg_wait_limit_ns = limit_ns;
+    g_dbg_short_a_box = true;
+    int rc = linear_pass(d, NML_PASS_FORWARD, x, w, nullptr, y, nullptr, ws, static_cast<cudaStream_t>(stream));
+    g_dbg_wait_limit_ns = 0;
+    g_dbg_short_a_box = false;
+    return rc;
 }
 
 int nml_debug_copy_to_host(void* host_dst, uintptr_t device_src, size_t bytes) {

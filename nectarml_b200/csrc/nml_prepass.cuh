@@ -35,8 +35,10 @@ __device__ __forceinline__ void store_enc(int enc, void* out0, void* out1, size_
 // Tile of 64 channels x 64 pixels through shared memory.  Loads run along pixels (one 256-byte
 // row segment per 16 threads when the rows allow 16-byte loads), stores along channels: 8 threads
 // write the 64 channels of one pixel as 16-byte (fp16) or 2 x 16-byte (tf32 planes) pieces, so a
-// warp store covers four whole pixels.  When `colsum` is given, the per-channel sum over all
-// pixels (the bias gradient) is accumulated with one atomic per channel per tile.
+// warp store covers four whole pixels.  When `colsum` is given, the per-channel sums over the tile's
+// pixels (a share of the bias gradient) go to row (n * gridDim.x + blockIdx.x) of that [tiles][C]
+// matrix of partial sums; colsum_finish_kernel adds the rows in a fixed order (no atomics, so the
+// bias gradient is bitwise repeatable).
 template <typename TIn>
 __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict__ in, void* out0,
                                                            void* out1, int enc, int C, int Cp, int HW,
@@ -72,7 +74,7 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_kernel(const TIn* __restrict
     if (colsum != nullptr && threadIdx.x < 64 && c0 + threadIdx.x < C) {
         float s = 0.f;
         for (int p = 0; p < 64; ++p) s += tile[threadIdx.x][(p + threadIdx.x) & 63];
-        atomicAdd(colsum + c0 + threadIdx.x, s);
+        colsum[(static_cast<size_t>(n) * gridDim.x + blockIdx.x) * C + c0 + threadIdx.x] = s;
     }
     // store: 8 threads per pixel, 8 channels each
     const int j = threadIdx.x & 7, pp = threadIdx.x >> 3;  // 8 x 32
@@ -126,7 +128,8 @@ __global__ void __launch_bounds__(256) convert_rows_kernel(const TIn* __restrict
     }
 }
 
-// Column sums of a row-major [R][C] matrix (bias gradient of Linear, or of an NHWC dY).
+// Column sums of a row-major [R][C] matrix (bias gradient of Linear, or of an NHWC dY), first stage:
+// row block blockIdx.y writes its sums to row blockIdx.y of the [row blocks][C] partial-sum matrix.
 template <typename TIn>
 __global__ void __launch_bounds__(256) colsum_rows_kernel(const TIn* __restrict__ in, float* colsum,
                                                           size_t R, int C, int rows_per_block) {
@@ -135,13 +138,13 @@ __global__ void __launch_bounds__(256) colsum_rows_kernel(const TIn* __restrict_
     for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < C; c += gridDim.x * blockDim.x) {
         float s = 0.f;
         for (size_t r = r0; r < r1; ++r) s += load_as_float(in, r * C + c);
-        atomicAdd(colsum + c, s);
+        colsum[static_cast<size_t>(blockIdx.y) * C + c] = s;
     }
 }
 
 // Vectorised column sums for fp16 rows whose length is a multiple of 8: every thread owns 8
 // adjacent columns (one 16-byte load per row), a warp covers 256 columns, blockDim.y warps take
-// interleaved rows, and each block adds its partial sums with one atomic per column.
+// interleaved rows, and each block writes its partial sums to its row of the partial-sum matrix.
 __global__ void __launch_bounds__(256) colsum_rows_f16x8_kernel(const __half* __restrict__ in, float* colsum,
                                                                 size_t R, int C, int rows_per_block) {
     __shared__ float part[8][256];
@@ -171,7 +174,7 @@ __global__ void __launch_bounds__(256) colsum_rows_f16x8_kernel(const __half* __
         float sum = 0.f;
 #pragma unroll
         for (int w = 0; w < 8; ++w) sum += part[w][threadIdx.x];
-        atomicAdd(colsum + c, sum);
+        colsum[static_cast<size_t>(blockIdx.y) * C + c] = sum;
     }
 }
 
@@ -210,7 +213,7 @@ __global__ void __launch_bounds__(256) pad_pack_c8_kernel(const TIn* __restrict_
                                                           int N, int C, int H, int W, int pad_h, int pad_w, int Hp,
                                                           int Wp, float* colsum) {
     const size_t total = static_cast<size_t>(N) * Hp * Wp;
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // per-channel sums of the values written (bias gradient)
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // per-channel sums of the values read (bias gradient)
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         const int wp = static_cast<int>(i % Wp);
@@ -227,8 +230,9 @@ __global__ void __launch_bounds__(256) pad_pack_c8_kernel(const TIn* __restrict_
                 if (c < C) {
                     size_t src = nchw ? ((static_cast<size_t>(n) * C + c) * H + h) * W + w
                                       : ((static_cast<size_t>(n) * H + h) * W + w) * C + c;
-                    v[c] = __float2half_rn(load_as_float(in, src));
-                    acc[c] += __half2float(v[c]);
+                    const float xv = load_as_float(in, src);
+                    v[c] = __float2half_rn(xv);
+                    acc[c] += xv;  // the bias gradient sums the values as given, like every other column-sum path
                 }
             }
         }
@@ -245,11 +249,11 @@ __global__ void __launch_bounds__(256) pad_pack_c8_kernel(const TIn* __restrict_
             if (lane == 0) part[wy][c] = x;
         }
         __syncthreads();
-        if (threadIdx.x < C) {
+        if (threadIdx.x < 8) {  // row blockIdx.x of the [blocks][8] partial-sum matrix
             float sum = 0.f;
 #pragma unroll
             for (int w8 = 0; w8 < 8; ++w8) sum += part[w8][threadIdx.x];
-            atomicAdd(colsum + threadIdx.x, sum);
+            colsum[static_cast<size_t>(blockIdx.x) * 8 + threadIdx.x] = sum;
         }
     }
 }
@@ -271,10 +275,11 @@ __global__ void __launch_bounds__(256) repack_weight_c8_kernel(const TIn* __rest
     }
 }
 
-// Partial sums of a K-split forward walk, fp32 [pixels][C] -> the output tensor: bias, optional
-// rounding through fp16, cast, and the caller's layout (nchw: out[n][c][pixel of the image]).
+// Partial sums of a K-split forward walk, `planes` fp32 planes of [pixels][C] (one per K slice) -> the
+// output tensor: the planes are added in slice order (so the result is bitwise repeatable), then bias,
+// optional rounding through fp16, cast, and the caller's layout (nchw: out[n][c][pixel of the image]).
 template <typename TOut>
-__global__ void __launch_bounds__(256) finish_rows_kernel(const float* __restrict__ acc, const float* __restrict__ bias,
+__global__ void __launch_bounds__(256) finish_rows_kernel(const float* __restrict__ acc, int planes, const float* __restrict__ bias,
                                                           TOut* __restrict__ out, size_t pixels, int C, int hw, int nchw,
                                                           int round_f16) {
     const size_t total = pixels * C;
@@ -283,6 +288,7 @@ __global__ void __launch_bounds__(256) finish_rows_kernel(const float* __restric
         const size_t p = i / C;
         const int c = static_cast<int>(i - p * C);
         float v = acc[i];
+        for (int z = 1; z < planes; ++z) v += acc[static_cast<size_t>(z) * total + i];
         if (bias != nullptr) v += bias[c];
         if (round_f16) v = __half2float(__float2half_rn(v));
         size_t o = i;
@@ -326,6 +332,85 @@ __global__ void __launch_bounds__(256) pack_phase_weights_kernel(const TIn* __re
     }
     if (bias_out != nullptr && blockIdx.x == 0 && threadIdx.x < np)
         bias_out[threadIdx.x] = (bias != nullptr) ? load_as_float(bias, threadIdx.x % C) : 0.f;
+}
+
+// Second stage of the column sums: adds rows [blockIdx.y * rows_per_block, ...) of the [P][stride]
+// partial-sum matrix in a fixed order (eight interleaved running sums, then those eight in order) and
+// writes row blockIdx.y of `out` ([segments][out_stride]).  Launched again on its own output while more
+// than one segment is left.  blockDim = (32, 8).
+__global__ void __launch_bounds__(256) colsum_finish_kernel(const float* __restrict__ partial, int P, int stride, int C,
+                                                            float* __restrict__ out, int out_stride, int rows_per_block) {
+    __shared__ float part[8][33];
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    const int p0 = blockIdx.y * rows_per_block;
+    const int p1 = min(P, p0 + rows_per_block);
+    float s = 0.f;
+    if (c < C) {
+#pragma unroll 4
+        for (int p = p0 + threadIdx.y; p < p1; p += 8) s += __ldg(partial + static_cast<size_t>(p) * stride + c);
+    }
+    part[threadIdx.y][threadIdx.x] = s;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < C) {
+        float t = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) t += part[k][threadIdx.x];
+        out[static_cast<size_t>(blockIdx.y) * out_stride + c] = t;
+    }
+}
+
+// Second stage of a split-K weight gradient: adds the K slices' planes in slice order (bitwise
+// repeatable, unlike atomics) and writes dW once.  Row form: dW is `rows` rows of `row_len4` float4,
+// plane z holds row r at planes + z * plane_elems + r * src_pitch (floats).
+__global__ void __launch_bounds__(256) wgrad_reduce_rows4_kernel(const float* __restrict__ planes, float* __restrict__ dw,
+                                                                 int split, size_t plane_elems, size_t rows, int row_len4,
+                                                                 size_t src_pitch) {
+    const size_t total = rows * row_len4;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const size_t r = i / row_len4;
+        const int c4 = static_cast<int>(i - r * row_len4);
+        const float4* src = reinterpret_cast<const float4*>(planes + r * src_pitch) + c4;
+        float4 a = __ldg(src);
+        const size_t step = plane_elems / 4;
+#pragma unroll 4
+        for (int z = 1; z < split; ++z) {
+            const float4 b = __ldg(src + z * step);
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        reinterpret_cast<float4*>(dw)[i] = a;
+    }
+}
+
+// General form, one thread per dW element.  layout 0: a plane is laid out like dW.  layout 1: a plane is
+// [plain channel][R rows of the tile walk] and dW element (plain, pc, t) sits at row
+// (t * c_blocks + pc / kb) * kb + pc % kb.  layout 2 (few-channel window walk): dW element
+// (plain, c, kh, kw) sits at row kh * kb + kw * 8 + c.
+__global__ void __launch_bounds__(256) wgrad_reduce_kernel(const float* __restrict__ planes, float* __restrict__ dw, int split,
+                                                           size_t plane_elems, size_t total, int layout, int c_patch,
+                                                           int n_taps, int kw_count, int c_blocks, int kb, int R) {
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        size_t src = i;
+        if (layout == 1) {
+            const int t = static_cast<int>(i % n_taps);
+            const size_t q = i / n_taps;
+            const int pc = static_cast<int>(q % c_patch);
+            const size_t plain = q / c_patch;
+            src = plain * R + static_cast<size_t>(t * c_blocks + pc / kb) * kb + pc % kb;
+        } else if (layout == 2) {
+            const int kw = static_cast<int>(i % kw_count);
+            size_t q = i / kw_count;
+            const int kh = static_cast<int>(q % n_taps);
+            q /= n_taps;
+            const int c = static_cast<int>(q % c_patch);
+            const size_t plain = q / c_patch;
+            src = plain * R + static_cast<size_t>(kh) * kb + kw * 8 + c;
+        }
+        float a = __ldg(planes + src);
+        for (int z = 1; z < split; ++z) a += __ldg(planes + z * plane_elems + src);
+        dw[i] = a;
+    }
 }
 
 template <typename TIn>

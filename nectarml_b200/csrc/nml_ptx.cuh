@@ -71,14 +71,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Time limit of one wait, in nanoseconds of %globaltimer.
+// Default time limit of one wait, in nanoseconds of %globaltimer.
 #ifndef NML_WAIT_LIMIT_NS
 #define NML_WAIT_LIMIT_NS 1500000000ull
 #endif
 
-// Bounded wait.  `abort_flag` lives in shared memory and is raised by whichever
-// role gives up first; the others see it within ~1k polls and leave too.
-// Returns false when the wait was abandoned.
+// Abort state of one CTA: four ints in shared memory, 8-byte aligned.
+//   [0]    abort flag, raised by whichever role gives up first
+//   [2..3] the time limit of one wait in nanoseconds (a 64-bit value; the kernel's set-up thread
+//          writes it, so a launch can carry its own limit)
+__device__ __forceinline__ void abort_state_init(volatile int* abort_state, unsigned long long limit_ns) {
+    abort_state[0] = 0;
+    abort_state[1] = 0;
+    *reinterpret_cast<volatile unsigned long long*>(abort_state + 2) = limit_ns ? limit_ns : NML_WAIT_LIMIT_NS;
+}
+
+// Bounded wait.  `abort_flag` points at the CTA's abort state (above); the others see a raised flag
+// within ~16 polls and leave too.  Returns false when the wait was abandoned.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* err_word, int err_code) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -90,7 +99,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             uint64_t now = globaltimer_ns();
             if (t0 == 0) {
                 t0 = now;
-            } else if (now - t0 > NML_WAIT_LIMIT_NS) {
+            } else if (now - t0 > *reinterpret_cast<volatile unsigned long long*>(abort_flag + 2)) {
                 *abort_flag = 1;
                 atomicCAS(err_word, 0, err_code);
                 return false;

@@ -21,7 +21,8 @@
 //               several taps use the patch walk instead (see KParams::patch).
 //   MODE_WGRAD  rows of the tile are (tap, patch channel), columns are the other tensor's
 //               channels, the K loop runs over pixels; both operands are MN-major boxes of the
-//               NHWC tensors.  Partial sums of the split-K slices are added with fp32 atomics.
+//               NHWC tensors.  Each split-K slice stores its partial sums into its own plane of a
+//               scratch buffer; a second kernel adds the planes in slice order (no atomics).
 //               Covers Conv2d / ConvTranspose2d weight-gradient and Linear weight-gradient.
 // 256-wide tiles of long-K problems run as CTA pairs (cta_group::2, see the kernel's comment).
 #pragma once
@@ -98,8 +99,8 @@ struct KParams {
     // A is then read from L2 about once instead of once per tap.  B slices stream through the stage ring,
     // or stay resident in shared memory for the whole launch when all of them fit.
     // Forward walk, few tiles and a long K loop (U-Net bottleneck layers): the K iterations of a tile are
-    // cut into fsplit slices that run as separate tiles; their partial sums are added with fp32
-    // atomics into a zeroed row-major scratch, which a small pass turns into the output.
+    // cut into fsplit slices that run as separate tiles; slice z stores its partial sums into plane z
+    // of a row-major scratch, and a small pass adds the planes in order and produces the output.
     int fsplit;          // K slices per tile (1 = off)
     int base_tiles;      // tiles of one slice; tile id = slice * base_tiles + tile
     // Phase-packed gather walk (strided input gradients / transposed forwards with very few output
@@ -117,7 +118,7 @@ struct KParams {
     // once instead of once per tap / once per row tile.
     int wpatch;          // 1: weight-gradient patch walk
     int w_mtiles;        // row tiles (accumulators), w_mtiles * bn <= 512
-    int w_coalesce;      // 1: the partial gradient leaves through shared memory as contiguous runs of adds
+    int w_coalesce;      // 1: the partial gradient leaves through shared memory as contiguous runs of stores
                          //    (needs 32 gradient columns, 32 * c_patch * taps floats, to fit in the operand ring)
     int patch;           // 1: patch walk
     int patch_w, patch_h;    // patch extent in pixels
@@ -151,23 +152,16 @@ struct KParams {
     int out_h, out_w;    // output image
     int ld_out;          // NHWC: elements between consecutive pixels
     int* err;
-#ifdef NML_TRACE
-    long long* trace;  // [cta][tile iteration][8] clock64 stamps, diagnosis builds only
-    int dbg_alt;
-    int dbg_skip;      // 1: skip the B loads, 2: skip the A loads (results are garbage; timing only)
-#endif
+    unsigned long long wait_limit_ns;  // time limit of one bounded wait; 0 = the built-in default
+    // Partial sums of K slices (split-K weight gradient, K-split forward walk) are never added with
+    // atomics: slice z stores its partial tile into plane z of `out` (planes are plane_elems floats
+    // apart) and a second kernel adds the planes in slice order, so results are bitwise repeatable.
+    // wgrad planes are laid out [plain channel][ld_plane rows of the tile walk] (patch walk: like dW).
+    unsigned long long plane_elems;
+    int ld_plane;
     Phase phases[kMaxPhases];
     Tap taps[kMaxTaps];
 };
-
-#ifdef NML_TRACE
-#define NML_STAMP(titer, slot)                                                                  \
-    do {                                                                                        \
-        if (P.trace && (titer) < 64) P.trace[(static_cast<size_t>(blockIdx.x) * 64 + (titer)) * 8 + (slot)] = clock64(); \
-    } while (0)
-#else
-#define NML_STAMP(titer, slot) do {} while (0)
-#endif
 
 // Tile decode runs once per tile in every role, and the epilogue warps in particular are bound by
 // instruction issue: a runtime integer division is ~25 instructions, the multiply-and-shift 4.
@@ -306,7 +300,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
     uint64_t* aempty_bar = afull_bar + 4;                             // [4]
     uint64_t* bres_bar = aempty_bar + 4;                              // [1] patch walk: resident B has landed
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bres_bar + 1);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 2);  // abort state: 4 ints, 8-byte aligned
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -329,7 +323,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             mbar_init(smem_u32(&aempty_bar[s]), 1);
         }
         mbar_init(smem_u32(bres_bar), 1);
-        *abort_flag = 0;
+        abort_state_init(abort_flag, P.wait_limit_ns);
         fence_mbar_init();
         tma_prefetch_desc(&P.tmA[0]);
         tma_prefetch_desc(&P.tmB[0]);
@@ -384,7 +378,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             const uint32_t tpar = (titer >> 1) & 1;
             if (!mbar_wait(smem_u32(&tempty_bar[buf]), tpar ^ 1, abort_flag, P.err, ERR_WAIT_TMEM_EMPTY)) return;
             tc_fence_after();
-            if (lane == 0) NML_STAMP(titer, 0);
             const uint32_t d_tmem = tmem_base + buf * P.bn;
             uint32_t acc = 0;
             for (int cb = 0; cb < P.c_blocks; ++cb) {
@@ -393,7 +386,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 const uint32_t pparity = (pi / P.a_stages) & 1;
                 if (!mbar_wait(smem_u32(&afull_bar[pstage]), pparity, abort_flag, P.err, ERR_WAIT_FULL)) return;
                 tc_fence_after();
-                if (cb == 0 && lane == 0) NML_STAMP(titer, 1);
                 if (elect_one()) {
                     const uint64_t adesc0 = make_smem_desc(smem_u32(smem + P.a_ring_off) + pstage * P.patch_bytes, 16, sbo_a, 2);
                     uint64_t bdesc = make_smem_desc(smem_u32(smem) + (cb * P.n_taps + tb0) * stage_b_bytes, lbo_b, b32 ? 512 : 1024, b32 ? 1 : 2);
@@ -416,7 +408,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     }
                     umma_commit(smem_u32(&aempty_bar[pstage]));
                     if (cb + 1 == P.c_blocks) {
-                        NML_STAMP(titer, 2);
                         umma_commit(smem_u32(&tfull_bar[buf]));
                     }
                 }
@@ -492,10 +483,8 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                                     break;
                                 }
                                 const uint32_t fb = smem_u32(&afull_bar[abuf]);
-                                if (pass == 0 && cb == 0) NML_STAMP((tile - tile_first) / tile_step, 5);
                                 mbar_arrive_expect_tx(fb, patch_tx);
                                 tma_load_4d(a_base + abuf * P.patch_bytes, ta, fb, cb * P.kb, w0, h0, tn);
-                                if (pass == 0 && cb == 0) NML_STAMP((tile - tile_first) / tile_step, 6);
                                 ++issued;
                                 if (++abuf == P.a_stages) {
                                     abuf = 0;
@@ -588,9 +577,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                         k_first = min(kz * per, k_iters);
                         k_iters = min(k_first + per, k_iters) - k_first;
                     }
-#ifdef NML_TRACE
-                    if (P.dbg_skip == 3) k_iters = 0;  // MMA-rate experiment: no loads at all
-#endif
                     // this lane's position in the K loop, (pass, tap, channel block) of iteration it + lane, kept
                     // by counting: a division per stage is time the 256-wide tiles' producer does not have
                     int pass = 0, t = 0, cb = 0;
@@ -962,7 +948,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     break;
                 }
                 tc_fence_after();
-                if (lane == 0) NML_STAMP(titer, 0);
                 const uint32_t w_stage = static_cast<uint32_t>(P.patch_bytes) + stage_b_bytes;
                 const uint32_t sbo_a = static_cast<uint32_t>(P.patch_w * P.a_stride_h) * 128u;  // next pixel row of the K block
                 // Row tile i = taps (2i, 2i+1): its descriptor relative to stage 0, built once (a 64-column MMA
@@ -1008,7 +993,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 }
                 if (!ok) break;
                 if (elect_one()) {
-                    NML_STAMP(titer, 2);
                     if (nkb > 0) umma_commit(smem_u32(&tfull_bar[0]));
                     else mbar_arrive(smem_u32(&tfull_bar[0]));
                 }
@@ -1019,7 +1003,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 break;
             }
             tc_fence_after();
-            if (lane == 0) NML_STAMP(titer, 0);
             const uint32_t d_tmem = tmem_base + buf * P.bn;
             uint32_t acc = 0;
             if (kMode == MODE_FPROP && !kPair && P.patch) {
@@ -1035,7 +1018,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                             break;
                         }
                         tc_fence_after();
-                        if (pass == 0 && cb == 0 && lane == 0) NML_STAMP(titer, 1);
                         const uint32_t patch_addr = smem_u32(smem + P.a_ring_off) + pstage * P.patch_bytes;
                         const uint64_t adesc0 = make_smem_desc(patch_addr, 16, sbo_a, 2);
                         for (int t = 0; t < ph.tap_count; t += P.ka) {
@@ -1081,14 +1063,10 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             } else
             for (int it = 0; it < k_iters; it += P.ka) {
                 const int n_atoms = min(P.ka, k_iters - it);
-#ifdef NML_TRACE
-                if (P.dbg_skip != 3)
-#endif
                 if (!mbar_wait(smem_u32(&full_bar[stage]), parity, abort_flag, P.err, ERR_WAIT_FULL)) {
                     ok = false;
                     break;
                 }
-                if (it == 0 && lane == 0) NML_STAMP(titer, 1);
                 tc_fence_after();
                 if (elect_one()) {  // elect.sync keeps the issue path on the uniform datapath
                     uint64_t adesc = adesc0 + static_cast<uint64_t>(stage * stage_step);
@@ -1133,7 +1111,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             }
             if (!ok) break;
             if (elect_one()) {
-                NML_STAMP(titer, 2);
                 if (kPair) {
                     if (k_iters > 0) {
                         umma_commit_pair(smem_u32(&tfull_bar[buf]));
@@ -1173,14 +1150,16 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     break;
                 }
                 tc_fence_after();
-                if (threadIdx.x == 64) NML_STAMP(titer, 3);
                 const int w_col_base = w_ntile * P.bn;
-                if (P.w_coalesce && nkb > 0) {
+                // this K slice's plane of the partial gradient (laid out like dW itself)
+                float* const w_plane = reinterpret_cast<float*>(P.out) + static_cast<size_t>(w_z) * P.plane_elems;
+                const bool w_live = nkb > 0;  // an empty slice stores zeros (its accumulators were never written)
+                if (P.w_coalesce) {
                     // A column of the gradient (one channel of the other tensor) is ONE contiguous run of
                     // c_patch * taps floats in memory, and 32 columns are 32 such runs back to back.  Scattering the
-                    // accumulators' rows straight into them costs a 32-sector atomic per instruction; instead the
+                    // accumulators' rows straight into them costs a 32-sector store per instruction; instead the
                     // four warps lay 32 columns out in shared memory (the operand ring is idle by now: this CTA has
-                    // no further tile) and add them as contiguous 128-byte pieces.
+                    // no further tile) and store them as contiguous 128-byte pieces.
                     float* S = reinterpret_cast<float*>(smem);
                     const size_t run = static_cast<size_t>(P.c_patch) * P.n_taps * (P.kw_pack ? P.kw_count : 1);
                     uint32_t syncs = 0;
@@ -1217,7 +1196,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                             if (w_valid) {
 #pragma unroll
                                 for (int j = 0; j < 32; ++j)
-                                    if (j < ncols) S[j * run + w_off] = __uint_as_float(r[j]);
+                                    if (j < ncols) S[j * run + w_off] = w_live ? __uint_as_float(r[j]) : 0.f;
                             }
                             __syncwarp();
                         }
@@ -1225,9 +1204,9 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                             ok = false;
                             break;
                         }
-                        float* o = reinterpret_cast<float*>(P.out) + static_cast<size_t>(cg) * run;
+                        float* o = w_plane + static_cast<size_t>(cg) * run;
                         const size_t total = static_cast<size_t>(ncols) * run;
-                        for (size_t idx = static_cast<size_t>(ew) * 32 + lane; idx < total; idx += 128) atomicAdd(o + idx, S[idx]);
+                        for (size_t idx = static_cast<size_t>(ew) * 32 + lane; idx < total; idx += 128) o[idx] = S[idx];
                         if (!meet()) {  // the next 32 columns overwrite S
                             ok = false;
                             break;
@@ -1236,7 +1215,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     if (!ok) break;
                 } else
 #pragma unroll 1
-                for (int i = 0; nkb > 0 && i < P.w_mtiles; ++i) {
+                for (int i = 0; i < P.w_mtiles; ++i) {
                     const int gi = i * (kTileM / P.kb) + row / P.kb;  // tap (kernel row with kw packing) of this row
                     const int pc = row % P.kb;
                     bool w_valid;
@@ -1260,17 +1239,16 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                         const int cg = w_col_base + c0;
                         const int ncols = min(32, P.c_out - cg);
                         if (w_valid) {
-                            float* o = reinterpret_cast<float*>(P.out) + w_off + static_cast<size_t>(cg) * w_stride;
+                            float* o = w_plane + w_off + static_cast<size_t>(cg) * w_stride;
 #pragma unroll
                             for (int j = 0; j < 32; ++j)
-                                if (j < ncols) atomicAdd(o + j * w_stride, __uint_as_float(r[j]));
+                                if (j < ncols) o[j * w_stride] = w_live ? __uint_as_float(r[j]) : 0.f;
                         }
                         __syncwarp();  // tcgen05.ld is warp-collective: reconverge before the next chunk
                     }
                 }
                 tc_fence_before();
                 __syncwarp();
-                if (threadIdx.x == 64) NML_STAMP(titer, 4);
                 if (lane == 0) mbar_arrive(smem_u32(&tempty_bar[0]));
                 continue;
             }
@@ -1282,6 +1260,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             int pix_n = 0, pix_h = 0, pix_w = 0;  // forward walk: this row's pixel within its phase grid
             size_t row_off = 0;     // NHWC / wgrad: element offset of column 0; NCHW: pixel offset
             size_t col_stride = 1;  // element distance between consecutive columns
+            int kslice = kz;        // K slice of this tile (K-split forward walk, split-K weight gradient)
             if (kMode == MODE_FPROP) {
                 int p = 0;
                 while (p + 1 < P.n_phases && tile >= P.phases[p + 1].tile_begin) ++p;
@@ -1320,6 +1299,7 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 if (kPair) mt = 2 * mt + static_cast<int>(cta_rank);
                 int per = (P.kblocks_total + P.split_k - 1) / P.split_k;
                 k_iters = max(min(z * per + per, P.kblocks_total) - z * per, 0);
+                kslice = z;
                 int gi = mt * (kTileM / P.kb) + row / P.kb;
                 int t = gi / P.c_blocks;
                 int cib = gi - t * P.c_blocks;
@@ -1335,6 +1315,14 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                     // dW[plain][patch][tap]
                     row_off = static_cast<size_t>(pc) * P.n_taps + t;
                     col_stride = static_cast<size_t>(P.c_patch) * P.n_taps;
+                }
+                if (P.split_k > 1) {
+                    // partial sums go to this slice's plane, [column][row of the tile walk]: lanes are consecutive
+                    // rows, so every column store coalesces; rows beyond the gradient are written too (the planes
+                    // are padded to whole tiles) and never read
+                    row_valid = true;
+                    row_off = static_cast<size_t>(mt) * kTileM + row;
+                    col_stride = static_cast<size_t>(P.ld_plane);
                 }
             }
             if (kMode == MODE_FPROP && NML_IS_TMA_OUT(kOutMode) && P.bias != nullptr) {
@@ -1380,7 +1368,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 break;
             }
             tc_fence_after();
-            if (threadIdx.x == 64) NML_STAMP(titer, 3);
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * P.bn;
             const int col_base = ntile * P.bn;
             if (kMode == MODE_FPROP && NML_IS_TMA_OUT(kOutMode)) {
@@ -1719,13 +1706,22 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
                 }
                 const int cg = col_base + c0;
                 const int ncols = min(32, P.c_out - cg);
-                if (kMode == MODE_WGRAD || (kOutMode == OUT_NHWC && P.fsplit > 1)) {  // partial sums
-                    if (row_valid && k_iters > 0) {
-                        float* o = reinterpret_cast<float*>(P.out) + row_off +
+                if (kMode == MODE_WGRAD || (kOutMode == OUT_NHWC && P.fsplit > 1)) {
+                    // the gradient itself (one K slice) or this K slice's plane of partial sums; an empty
+                    // slice stores the zeros loaded above
+                    if (row_valid) {
+                        float* o = reinterpret_cast<float*>(P.out) + static_cast<size_t>(kslice) * P.plane_elems + row_off +
                                    static_cast<size_t>(cg) * col_stride;
+                        if (kMode == MODE_FPROP && ncols == 32 && (P.ld_out & 3) == 0) {
 #pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                            if (j < ncols) atomicAdd(o + j * col_stride, __uint_as_float(r[j]));
+                            for (int q = 0; q < 8; ++q)
+                                reinterpret_cast<float4*>(o)[q] = make_float4(__uint_as_float(r[4 * q]), __uint_as_float(r[4 * q + 1]),
+                                                                              __uint_as_float(r[4 * q + 2]), __uint_as_float(r[4 * q + 3]));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; ++j)
+                                if (j < ncols) o[j * col_stride] = __uint_as_float(r[j]);
+                        }
                     }
                 } else {
                     float v[32];
@@ -1742,7 +1738,6 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
             }
             tc_fence_before();
             __syncwarp();
-            if (threadIdx.x == 64) NML_STAMP(titer, 4);
             if (lane == 0) {
                 if (kPair && !leader) mbar_arrive_cluster(map_to_cta(smem_u32(&tempty_bar[buf]), 0));
                 else mbar_arrive(smem_u32(&tempty_bar[buf]));

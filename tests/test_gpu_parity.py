@@ -306,16 +306,83 @@ def test_reference_shaped_matmul(oracle):
     ops.device_status()
 
 
-def test_forward_is_bitwise_repeatable():
-    g = geometry(cases.CONV_CASES["c72"])
-    x, w, b, dy = cases.draw_conv("c72", cases.CONV_CASES["c72"])
-    xd, wd, bd = dev(x), dev(w), dev(b)
-    a = ops.conv_forward(g, xd, wd, bd, math="3xtf32")
-    c = ops.conv_forward(g, xd, wd, bd, math="3xtf32")
-    d1 = ops.conv_backward_data(g, dev(dy), wd, math="3xtf32")
-    d2 = ops.conv_backward_data(g, dev(dy), wd, math="3xtf32")
+def _twice(fn):
+    a = fn()
+    a = [t.clone() for t in (a if isinstance(a, tuple) else (a,))]
+    b = fn()
+    b = b if isinstance(b, tuple) else (b,)
+    return all(torch.equal(u, v) for u, v in zip(a, b))
+
+
+@pytest.mark.parametrize("name", ["c72", "s_conv_k4_s2", "s_convT_k4_s2", "w_3x3_64_64", "w_stem_7x7_s2", "w_convT_to_5",
+                                  "p_3x3_128_32", "k4_s2"])
+def test_every_result_is_bitwise_repeatable(name):
+    """y, dx, dw and db of two identical calls are equal bit for bit, also where the K loop is split over
+    CTAs (forward walk of the few-pixel layers, every weight gradient): the slices' partial sums go to
+    planes that are added in a fixed order, never through atomics.  The reference's single cuBLAS GEMM per
+    pass is repeatable too."""
+    case = {**cases.CONV_CASES, **WALK_SHAPES, **WGRAD_PATCH_SHAPES}[name]
+    g = geometry(case)
+    x, w, b, dy = cases.draw_conv(name, case)
+    h = torch.float16
+    xd, dyd, wd = dev(x, h, nhwc=True), dev(dy, h, nhwc=True), dev(w, h)
+    bd = dev(b, h) if b is not None else None
+    assert _twice(lambda: ops.conv_forward(g, xd, wd, bd, layout="nhwc")), "y (fp16)"
+    assert _twice(lambda: ops.conv_backward_data(g, dyd, wd, layout="nhwc")), "dx (fp16)"
+    assert _twice(lambda: ops.conv_backward_weight(g, xd, dyd, layout="nhwc")), "dw, db (fp16)"
+    x32, dy32, w32 = dev(x), dev(dy), dev(w)
+    assert _twice(lambda: ops.conv_forward(g, x32, w32, dev(b) if b is not None else None, math="3xtf32")), "y (fp32)"
+    assert _twice(lambda: ops.conv_backward_data(g, dy32, w32, math="3xtf32")), "dx (fp32)"
+    assert _twice(lambda: ops.conv_backward_weight(g, x32, dy32, math="3xtf32")), "dw, db (fp32)"
     ops.device_status()
-    assert torch.equal(a, c) and torch.equal(d1, d2)
+
+
+@pytest.mark.parametrize("rows,fin,fout", [(4096, 512, 2048), (3000, 264, 520)])
+def test_linear_is_bitwise_repeatable(rows, fin, fout):
+    """Linear at a split-K shape (the weight gradient of 4096 x 512 -> 2048 is cut into K slices)."""
+    gen = torch.Generator(device=DEV).manual_seed(3)
+    x = torch.randn(rows, fin, device=DEV, generator=gen).half()
+    w = (torch.randn(fout, fin, device=DEV, generator=gen) * 0.05).half()
+    b = torch.randn(fout, device=DEV, generator=gen).half()
+    dy = torch.randn(rows, fout, device=DEV, generator=gen).half()
+    assert _twice(lambda: ops.linear_forward(x, w, b))
+    assert _twice(lambda: ops.linear_backward_data(dy, w))
+    assert _twice(lambda: ops.linear_backward_weight(x, dy))
+    ops.device_status()
+
+
+@pytest.mark.parametrize("name", ["ref_basic", "ref_stride", "c72", "k4_s2", "k7_s2_p3", "ref_transpose", "t_k4_s2", "t_rect_dil"])
+def test_reference_shaped_fp16_dtype_forward(name, oracle):
+    """`dtype=Float16` tensors (the reference's run_conv2d<half> / run_conv_transpose2d<half>,
+    nectarml/csrc/ops/tensor/conv/conv2d.cpp:71-211): NCHW fp16 in, NCHW fp16 out, no half_precision flag."""
+    case = cases.CONV_CASES[name]
+    x, w, b, dy = cases.draw_conv(name, case)
+    r = oracle.round_f16
+    y_o = oracle_all(oracle, case, r(x), r(w), r(b) if b is not None else None, dy)[0]
+    h = torch.float16
+    y = shim_forward(case, dev(x, h), dev(w, h), dev(b, h) if b is not None else None, F16, False)
+    ops.device_status()
+    assert y.dtype == np.float16
+    assert_f16(y.astype(np.float32), y_o, f"{name} fp16-dtype y")
+
+
+def test_matmul_2d_right_operand_is_shared_over_the_batch(oracle):
+    """[B, T, d] @ [d, 4d]: the projection of an attention block.  The reference advances the 2-D right
+    operand per batch entry and reads past its end (nectarml/csrc/ops/tensor/matmul.cpp:27,39); here it is
+    shared, which is what `np.matmul` (the reference's CPU backend, nectarml/cpu/math.py:80-81) computes."""
+    rng = np.random.default_rng(6)
+    for a_shape, b_shape in (((3, 50, 64), (64, 256)), ((2, 4, 17, 40), (40, 24))):
+        a = rng.standard_normal(a_shape, dtype=np.float32)
+        b = rng.standard_normal(b_shape, dtype=np.float32)
+        a32, b32 = dev(a), dev(b)
+        ptr = _nectarml.tensor.matmul(a32.data_ptr(), b32.data_ptr(), list(a_shape), list(b_shape), F32)
+        got = fetch(ptr, a_shape[:-1] + (b_shape[-1],))
+        assert_f32(got, oracle.matmul(a, b), f"matmul {a_shape}x{b_shape}")
+        a16, b16 = dev(a, torch.float16), dev(b, torch.float16)
+        ptr = _nectarml.tensor.matmul(a16.data_ptr(), b16.data_ptr(), list(a_shape), list(b_shape), F16)
+        got = fetch(ptr, a_shape[:-1] + (b_shape[-1],), np.float16)
+        assert_f16(got, oracle.matmul(oracle.round_f16(a), oracle.round_f16(b)), f"matmul fp16 {a_shape}")
+    ops.device_status()
 
 
 def test_workspace_too_small_is_reported():
