@@ -1,15 +1,19 @@
 #!/usr/bin/env python
 """Benchmark of the dense-contraction path.
 
-One "step" = forward + input-gradient + weight-gradient (with bias gradient) of every layer of
-the workload, inputs resident in HBM.  The default workload is the Linear projection sweep
+One "step" = forward + input-gradient + weight-gradient (with bias gradient) of every layer of a
+workload, inputs resident in HBM.  The headline workload (`value`) is the Linear projection sweep
 (X[B*T, d] @ W^T[d, 4d] + b for d in {512, 1024, 2048}, B*T in {4096, 16384}; fp16 storage, fp32
-accumulation; synthetic N(0,1) activations, Xavier-uniform weights).  Prints ONE JSON line.
+accumulation; synthetic N(0,1) activations, Xavier-uniform weights).  The same JSON line carries,
+under `workloads`, the ResNet-style conv shapes at batch 256, the 16 convolutions of the Pix2Pix
+U-Net generator at batch 64 and the fp32 (3xTF32) Conv2d of configuration 1, each with its own
+roofline block, per-layer table and CPU baseline.  Prints ONE JSON line.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload linear|resnet]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload linear|resnet|pix2pix|config1]
 
-N > 1 is launched with torch.distributed.run; every rank owns its own shard of the rows (weak
-scaling: per-GPU work fixed), the weight and bias gradients are all-reduced over NCCL each step.
+N > 1 is launched with torch.distributed.run; every rank owns its own shard of the rows / batch (weak
+scaling: per-GPU work fixed); the weight and bias gradients are written straight into flat fp32
+buckets that are all-reduced over NCCL, a bucket as soon as its layers are done.
 `--impl reference` times the reference's own CPU arithmetic for the path (NumPy matmul, all host
 threads) on a bounded sample of the same workload.
 """
@@ -18,6 +22,7 @@ from __future__ import annotations
 import argparse
 import json
 import os
+import re
 import statistics
 import subprocess
 import sys
@@ -30,8 +35,6 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 LINEAR_SWEEP = [(rows, d) for d in (512, 1024, 2048) for rows in (4096, 16384)]
-# ResNet-style conv shapes at batch 256 (7x7 s2 p3 3->64 @224 is left to the parity tests until
-# its small-channel path exists): (c_in, hw, c_out, k, stride, pad)
 # (c_in, input h = w, c_out, kernel, stride, padding, transposed)
 RESNET_SWEEP = [(3, 224, 64, 7, 2, 3, False), (64, 56, 64, 3, 1, 1, False), (256, 56, 64, 1, 1, 0, False),
                 (128, 28, 128, 3, 2, 1, False), (1024, 14, 2048, 1, 2, 0, False)]
@@ -44,6 +47,8 @@ PIX2PIX_SWEEP = ([(ci, hw, co, 4, 2, 1, False) for ci, hw, co in
                   ((512, 1, 512), (1024, 2, 512), (1024, 4, 512), (1024, 8, 512), (1024, 16, 256), (512, 32, 128),
                    (256, 64, 64), (128, 128, 3))])
 PIX2PIX_BATCH = 64
+CONFIG1_LAYER = (64, 56, 64, 3, 1, 1, False)
+CONFIG1_BATCH = 8
 LINEAR_NAME = ("Linear sweep X[B*T,d]@W^T[d,4d]+b, d in {512,1024,2048} x B*T in {4096,16384}, "
                "forward+dgrad+wgrad+db, fp16 storage / fp32 accumulate")
 RESNET_NAME = ("ResNet-style conv shapes, batch 256 per GPU, NHWC fp16: 7x7 s2 3->64 @224, 3x3 64->64 @56, 1x1 256->64 @56, "
@@ -51,6 +56,13 @@ RESNET_NAME = ("ResNet-style conv shapes, batch 256 per GPU, NHWC fp16: 7x7 s2 3
 PIX2PIX_NAME = ("Pix2Pix U-Net generator convolutions, batch 64 per GPU, NHWC fp16: 8 Conv2d 4x4 s2 p1 "
                 "(3-64-128-256-512-512-512-512-512) + 8 ConvTranspose2d 4x4 s2 p1 with skip-concat inputs; "
                 "forward+dgrad+wgrad+db of every layer (normalisation and activations not included)")
+CONFIG1_NAME = ("Conv2d fp32 NCHW N=8 64->64 56x56 3x3 s1 p1 with bias, 3xTF32 arithmetic (three tf32 tensor-core "
+                "products per fp32 product), forward+dgrad+wgrad+db through the reference-shaped tensors")
+WORKLOAD_NAMES = {"linear": LINEAR_NAME, "resnet": RESNET_NAME, "pix2pix": PIX2PIX_NAME, "config1": CONFIG1_NAME}
+
+# NVIDIA's B200 datasheet figures for dense (no 2:4 sparsity) tensor throughput, TFLOP/s
+NOMINAL_F16_TFLOPS = 2250.0
+NOMINAL_TF32_TFLOPS = 1100.0
 
 
 def measured_peaks():
@@ -58,12 +70,24 @@ def measured_peaks():
     if os.path.exists(path):
         with open(path) as f:
             p = json.load(f)
-        return {"tflops": float(p["bf16_tflops"]), "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
-    return {"tflops": 1590.0, "hbm_gbs": 6650.0, "source": "fallback"}
+        return {"tflops": float(p["bf16_tflops"]), "tflops_sustained": float(p.get("bf16_tflops_sustained", 0)) or None,
+                "hbm_gbs": float(p["hbm_gbs"]), "source": "measured"}
+    return {"tflops": 1590.0, "tflops_sustained": 1400.0, "hbm_gbs": 6650.0, "source": "fallback"}
+
+
+def profiled_traffic(workload: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum per contraction launch, averaged over one step, read from
+    the ncu summary under profiles/ (a line `traffic_bytes_per_launch: <number>`); None without a capture."""
+    path = os.path.join(ROOT, "profiles", f"launch_list_{workload}.md")
+    try:
+        m = re.search(r"traffic_bytes_per_launch:\s*([0-9.eE+]+)", open(path).read())
+        return float(m.group(1)) if m else None
+    except OSError:
+        return None
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons while a timed region runs."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
@@ -84,17 +108,12 @@ class ClockSampler:
         for line in self.proc.stdout:
             self.lines.append((time.time(), line.strip()))
 
-    def stop(self, t0: float, t1: float):
+    def window(self, t0: float, t1: float):
+        """Clock summary of the samples taken between t0 and t1 (the sampler keeps running)."""
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=2)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
         sm, mx, reasons = [], [], set()
-        for ts, line in self.lines:
+        for ts, line in list(self.lines):
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6 or not (t0 - 0.05 <= ts <= t1 + 0.15):
                 continue
@@ -107,7 +126,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         if not sm:  # timed region shorter than one sample: fall back to every sample taken
-            for _, line in self.lines:
+            for _, line in list(self.lines):
                 parts = [p.strip() for p in line.split(",")]
                 try:
                     sm.append(float(parts[0]))
@@ -117,8 +136,17 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "reasons": sorted(reasons), "samples": len(sm)}
 
+    def stop(self):
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
 
-# ------------------------------------------------------------------ workloads --
+
+# ------------------------------------------------------------------ accounting --
 def linear_flops(rows, d):
     return 3 * 2.0 * rows * d * 4 * d  # forward + dgrad + wgrad
 
@@ -128,28 +156,226 @@ def conv_flops(batch, c_in, hw, c_out, k, s, p, transposed=False):
     return 3 * 2.0 * batch * ho * ho * c_out * c_in * k * k
 
 
-def make_linear_host(seed, sweep):
-    """Pinned host buffers of one step's inputs, and the parameters."""
-    import torch
-    rng = np.random.default_rng(seed)
-    layers = []
-    for rows, d in sweep:
-        bound = np.sqrt(6.0 / (d + 4 * d))
-        layers.append({
-            "rows": rows, "d": d,
-            "x": torch.from_numpy(rng.standard_normal((rows, d), dtype=np.float32)).half().pin_memory(),
-            "dy": torch.from_numpy(rng.standard_normal((rows, 4 * d), dtype=np.float32)).half().pin_memory(),
-            "w": torch.from_numpy(rng.uniform(-bound, bound, (4 * d, d)).astype(np.float32)).half(),
-            "b": torch.zeros(4 * d, dtype=torch.float16),
-        })
-    return layers
+def conv_out_hw(hw, k, s, p, transposed):
+    return (hw - 1) * s - 2 * p + k if transposed else (hw + 2 * p - k) // s + 1
+
+
+def pass_bytes(n_x, n_w, n_y, es):
+    """Algorithmic minimum traffic of the three passes: each operand and result once at storage width, the weight
+    gradient in fp32."""
+    return [(n_x + n_w + n_y) * es, (n_y + n_w + n_x) * es, (n_x + n_y) * es + n_w * 4]
+
+
+# ------------------------------------------------------------------ workloads --
+class Workload:
+    """Tensors of one workload on one GPU, its step, and the algorithmic work of every contraction launch."""
+
+    def __init__(self, key, dev, rank, world, only=""):
+        import torch
+        from nectarml_b200 import ops
+        from nectarml_b200.ops import ConvGeometry
+        from nectarml_b200.parallel import GradientBucket
+        self.key, self.dev, self.world = key, dev, world
+        self.ops, self.torch = ops, torch
+        self.launches = []  # one dict per contraction launch of a step, in launch order
+        self.layers = []
+        self.math = "3xtf32" if key == "config1" else "f16"
+        self.es = 4 if key == "config1" else 2
+        if key == "linear":
+            # under data parallelism the largest shapes go first, so that their gradient all-reduce overlaps the
+            # smaller shapes' kernels (on one GPU the listed order measured 1-2 % faster)
+            sweep = sorted(LINEAR_SWEEP, key=lambda s_: -s_[0] * s_[1] * s_[1]) if world > 1 else list(LINEAR_SWEEP)
+            if only:  # profiling aid: one shape of the sweep, e.g. --only 16384x1024
+                r_, d_ = (int(v) for v in only.lower().split("x"))
+                sweep = [(r_, d_)]
+            rng = np.random.default_rng(1235 + rank)
+            for rows, d in sweep:
+                bound = np.sqrt(6.0 / (d + 4 * d))
+                l = {"name": f"linear {rows}x{d}->{4 * d}", "rows": rows, "d": d,
+                     "x": torch.from_numpy(rng.standard_normal((rows, d), dtype=np.float32)).half().pin_memory(),
+                     "dy": torch.from_numpy(rng.standard_normal((rows, 4 * d), dtype=np.float32)).half().pin_memory(),
+                     "w": torch.from_numpy(rng.uniform(-bound, bound, (4 * d, d)).astype(np.float32)).half(),
+                     "b": torch.zeros(4 * d, dtype=torch.float16)}
+                l.update(xd=l["x"].to(dev), dyd=l["dy"].to(dev), wd=l["w"].to(dev), bd=l["b"].to(dev),
+                         y=torch.empty(rows, 4 * d, dtype=torch.float16, device=dev),
+                         dx=torch.empty(rows, d, dtype=torch.float16, device=dev))
+                self.layers.append(l)
+                by = pass_bytes(rows * d, 4 * d * d, rows * 4 * d, 2)
+                for i, ps in enumerate(("fwd", "dgrad", "wgrad")):
+                    self.launches.append({"layer": l["name"], "pass": ps, "flops": 2.0 * rows * d * 4 * d, "bytes": by[i]})
+            shapes = []
+            for l in self.layers:
+                shapes += [(4 * l["d"], l["d"]), (4 * l["d"],)]
+        else:
+            sweep, batch = {"resnet": (RESNET_SWEEP, RESNET_BATCH), "pix2pix": (PIX2PIX_SWEEP, PIX2PIX_BATCH),
+                            "config1": ([CONFIG1_LAYER], CONFIG1_BATCH)}[key]
+            if only:  # profiling aid: one layer of the sweep by index
+                sweep = [sweep[int(only)]]
+            torch.manual_seed(1237 + rank)
+            nchw = key == "config1"
+            dt = torch.float32 if nchw else torch.float16
+            self.layout = "nchw" if nchw else "nhwc"
+            for (ci, hw, co, k, s, p, tr) in sweep:
+                g = ConvGeometry(batch, ci, hw, hw, co, k, k, (s, s), (p, p), transposed=tr)
+                ho, wo = g.out_hw()
+                std = 0.02 if key == "pix2pix" else float(np.sqrt(2.0 / (ci * k * k)))
+                xs, ys = g.act_shape("in", self.layout), g.act_shape("out", self.layout)
+                l = {"g": g, "name": f"{'convT' if tr else 'conv'} {k}x{k} s{s} {ci}->{co} @{hw}",
+                     "xd": torch.randn(*xs, device=dev).to(dt), "dyd": torch.randn(*ys, device=dev).to(dt),
+                     "wd": (torch.randn(*g.weight_shape(), device=dev) * std).to(dt),
+                     "bd": (torch.randn(co, device=dev) * 0.1).to(dt) if nchw else None,
+                     "y": torch.empty(*ys, dtype=dt, device=dev), "dx": torch.empty(*xs, dtype=dt, device=dev)}
+                self.layers.append(l)
+                fl = conv_flops(batch, ci, hw, co, k, s, p, tr) / 3
+                by = pass_bytes(batch * hw * hw * ci, ci * co * k * k, batch * ho * wo * co, self.es)
+                for i, ps in enumerate(("fwd", "dgrad", "wgrad")):
+                    self.launches.append({"layer": l["name"], "pass": ps, "flops": fl, "bytes": by[i]})
+            shapes = []
+            for l in self.layers:
+                shapes += [l["g"].weight_shape(), (l["g"].c_out,)]
+        # Weight and bias gradients land directly in flat fp32 buckets (dw / db are caller-owned pointers of the
+        # C ABI), so that one all-reduce per bucket moves them: the first bucket holds the layers that run first.
+        n_first = max(1, len(self.layers) // 3)
+        self.buckets = [GradientBucket(shapes[:2 * n_first], dev)]
+        if len(self.layers) > n_first:
+            self.buckets.append(GradientBucket(shapes[2 * n_first:], dev))
+        for i, l in enumerate(self.layers):
+            b, j = (0, i) if i < n_first else (1, i - n_first)
+            l["dw"], l["db"], l["bucket"] = self.buckets[b].view(2 * j), self.buckets[b].view(2 * j + 1), b
+        self.last_of_bucket = {n_first - 1: 0, len(self.layers) - 1: len(self.buckets) - 1}
+        self.step_flops = sum(x["flops"] for x in self.launches)
+        self.bytes_resident = sum(t.numel() * t.element_size() for l in self.layers for t in
+                                  (l["xd"], l["dyd"], l["wd"], l["y"], l["dx"], l["dw"]))
+
+    def layer_passes(self, l):
+        ops = self.ops
+        if self.key == "linear":
+            ops.linear_forward(l["xd"], l["wd"], l["bd"], out=l["y"])
+            ops.linear_backward_data(l["dyd"], l["wd"], out=l["dx"])
+            ops.linear_backward_weight(l["xd"], l["dyd"], dw=l["dw"], db=l["db"])
+        else:
+            ops.conv_forward(l["g"], l["xd"], l["wd"], l["bd"], layout=self.layout, math=self.math, out=l["y"])
+            ops.conv_backward_data(l["g"], l["dyd"], l["wd"], layout=self.layout, math=self.math, out=l["dx"])
+            ops.conv_backward_weight(l["g"], l["xd"], l["dyd"], layout=self.layout, math=self.math, dw=l["dw"], db=l["db"])
+
+    def step(self, communicate=True):
+        pending = []
+        for i, l in enumerate(self.layers):
+            self.layer_passes(l)
+            if self.world > 1 and communicate and i in self.last_of_bucket:
+                pending.append(self.buckets[self.last_of_bucket[i]].all_reduce(async_op=True))
+        for p in pending:
+            if p is not None:
+                p.wait()
+
+
+def time_steps(torch, dist, world, dev, fn, steps):
+    """Times `steps` calls on the device between barriers; returns max-over-ranks milliseconds."""
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    barrier()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+    return float(ms.item())
+
+
+def measure(wl, args, peaks, sampler, torch, dist, steps, per_layer):
+    """Warm-up, the timed region, and per-launch CUDA-event durations of the contraction launches of one workload."""
+    ops, world, dev = wl.ops, wl.world, wl.dev
+    for _ in range(max(args.warmup, 3)):
+        wl.step()
+    ops.device_status()
+    launches0 = ops.launch_count()
+    t0 = time.time()
+    ms_total = time_steps(torch, dist, world, dev, wl.step, steps)
+    t1 = time.time()
+    launches = ops.launch_count() - launches0
+    clocks = sampler.window(t0, t1) if sampler else None
+    ops.device_status()
+    comm_ms_exposed = None
+    if world > 1:  # the same step without its all-reduces: the difference is what the exchange costs the step
+        ms_nocomm = time_steps(torch, dist, world, dev, lambda: wl.step(communicate=False), steps)
+        comm_ms_exposed = (ms_total - ms_nocomm) / steps
+
+    # per-launch durations of the contraction kernel (with its second-stage reduction where it has one),
+    # CUDA events on the launching stream
+    n1 = len(wl.launches)
+    n_rec = n1 * steps
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ops.profile_begin(n_rec)
+    for _ in range(steps):
+        wl.step()
+    per_launch_ms = ops.profile_end(n_rec)
+    reps = len(per_launch_ms) // n1 if n1 else 0
+    mean = [sum(per_launch_ms[i:reps * n1:n1]) / reps for i in range(n1)] if reps else []
+    kern_ms = sum(mean)
+    tensor_peak = (NOMINAL_TF32_TFLOPS / 3) if wl.key == "config1" else peaks["tflops"]
+    ridge = tensor_peak * 1e12 / (peaks["hbm_gbs"] * 1e9)  # FLOP per byte above which the tensor pipe is the bound
+    table, t_tensor, f_tensor, t_hbm, b_hbm = [], 0.0, 0.0, 0.0, 0.0
+    for i, x in enumerate(wl.launches):
+        if not mean:
+            break
+        sec = mean[i] * 1e-3
+        hbm = (x["flops"] / x["bytes"]) < ridge
+        if hbm:
+            t_hbm += sec
+            b_hbm += x["bytes"]
+        else:
+            t_tensor += sec
+            f_tensor += x["flops"]
+        row = {"layer": x["layer"], "pass": x["pass"], "us": round(mean[i] * 1e3, 1),
+               "tflops": round(x["flops"] / sec / 1e12, 1), "gbs": round(x["bytes"] / sec / 1e9, 0),
+               "bound": "hbm" if hbm else "tensor",
+               "frac": round((x["bytes"] / sec / 1e9 / peaks["hbm_gbs"]) if hbm else (x["flops"] / sec / 1e12 / tensor_peak), 3)}
+        table.append(row)
+    achieved = wl.step_flops / (kern_ms * 1e-3) / 1e12 if kern_ms > 0 else None
+    src = f"{peaks['source']} burst bf16 (MEASURED_PEAKS.json)" if peaks["source"] == "measured" else "fallback"
+    if wl.key == "config1":
+        src = "NVIDIA nominal dense tf32 (1100 TFLOP/s) / 3, three tensor-core products per fp32 product"
+    nominal = (NOMINAL_TF32_TFLOPS / 3) if wl.key == "config1" else NOMINAL_F16_TFLOPS
+    roof = {"bound": "tensor", "achieved": achieved, "peak": tensor_peak, "unit": "TFLOP/s",
+            "frac": (achieved / tensor_peak) if achieved else None, "peak_source": src,
+            "frac_nominal": (achieved / nominal) if achieved else None,
+            "nominal_peak": nominal, "nominal_source": "NVIDIA B200 datasheet, dense (half of the 2:4-sparsity figure)",
+            "kernel": "umma_conv_kernel", "launches_timed": len(per_launch_ms),
+            "traffic": profiled_traffic(wl.key),
+            "algorithmic_bytes_per_launch": sum(x["bytes"] for x in wl.launches) / max(n1, 1)}
+    if peaks.get("tflops_sustained") and wl.key != "config1":
+        roof["frac_of_sustained_peak"] = (achieved / peaks["tflops_sustained"]) if achieved else None
+    if t_hbm > 0:  # the layers below the ridge, judged on bandwidth
+        roof["hbm_bound_launches"] = {"achieved": b_hbm / t_hbm / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                                      "frac": b_hbm / t_hbm / 1e9 / peaks["hbm_gbs"],
+                                      "launches": sum(1 for r in table if r["bound"] == "hbm")}
+    if t_tensor > 0:
+        roof["tensor_bound_launches"] = {"achieved": f_tensor / t_tensor / 1e12, "peak": tensor_peak, "unit": "TFLOP/s",
+                                         "frac": f_tensor / t_tensor / 1e12 / tensor_peak,
+                                         "launches": sum(1 for r in table if r["bound"] == "tensor")}
+    out = {"value": wl.step_flops * world * steps / (ms_total * 1e-3) / 1e12, "unit": "TFLOP/s",
+           "ms_per_step": ms_total / steps, "steps": steps, "gpu_launches": int(launches), "clocks": clocks,
+           "roofline": roof, "workload": WORKLOAD_NAMES[wl.key]}
+    if comm_ms_exposed is not None:
+        out["comm_ms_exposed"] = comm_ms_exposed
+        out["roofline"]["achieved_scope"] = "rank 0's GPU, all-reduces in flight"
+    if per_layer:
+        out["per_layer"] = table
+    return out
 
 
 def run_gpu(args):
     import torch
     import torch.distributed as dist
     from nectarml_b200 import build, ops
-    from nectarml_b200.ops import ConvGeometry
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -161,52 +387,42 @@ def run_gpu(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
     build.build()
-
     peaks = measured_peaks()
-    flops_per_launch = []  # algorithmic FLOPs of each contraction launch of one step, in launch order
+    sampler = ClockSampler(local) if rank == 0 else None
+    if sampler:
+        sampler.start()
+        time.sleep(0.25)
 
+    wl = Workload(args.workload, dev, rank, world, args.only)
+    head = measure(wl, args, peaks, sampler, torch, dist, args.steps, per_layer=True)
+
+    # sustained leg: the same step back to back for >= 3 s, with the clocks seen (time x MHz compares rounds
+    # measured at different clocks)
+    sustained = None
+    if args.sustain_s > 0:
+        est_ms = max(head["ms_per_step"], 1e-3)
+        n = max(10, int(args.sustain_s * 1e3 / est_ms))
+        t0 = time.time()
+        ms = time_steps(torch, dist, world, dev, wl.step, n)
+        t1 = time.time()
+        ck = sampler.window(t0 + 0.5, t1) if sampler else None
+        sustained = {"value": wl.step_flops * world * n / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "seconds": ms * 1e-3,
+                     "steps": n, "ms_per_step": ms / n, "clocks": ck,
+                     "ms_per_step_x_sm_mhz": (ms / n) * ck["sm_mhz"] if ck and ck.get("sm_mhz") else None,
+                     "frac_of_sustained_peak": (wl.step_flops * n / (ms * 1e-3) / 1e12 / peaks["tflops_sustained"])
+                     if peaks.get("tflops_sustained") and wl.key != "config1" else None}
+        ops.device_status()
+
+    # End to end through the public API with host buffers (pinned), copies inside the timed region: every
+    # layer's x and dy come from the host and ALL its results (y, dx, dw, db) go back to it.  Copies run on their
+    # own streams, ordered against the compute stream by events, so a layer's transfers overlap the other
+    # layers' kernels; every step ends with the compute stream waiting for that step's last device-to-host copy.
+    e2e = None
     if args.workload == "linear":
-        # under data parallelism the largest shapes go first, so that their gradient all-reduce overlaps the
-        # smaller shapes' kernels (on one GPU the listed order measured 1-2 % faster)
-        sweep = sorted(LINEAR_SWEEP, key=lambda s_: -s_[0] * s_[1] * s_[1]) if world > 1 else list(LINEAR_SWEEP)
-        if args.only:  # profiling aid: one shape of the sweep, e.g. --only 16384x1024
-            r_, d_ = (int(v) for v in args.only.lower().split("x"))
-            sweep = [(r_, d_)]
-        host = make_linear_host(1235 + rank, sweep)
-        layers = []
-        for h in host:
-            rows, d = h["rows"], h["d"]
-            layers.append({
-                **h,
-                "xd": h["x"].to(dev), "dyd": h["dy"].to(dev), "wd": h["w"].to(dev), "bd": h["b"].to(dev),
-                "y": torch.empty(rows, 4 * d, dtype=torch.float16, device=dev),
-                "dx": torch.empty(rows, d, dtype=torch.float16, device=dev),
-                "dw": torch.empty(4 * d, d, dtype=torch.float32, device=dev),
-                "db": torch.empty(4 * d, dtype=torch.float32, device=dev),
-                "dw_host": torch.empty(4 * d, d, dtype=torch.float32).pin_memory(),
-                "db_host": torch.empty(4 * d, dtype=torch.float32).pin_memory(),
-            })
-            flops_per_launch += [2.0 * rows * d * 4 * d] * 3
-        step_flops = sum(linear_flops(l["rows"], l["d"]) for l in layers)
-        bytes_resident = sum(t.numel() * t.element_size() for l in layers for t in
-                             (l["xd"], l["dyd"], l["wd"], l["y"], l["dx"], l["dw"]))
-
-        def step():
-            pending = []
-            for l in layers:
-                ops.linear_forward(l["xd"], l["wd"], l["bd"], out=l["y"])
-                ops.linear_backward_data(l["dyd"], l["wd"], out=l["dx"])
-                ops.linear_backward_weight(l["xd"], l["dyd"], dw=l["dw"], db=l["db"])
-                if world > 1:
-                    pending.append(dist.all_reduce(l["dw"], async_op=True))
-                    pending.append(dist.all_reduce(l["db"], async_op=True))
-            for p in pending:
-                p.wait()
-
-        # End-to-end step: the same calls, with each layer's inputs coming from pinned host memory and its
-        # gradients going back to it.  Copies run on their own streams, ordered against the compute stream
-        # by events, so a layer's transfers overlap the other layers' kernels inside the step; every step
-        # ends with the compute stream waiting for that step's last device-to-host copy.
+        layers = wl.layers
+        for l in layers:
+            for k_ in ("y", "dx", "dw", "db"):
+                l[k_ + "_host"] = torch.empty(l[k_].shape, dtype=l[k_].dtype).pin_memory()
         s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
         ev_in = [torch.cuda.Event() for _ in layers]
         ev_done = [torch.cuda.Event() for _ in layers]
@@ -222,149 +438,66 @@ def run_gpu(args):
                     ev_in[i].record(s_in)
             for i, l in enumerate(layers):
                 cur.wait_event(ev_in[i])
-                cur.wait_event(ev_out[i])  # the previous step's copy of dw / db has left the device
-                ops.linear_forward(l["xd"], l["wd"], l["bd"], out=l["y"])
-                ops.linear_backward_data(l["dyd"], l["wd"], out=l["dx"])
-                ops.linear_backward_weight(l["xd"], l["dyd"], dw=l["dw"], db=l["db"])
+                cur.wait_event(ev_out[i])  # the previous step's copies of this layer's results have left the device
+                wl.layer_passes(l)
                 if world > 1:
                     dist.all_reduce(l["dw"])
                     dist.all_reduce(l["db"])
                 ev_done[i].record(cur)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_done[i])
-                    l["dw_host"].copy_(l["dw"], non_blocking=True)
-                    l["db_host"].copy_(l["db"], non_blocking=True)
+                    for k_ in ("y", "dx", "dw", "db"):
+                        l[k_ + "_host"].copy_(l[k_], non_blocking=True)
                     ev_out[i].record(s_out)
             cur.wait_event(ev_out[-1])
 
-        h2d = sum(l["x"].numel() * 2 + l["dy"].numel() * 2 for l in layers)
-        d2h = sum(l["dw"].numel() * 4 + l["db"].numel() * 4 for l in layers)
-        workload = {"workload": LINEAR_NAME,
-                    "layers": len(layers), "rows_per_gpu": sum(l["rows"] for l in layers)}
-    else:
-        torch.manual_seed(1237 + rank)
-        sweep, batch = (RESNET_SWEEP, RESNET_BATCH) if args.workload == "resnet" else (PIX2PIX_SWEEP, PIX2PIX_BATCH)
-        if args.only:  # profiling aid: one layer of the sweep by index, e.g. --workload resnet --only 1
-            sweep = [sweep[int(args.only)]]
-        layers = []
-        for (ci, hw, co, k, s, p, tr) in sweep:
-            g = ConvGeometry(batch, ci, hw, hw, co, k, k, (s, s), (p, p), transposed=tr)
-            ho, wo = g.out_hw()
-            std = np.sqrt(2.0 / (ci * k * k)) if args.workload == "resnet" else 0.02
-            layers.append({
-                "g": g, "name": f"{'convT' if tr else 'conv'} {k}x{k} s{s} {ci}->{co} @{hw}",
-                "xd": torch.randn(batch, hw, hw, ci, device=dev).half(),
-                "dyd": torch.randn(batch, ho, wo, co, device=dev).half(),
-                "wd": (torch.randn(*g.weight_shape(), device=dev) * std).half(),
-                "y": torch.empty(batch, ho, wo, co, dtype=torch.float16, device=dev),
-                "dx": torch.empty(batch, hw, hw, ci, dtype=torch.float16, device=dev),
-            })
-            flops_per_launch += [conv_flops(batch, ci, hw, co, k, s, p, tr) / 3] * 3
-        step_flops = sum(flops_per_launch)
-        bytes_resident = sum(t.numel() * t.element_size() for l in layers for t in (l["xd"], l["dyd"], l["y"], l["dx"]))
-        grads = {}
-
-        def step():
-            pending = []
-            for i, l in enumerate(layers):
-                ops.conv_forward(l["g"], l["xd"], l["wd"], None, layout="nhwc", out=l["y"])
-                ops.conv_backward_data(l["g"], l["dyd"], l["wd"], layout="nhwc", out=l["dx"])
-                grads[i] = ops.conv_backward_weight(l["g"], l["xd"], l["dyd"], layout="nhwc")
-                if world > 1:
-                    pending.append(dist.all_reduce(grads[i][0], async_op=True))
-                    pending.append(dist.all_reduce(grads[i][1], async_op=True))
-            for p in pending:
-                p.wait()
-
-        h2d = d2h = 0
-        workload = {"workload": RESNET_NAME if args.workload == "resnet" else PIX2PIX_NAME,
-                    "layers": len(layers)}
-
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-
-    def timed(fn, steps):
-        """Times `steps` calls on the device; returns max-over-ranks milliseconds."""
-        barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(steps):
-            fn()
-        e1.record()
-        barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
-        if world > 1:
-            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
-
-    for _ in range(max(args.warmup, 3)):
-        step()
-    ops.device_status()
-
-    sampler = ClockSampler(local) if rank == 0 else None
-    if sampler:
-        sampler.start()
-        time.sleep(0.25)
-    launches0 = ops.launch_count()
-    t0 = time.time()
-    ms_total = timed(lambda: step(), args.steps)
-    t1 = time.time()
-    launches = ops.launch_count() - launches0
-    clocks = sampler.stop(t0, t1) if sampler else None
-    ops.device_status()
-
-    # per-launch durations of the contraction kernel, CUDA events on the launching stream
-    n_rec = len(flops_per_launch) * args.steps
-    barrier()
-    ops.profile_begin(n_rec)
-    for _ in range(args.steps):
-        step()
-    per_launch_ms = ops.profile_end(n_rec)
-    kern_ms = sum(per_launch_ms)
-    per_layer = None
-    if args.per_layer and per_launch_ms:
-        n1 = len(flops_per_launch)
-        mean = [sum(per_launch_ms[i::n1]) / len(per_launch_ms[i::n1]) for i in range(n1)]
-        names = [l["name"] if "name" in l else f"linear {l['rows']}x{l['d']}->{4 * l['d']}" for l in layers]
-        per_layer = [{"layer": names[i // 3], "pass": ("fwd", "dgrad", "wgrad")[i % 3], "us": round(mean[i] * 1e3, 1),
-                      "tflops": round(flops_per_launch[i] / (mean[i] * 1e-3) / 1e12, 1)} for i in range(n1)]
-    kern_flops = sum(flops_per_launch) * (len(per_launch_ms) / max(len(flops_per_launch), 1))
-    achieved = kern_flops / (kern_ms * 1e-3) / 1e12 if kern_ms > 0 else None
-
-    # end to end through the public API with host buffers (pinned), copies inside the timed region
-    e2e = None
-    if args.workload == "linear":
         for _ in range(2):
             step_e2e()
         e2e_steps = max(2, min(args.steps, 5))
-        e2e_ms = timed(step_e2e, e2e_steps)
-        for l in layers:  # the gradients that reached the host are the ones on the device
-            if not torch.equal(l["db_host"], l["db"].cpu()):
-                raise SystemExit("bench.py: end-to-end leg returned stale gradients")
-        e2e = {"value": step_flops * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)}
+        e2e_ms = time_steps(torch, dist, world, dev, step_e2e, e2e_steps)
+        for l in layers:  # what reached the host is what is on the device
+            if not torch.equal(l["db_host"], l["db"].cpu()) or not torch.equal(l["y_host"][:64], l["y"][:64].cpu()):
+                raise SystemExit("bench.py: end-to-end leg returned stale results")
+        h2d = sum(l["x"].numel() * 2 + l["dy"].numel() * 2 for l in layers)
+        d2h = sum(l[k_].numel() * l[k_].element_size() for l in layers for k_ in ("y", "dx", "dw", "db"))
+        e2e = {"value": wl.step_flops * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "returns": "y, dx, dw, db of every layer"}
+
+    # the other workloads of the path, each with its own roofline block (device-resident inputs)
+    others = {}
+    if args.workload == "linear" and not args.only and not args.headline_only:
+        del wl
+        torch.cuda.empty_cache()
+        for key, label in (("resnet", "resnet_conv"), ("pix2pix", "pix2pix_conv"), ("config1", "config1_fp32_3xtf32")):
+            w2 = Workload(key, dev, rank, world)
+            others[label] = measure(w2, args, peaks, sampler, torch, dist, max(3, min(args.steps, 20)), per_layer=True)
+            if rank == 0 and world == 1 and not args.no_cpu_baseline:
+                others[label]["cpu_baseline"] = cpu_baseline(key, budget_s=4.0)
+            del w2
+            torch.cuda.empty_cache()
+    if sampler:
+        sampler.stop()
 
     out = None
     if rank == 0:
-        value = step_flops * world * args.steps / (ms_total * 1e-3) / 1e12
         out = {
-            "metric": "conv/linear fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_total / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16 (fp32 accumulate)",
+            "metric": "conv/linear fwd+bwd TFLOP/s", "value": head["value"], "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": head["ms_per_step"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32 via 3xTF32 (fp32 accumulate)" if args.workload == "config1" else "f16 (fp32 accumulate)",
             "data": "synthetic", "impl": "nectarml_b200",
-            "config": {**workload, "parallelism": f"dp{world} (rows sharded, NCCL all-reduce of dW/db)" if world > 1 else "1 GPU",
-                       "l2": f"working set {bytes_resident / 1e6:.0f} MB per GPU cycles through the 126 MB L2 every step"},
-            "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
-            "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["tflops"], "unit": "TFLOP/s",
-                         "frac": (achieved / peaks["tflops"]) if achieved else None,
-                         "peak_source": f"{peaks['source']} burst bf16 (MEASURED_PEAKS.json)" if peaks["source"] == "measured" else "fallback",
-                         "kernel": "umma_conv_kernel", "launches_timed": len(per_launch_ms),
-                         "traffic": TRAFFIC_BYTES_PER_LAUNCH.get(args.workload)},
+            "config": {"workload": WORKLOAD_NAMES[args.workload], "layers": len(head.get("per_layer", [])) // 3,
+                       "parallelism": f"dp{world} (rows / batch sharded, NCCL all-reduce of two flat dW/db buckets)" if world > 1 else "1 GPU",
+                       "l2": "inputs and outputs of one step exceed the 126 MB L2 several times over; every step cycles through it"},
+            "e2e": e2e, "gpu_launches": head["gpu_launches"], "clocks": head["clocks"], "roofline": head["roofline"],
+            "per_layer": head.get("per_layer"),
         }
-        if per_layer:
-            out["per_layer"] = per_layer
+        if "comm_ms_exposed" in head:
+            out["comm_ms_exposed"] = head["comm_ms_exposed"]
+        if sustained:
+            out["sustained"] = sustained
+        if others:
+            out["workloads"] = others
         if world == 1 and not args.no_cpu_baseline:
             out["cpu_baseline"] = cpu_baseline(args.workload, budget_s=12.0)
         print(json.dumps(out), flush=True)
@@ -372,11 +505,6 @@ def run_gpu(args):
         dist.barrier()
         dist.destroy_process_group()
     return out
-
-
-# dram__bytes_read.sum + dram__bytes_write.sum per contraction launch, averaged over one step of the
-# workload, from the ncu capture summarised under profiles/ (None until a capture exists).
-TRAFFIC_BYTES_PER_LAUNCH = {"linear": 164.5e6, "resnet": None, "pix2pix": None}
 
 
 # ------------------------------------------------------------ CPU reference arm --
@@ -403,13 +531,18 @@ def cpu_linear_sample(budget_s: float):
     return done_flops, t_used, "Linear layers " + ",".join(names) + " of the sweep, fp32 np.matmul"
 
 
-def cpu_conv_sample(budget_s: float):
+def cpu_conv_sample(workload: str, budget_s: float):
+    """One layer of the conv workload at batch 1 through the C port of the reference's NumPy loops."""
     from oracle import nectar_oracle as orc
     rng = np.random.default_rng(1237)
-    ci, hw, co, k, s, p, _ = RESNET_SWEEP[1]
+    if workload == "pix2pix":
+        ci, hw, co, k, s, p, tr = PIX2PIX_SWEEP[2]  # 4x4 s2 128->256 @64
+    else:
+        ci, hw, co, k, s, p, tr = RESNET_SWEEP[1]  # 3x3 64->64 @56 (also configuration 1's layer)
+    ho = conv_out_hw(hw, k, s, p, tr)
     x = rng.standard_normal((1, ci, hw, hw), dtype=np.float32)
     w = rng.standard_normal((co, ci, k, k), dtype=np.float32)
-    dy = rng.standard_normal((1, co, hw, hw), dtype=np.float32)
+    dy = rng.standard_normal((1, co, ho, ho), dtype=np.float32)
     t0 = time.perf_counter()
     n = 0
     while time.perf_counter() - t0 < budget_s / 3 or n == 0:
@@ -418,7 +551,7 @@ def cpu_conv_sample(budget_s: float):
         orc.conv2d_backward_weight(dy, x, w.shape, (s, s), (p, p))
         n += 1
     return n * conv_flops(1, ci, hw, co, k, s, p), time.perf_counter() - t0, \
-        "3x3 64->64 @56 at batch 1 (measured at reduced batch), C port of the reference's NumPy loops, 1 thread"
+        f"conv {k}x{k} s{s} {ci}->{co} @{hw} at batch 1 (measured at reduced batch), C port of the reference's NumPy loops, 1 thread"
 
 
 def cpu_threads():
@@ -442,7 +575,7 @@ def cpu_baseline(workload: str, budget_s: float):
         cores = cpu_threads()
         flops, secs, what = cpu_linear_sample(budget_s)
     else:
-        flops, secs, what = cpu_conv_sample(budget_s)
+        flops, secs, what = cpu_conv_sample(workload, budget_s)
         cores = 1
     return {"value": flops / secs / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": what,
             "seconds": secs}
@@ -466,12 +599,11 @@ def run_reference(args):
     value = flops / secs / 1e12
     base = {k: base[k] for k in ("unit", "cores", "kind", "sample")}
     base["value"] = value
-    name = {"linear": LINEAR_NAME, "resnet": RESNET_NAME, "pix2pix": PIX2PIX_NAME}[args.workload]
     print(json.dumps({
         "metric": "conv/linear fwd+bwd TFLOP/s", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": warm, "ms_per_step": secs / args.steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32 (CPU)", "data": "synthetic", "impl": "reference",
-        "config": {"workload": name, "parallelism": "host cores of rank 0",
+        "config": {"workload": WORKLOAD_NAMES[args.workload], "parallelism": "host cores of rank 0",
                    "note": "the reference's CPU arithmetic (NumPy, fp32) on a bounded sample of the workload per step"},
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -484,9 +616,9 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="nectarml_b200", choices=["nectarml_b200", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "resnet", "pix2pix"])
-    ap.add_argument("--per-layer", action="store_true",
-                    help="add the contraction kernel's mean time per layer and pass to the JSON line")
+    ap.add_argument("--workload", default="linear", choices=["linear", "resnet", "pix2pix", "config1"])
+    ap.add_argument("--headline-only", action="store_true", help="skip the extra workloads of the default run")
+    ap.add_argument("--sustain-s", type=float, default=3.0, help="seconds of the sustained leg (0: skip)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=0.0,
                     help="seconds of CPU work per step of the reference arm (default: sized from --steps)")

@@ -1579,7 +1579,9 @@ int nml_conv_output_size(const nml_conv_desc* d, int* h_out, int* w_out) {
 int nml_conv_workspace_size(const nml_conv_desc* d, int pass, size_t* bytes) {
     if (!d || !bytes) return NML_ERR_INVALID;
     Bump ws{nullptr, 0, 0, true};
-    int rc = conv_pass(d, pass, nullptr, nullptr, d, nullptr, nullptr, ws, nullptr);
+    // (bias and db stand in as non-null so that the scratch behind them is counted)
+    float db_stand_in;
+    int rc = conv_pass(d, pass, nullptr, nullptr, d, nullptr, &db_stand_in, ws, nullptr);
     *bytes = round_up(ws.off, 256);
     return rc;
 }
@@ -1587,7 +1589,8 @@ int nml_conv_workspace_size(const nml_conv_desc* d, int pass, size_t* bytes) {
 int nml_linear_workspace_size(const nml_linear_desc* d, int pass, size_t* bytes) {
     if (!d || !bytes) return NML_ERR_INVALID;
     Bump ws{nullptr, 0, 0, true};
-    int rc = linear_pass(d, pass, nullptr, nullptr, d, nullptr, nullptr, ws, nullptr);
+    float db_stand_in;
+    int rc = linear_pass(d, pass, nullptr, nullptr, d, nullptr, &db_stand_in, ws, nullptr);
     *bytes = round_up(ws.off, 256);
     return rc;
 }

@@ -168,13 +168,19 @@ def conv_backward_data(g: ConvGeometry, dy: torch.Tensor, w: torch.Tensor, *, la
 
 
 def conv_backward_weight(g: ConvGeometry, x: torch.Tensor, dy: torch.Tensor, *, layout: str = "nchw",
-                         math: str = "f16", want_bias_grad: bool = True,
+                         math: str = "f16", want_bias_grad: bool = True, dw: Optional[torch.Tensor] = None,
+                         db: Optional[torch.Tensor] = None,
                          ws: Optional[Workspace] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+    """dw (fp32, weight-shaped) and db (fp32, c_out); pass ``dw`` / ``db`` to have them written in place, e.g.
+    into the views of a flat gradient bucket."""
     assert tuple(x.shape) == g.act_shape("in", layout)
     assert tuple(dy.shape) == g.act_shape("out", layout)
     assert x.dtype == dy.dtype
-    dw = torch.empty(g.weight_shape(), dtype=torch.float32, device=x.device)
-    db = torch.empty(g.c_out, dtype=torch.float32, device=x.device) if want_bias_grad else None
+    if dw is None:
+        dw = torch.empty(g.weight_shape(), dtype=torch.float32, device=x.device)
+    if db is None and want_bias_grad:
+        db = torch.empty(g.c_out, dtype=torch.float32, device=x.device)
+    assert dw.dtype == torch.float32 and dw.numel() == g.c_in * g.c_out * g.kh * g.kw
     d = g.desc(_dt(x.dtype), layout, NML_F32, layout, NML_F32, math, False)
     wp, wb = _conv_ws(d, NML_PASS_BACKWARD_WEIGHT, ws, x.device)
     check(_lib.load().nml_conv_backward_weight(C.byref(d), _ptr(x), _ptr(dy), _ptr(dw), _ptr(db), wp, wb,
