@@ -294,6 +294,29 @@ def measure(wl, args, peaks, sampler, torch, dist, steps, per_layer):
     for _ in range(max(args.warmup, 3)):
         wl.step()
     ops.device_status()
+
+    def settle():
+        # Every leg below is a burst of a few tens of milliseconds that starts from an idle GPU, so that they see
+        # the same clocks (a 1 kW part power-caps within ~0.1 s of dense tensor work; the sustained leg of the
+        # headline workload reports that regime).
+        torch.cuda.synchronize()
+        time.sleep(args.idle_s)
+        if world > 1:
+            dist.barrier()
+
+    # per-launch durations of the contraction kernel (with its second-stage reduction where it has one),
+    # CUDA events on the launching stream
+    n1 = len(wl.launches)
+    n_rec = n1 * steps
+    settle()
+    t0 = time.time()
+    ops.profile_begin(n_rec)
+    for _ in range(steps):
+        wl.step()
+    per_launch_ms = ops.profile_end(n_rec)
+    clocks_launches = sampler.window(t0, time.time()) if sampler else None
+
+    settle()
     launches0 = ops.launch_count()
     t0 = time.time()
     ms_total = time_steps(torch, dist, world, dev, wl.step, steps)
@@ -303,20 +326,9 @@ def measure(wl, args, peaks, sampler, torch, dist, steps, per_layer):
     ops.device_status()
     comm_ms_exposed = None
     if world > 1:  # the same step without its all-reduces: the difference is what the exchange costs the step
+        settle()
         ms_nocomm = time_steps(torch, dist, world, dev, lambda: wl.step(communicate=False), steps)
         comm_ms_exposed = (ms_total - ms_nocomm) / steps
-
-    # per-launch durations of the contraction kernel (with its second-stage reduction where it has one),
-    # CUDA events on the launching stream
-    n1 = len(wl.launches)
-    n_rec = n1 * steps
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ops.profile_begin(n_rec)
-    for _ in range(steps):
-        wl.step()
-    per_launch_ms = ops.profile_end(n_rec)
     reps = len(per_launch_ms) // n1 if n1 else 0
     mean = [sum(per_launch_ms[i:reps * n1:n1]) / reps for i in range(n1)] if reps else []
     kern_ms = sum(mean)
@@ -349,7 +361,7 @@ def measure(wl, args, peaks, sampler, torch, dist, steps, per_layer):
             "frac_nominal": (achieved / nominal) if achieved else None,
             "nominal_peak": nominal, "nominal_source": "NVIDIA B200 datasheet, dense (half of the 2:4-sparsity figure)",
             "kernel": "umma_conv_kernel", "launches_timed": len(per_launch_ms),
-            "traffic": profiled_traffic(wl.key),
+            "clocks": clocks_launches, "traffic": profiled_traffic(wl.key),
             "algorithmic_bytes_per_launch": sum(x["bytes"] for x in wl.launches) / max(n1, 1)}
     if peaks.get("tflops_sustained") and wl.key != "config1":
         roof["frac_of_sustained_peak"] = (achieved / peaks["tflops_sustained"]) if achieved else None
@@ -488,7 +500,8 @@ def run_gpu(args):
             "data": "synthetic", "impl": "nectarml_b200",
             "config": {"workload": WORKLOAD_NAMES[args.workload], "layers": len(head.get("per_layer", [])) // 3,
                        "parallelism": f"dp{world} (rows / batch sharded, NCCL all-reduce of two flat dW/db buckets)" if world > 1 else "1 GPU",
-                       "l2": "inputs and outputs of one step exceed the 126 MB L2 several times over; every step cycles through it"},
+                       "l2": "inputs and outputs of one step exceed the 126 MB L2 several times over; every step cycles through it",
+                       "timing": f"every timed region is a burst of `steps` steps from an idle GPU ({args.idle_s} s pause); `sustained` is the same step for >= {args.sustain_s} s"},
             "e2e": e2e, "gpu_launches": head["gpu_launches"], "clocks": head["clocks"], "roofline": head["roofline"],
             "per_layer": head.get("per_layer"),
         }
@@ -619,6 +632,7 @@ def main():
     ap.add_argument("--workload", default="linear", choices=["linear", "resnet", "pix2pix", "config1"])
     ap.add_argument("--headline-only", action="store_true", help="skip the extra workloads of the default run")
     ap.add_argument("--sustain-s", type=float, default=3.0, help="seconds of the sustained leg (0: skip)")
+    ap.add_argument("--idle-s", type=float, default=0.5, help="pause before each timed burst")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-budget", type=float, default=0.0,
                     help="seconds of CPU work per step of the reference arm (default: sized from --steps)")

@@ -224,7 +224,7 @@ static int load_helper_kernels() {
         (const void*)pack_phase_weights_kernel<float, float>, (const void*)pack_phase_weights_kernel<float, __half>,
         (const void*)pack_phase_weights_kernel<__half, float>, (const void*)pack_phase_weights_kernel<__half, __half>,
         (const void*)to_float_kernel<__half>, (const void*)colsum_finish_kernel,
-        (const void*)wgrad_reduce_rows4_kernel, (const void*)wgrad_reduce_kernel,
+        (const void*)wgrad_reduce_rows4_kernel, (const void*)wgrad_reduce_kernel, (const void*)wgrad_reduce_deep4_kernel,
     };
     for (const void* f : fns) {
         cudaFuncAttributes a;
@@ -1260,14 +1260,20 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     // that minimises it; ties go to the smaller split (fewer atomics).
     int split = 1;
     {
-        long long best = -1;
+        // Costs in microseconds: a K block of a 256-wide tile keeps the tensor pipe busy for ~0.27 us (four
+        // 128-clock MMAs); more than one slice adds the second-stage reduction, which writes and re-reads one
+        // plane of dW per slice and then writes dW (~5 TB/s), plus its launch.
+        const double block_us = 0.27 * P.bn / 256.0 * P.passes;
+        const double dw_bytes = 4.0 * g.plain_c * g.patch_c * T;
+        double best = -1;
         const int max_split = std::min(P.kblocks_total, 64);
         for (int sp = 1; sp <= max_split; ++sp) {
             int per_sp = ceil_div(P.kblocks_total, sp);
             int real = ceil_div(P.kblocks_total, per_sp);  // every slice gets at least one K block
             if (real != sp) continue;
             long long rounds = ceil_div(mn_tiles * sp, P.pair ? sms / 2 : sms);
-            long long cost = rounds * (per_sp + 4);
+            double cost = rounds * (per_sp + 4) * block_us;
+            if (sp > 1) cost += 3.0 + (2.0 * sp + 1.0) * dw_bytes / 5e6;
             if (best < 0 || cost < best) {
                 best = cost;
                 split = sp;
@@ -1365,7 +1371,10 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
     if (rc) return rc;
     if (split > 1) {
         const bool vec_ok = (reinterpret_cast<uintptr_t>(g.dw) & 15) == 0;
-        if (P.wpatch && vec_ok && dw_elems % 4 == 0) {
+        if (P.wpatch && vec_ok && dw_elems % 4 == 0 && split > 8) {
+            const size_t total4 = dw_elems / 4;
+            wgrad_reduce_deep4_kernel<<<static_cast<unsigned>((total4 + 31) / 32), dim3(32, 8), 0, st>>>(planes, g.dw, split, plane_elems, total4);
+        } else if (P.wpatch && vec_ok && dw_elems % 4 == 0) {
             const int blocks = static_cast<int>(std::min<size_t>((dw_elems / 4 + 255) / 256, 148 * 8));
             wgrad_reduce_rows4_kernel<<<blocks, 256, 0, st>>>(planes, g.dw, split, plane_elems, 1, static_cast<int>(dw_elems / 4), 0);
         } else if (!P.wpatch && !P.kw_pack && T == 1 && vec_ok && g.patch_c % 4 == 0) {

@@ -288,7 +288,8 @@ __global__ void __launch_bounds__(256) finish_rows_kernel(const float* __restric
         const size_t p = i / C;
         const int c = static_cast<int>(i - p * C);
         float v = acc[i];
-        for (int z = 1; z < planes; ++z) v += acc[static_cast<size_t>(z) * total + i];
+#pragma unroll 4
+        for (int z = 1; z < planes; ++z) v += __ldg(acc + static_cast<size_t>(z) * total + i);
         if (bias != nullptr) v += bias[c];
         if (round_f16) v = __half2float(__float2half_rn(v));
         size_t o = i;
@@ -379,6 +380,37 @@ __global__ void __launch_bounds__(256) wgrad_reduce_rows4_kernel(const float* __
             a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
         }
         reinterpret_cast<float4*>(dw)[i] = a;
+    }
+}
+
+// The same for many planes over a small gradient (the patch walk cuts K into one slice per SM): a thread
+// per element would walk ~150 planes one load latency at a time.  blockDim = (32, 8): lane ty adds
+// planes ty, ty + 8, ... of its float4 in order, then the eight running sums are added in order -- a
+// fixed association, so still bitwise repeatable.  Planes are laid out like dW.
+__global__ void __launch_bounds__(256) wgrad_reduce_deep4_kernel(const float* __restrict__ planes, float* __restrict__ dw,
+                                                                 int split, size_t plane_elems, size_t total4) {
+    __shared__ float4 part[8][32];
+    const size_t i = blockIdx.x * 32ull + threadIdx.x;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < total4) {
+        const float4* src = reinterpret_cast<const float4*>(planes) + i;
+        const size_t step = plane_elems / 4;
+#pragma unroll 4
+        for (int z = threadIdx.y; z < split; z += 8) {
+            const float4 b = __ldg(src + z * step);
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+    }
+    part[threadIdx.y][threadIdx.x] = a;
+    __syncthreads();
+    if (threadIdx.y == 0 && i < total4) {
+        float4 t = part[0][threadIdx.x];
+#pragma unroll
+        for (int k = 1; k < 8; ++k) {
+            const float4 b = part[k][threadIdx.x];
+            t.x += b.x; t.y += b.y; t.z += b.z; t.w += b.w;
+        }
+        reinterpret_cast<float4*>(dw)[i] = t;
     }
 }
 
