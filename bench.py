@@ -182,9 +182,9 @@ class Workload:
         self.math = "3xtf32" if key == "config1" else "f16"
         self.es = 4 if key == "config1" else 2
         if key == "linear":
-            # under data parallelism the largest shapes go first, so that their gradient all-reduce overlaps the
-            # smaller shapes' kernels (on one GPU the listed order measured 1-2 % faster)
-            sweep = sorted(LINEAR_SWEEP, key=lambda s_: -s_[0] * s_[1] * s_[1]) if world > 1 else list(LINEAR_SWEEP)
+            # under data parallelism the layers with the largest gradients go first, so that their all-reduce
+            # overlaps the other layers' kernels (on one GPU the listed order measured 1-2 % faster)
+            sweep = sorted(LINEAR_SWEEP, key=lambda s_: (-s_[1], -s_[0])) if world > 1 else list(LINEAR_SWEEP)
             if only:  # profiling aid: one shape of the sweep, e.g. --only 16384x1024
                 r_, d_ = (int(v) for v in only.lower().split("x"))
                 sweep = [(r_, d_)]
@@ -234,36 +234,76 @@ class Workload:
             for l in self.layers:
                 shapes += [l["g"].weight_shape(), (l["g"].c_out,)]
         # Weight and bias gradients land directly in flat fp32 buckets (dw / db are caller-owned pointers of the
-        # C ABI), so that one all-reduce per bucket moves them: the first bucket holds the layers that run first.
-        n_first = max(1, len(self.layers) // 3)
-        self.buckets = [GradientBucket(shapes[:2 * n_first], dev)]
-        if len(self.layers) > n_first:
-            self.buckets.append(GradientBucket(shapes[2 * n_first:], dev))
-        for i, l in enumerate(self.layers):
-            b, j = (0, i) if i < n_first else (1, i - n_first)
-            l["dw"], l["db"], l["bucket"] = self.buckets[b].view(2 * j), self.buckets[b].view(2 * j + 1), b
-        self.last_of_bucket = {n_first - 1: 0, len(self.layers) - 1: len(self.buckets) - 1}
+        # C ABI), so that one all-reduce per bucket moves them.  Layers are taken in execution order; a bucket is
+        # closed once it holds at least `bucket_ratio` times what is still to come (and 8 MB), so the early
+        # buckets are large and overlap the remaining layers while the last, exposed one is small.
+        ratio = float(os.environ.get("NML_BENCH_BUCKET_RATIO", "0.5"))
+        numel = [int(np.prod(shapes[2 * i])) + int(np.prod(shapes[2 * i + 1])) for i in range(len(self.layers))]
+        groups, cur, acc = [], [], 0
+        for i, n_ in enumerate(numel):
+            cur.append(i)
+            acc += n_
+            rest = sum(numel[i + 1:])
+            if rest and acc >= ratio * rest and acc * 4 >= (8 << 20):
+                groups.append(cur)
+                cur, acc = [], 0
+        if cur:
+            groups.append(cur)
+        self.buckets, self.last_of_bucket = [], {}
+        for b, grp in enumerate(groups):
+            bucket = GradientBucket([sh for i in grp for sh in (shapes[2 * i], shapes[2 * i + 1])], dev)
+            self.buckets.append(bucket)
+            for j, i in enumerate(grp):
+                self.layers[i]["dw"], self.layers[i]["db"] = bucket.view(2 * j), bucket.view(2 * j + 1)
+            self.last_of_bucket[grp[-1]] = b
+        # SMs left to NCCL while an all-reduce may be in flight (see nml_set_sm_limit); 0 = none
+        self.sm_reserve = int(os.environ.get("NML_BENCH_SM_RESERVE", "8")) if world > 1 else 0
+        self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        if world > 1:  # launch order of the data-parallel step: every weight gradient, then forward + dgrad per layer
+            self.launches = [x for x in self.launches if x["pass"] == "wgrad"] + [x for x in self.launches if x["pass"] != "wgrad"]
         self.step_flops = sum(x["flops"] for x in self.launches)
         self.bytes_resident = sum(t.numel() * t.element_size() for l in self.layers for t in
                                   (l["xd"], l["dyd"], l["wd"], l["y"], l["dx"], l["dw"]))
 
-    def layer_passes(self, l):
+    def forward_and_dgrad(self, l):
         ops = self.ops
         if self.key == "linear":
             ops.linear_forward(l["xd"], l["wd"], l["bd"], out=l["y"])
             ops.linear_backward_data(l["dyd"], l["wd"], out=l["dx"])
-            ops.linear_backward_weight(l["xd"], l["dyd"], dw=l["dw"], db=l["db"])
         else:
             ops.conv_forward(l["g"], l["xd"], l["wd"], l["bd"], layout=self.layout, math=self.math, out=l["y"])
             ops.conv_backward_data(l["g"], l["dyd"], l["wd"], layout=self.layout, math=self.math, out=l["dx"])
+
+    def wgrad(self, l):
+        ops = self.ops
+        if self.key == "linear":
+            ops.linear_backward_weight(l["xd"], l["dyd"], dw=l["dw"], db=l["db"])
+        else:
             ops.conv_backward_weight(l["g"], l["xd"], l["dyd"], layout=self.layout, math=self.math, dw=l["dw"], db=l["db"])
 
+    def layer_passes(self, l):
+        self.forward_and_dgrad(l)
+        self.wgrad(l)
+
     def step(self, communicate=True):
+        if self.world == 1:
+            for l in self.layers:
+                self.layer_passes(l)
+            return
+        # Data parallel: the weight gradients are the only thing exchanged, so they are computed first (largest
+        # first) and each bucket's all-reduce is issued as soon as its layers are done; the forward and
+        # input-gradient passes of all layers then run while the exchange is in flight, on the SMs NCCL leaves.
         pending = []
         for i, l in enumerate(self.layers):
-            self.layer_passes(l)
-            if self.world > 1 and communicate and i in self.last_of_bucket:
+            self.wgrad(l)
+            if communicate and i in self.last_of_bucket:
                 pending.append(self.buckets[self.last_of_bucket[i]].all_reduce(async_op=True))
+                if self.sm_reserve:  # the kernels that follow share the GPU with this exchange
+                    self.ops.set_sm_limit(self.sms - self.sm_reserve)
+        for l in self.layers:
+            self.forward_and_dgrad(l)
+        if self.sm_reserve:
+            self.ops.set_sm_limit(0)
         for p in pending:
             if p is not None:
                 p.wait()
@@ -375,7 +415,7 @@ def measure(wl, args, peaks, sampler, torch, dist, steps, per_layer):
                                          "launches": sum(1 for r in table if r["bound"] == "tensor")}
     out = {"value": wl.step_flops * world * steps / (ms_total * 1e-3) / 1e12, "unit": "TFLOP/s",
            "ms_per_step": ms_total / steps, "steps": steps, "gpu_launches": int(launches), "clocks": clocks,
-           "roofline": roof, "workload": WORKLOAD_NAMES[wl.key]}
+           "roofline": roof, "workload": WORKLOAD_NAMES[wl.key], "buckets": len(wl.buckets), "sm_reserve": wl.sm_reserve}
     if comm_ms_exposed is not None:
         out["comm_ms_exposed"] = comm_ms_exposed
         out["roofline"]["achieved_scope"] = "rank 0's GPU, all-reduces in flight"
@@ -397,6 +437,9 @@ def run_gpu(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        # a fixed, small CTA budget for NCCL: the contraction kernels are persistent, one CTA per SM, so every SM
+        # NCCL takes is one of theirs (NVSwitch keeps the all-reduce fast at a few CTAs)
+        os.environ.setdefault("NCCL_MAX_CTAS", os.environ.get("NML_BENCH_NCCL_CTAS", "8"))
         dist.init_process_group("nccl", device_id=dev)
     build.build()
     peaks = measured_peaks()
@@ -499,7 +542,9 @@ def run_gpu(args):
             "dtype": "f32 via 3xTF32 (fp32 accumulate)" if args.workload == "config1" else "f16 (fp32 accumulate)",
             "data": "synthetic", "impl": "nectarml_b200",
             "config": {"workload": WORKLOAD_NAMES[args.workload], "layers": len(head.get("per_layer", [])) // 3,
-                       "parallelism": f"dp{world} (rows / batch sharded, NCCL all-reduce of two flat dW/db buckets)" if world > 1 else "1 GPU",
+                       "parallelism": (f"dp{world} (rows / batch sharded, NCCL all-reduce of {head['buckets']} flat dW/db buckets, "
+                                       f"NCCL_MAX_CTAS={os.environ.get('NCCL_MAX_CTAS')}, {head['sm_reserve']} SMs left to it while in flight)")
+                       if world > 1 else "1 GPU",
                        "l2": "inputs and outputs of one step exceed the 126 MB L2 several times over; every step cycles through it",
                        "timing": f"every timed region is a burst of `steps` steps from an idle GPU ({args.idle_s} s pause); `sustained` is the same step for >= {args.sustain_s} s"},
             "e2e": e2e, "gpu_launches": head["gpu_launches"], "clocks": head["clocks"], "roofline": head["roofline"],

@@ -167,6 +167,15 @@ int nml_linear_backward_weight(const nml_linear_desc* d, const void* x, const vo
  * entry points above never block, so this is how a caller learns of a device-side give-up. */
 int nml_device_status(int* code);
 
+/* Caps the number of SMs the persistent kernels of later launches occupy (their grid and their tile
+ * / split-K plan); 0 restores "all SMs".  For callers that run something else on the GPU at the
+ * same time: a contraction kernel launched on every SM while an NCCL all-reduce of the previous
+ * layer's gradients holds a few of them leaves some of its CTAs waiting for a free SM, and with a
+ * static tile schedule those late CTAs set the kernel's duration; launching on `all - reserved`
+ * SMs avoids that.  Process-wide; workspace sizes depend on it, so query them under the same
+ * limit the call will run under.  The reference has no counterpart (single stream, no overlap). */
+int nml_set_sm_limit(int sms);
+
 /* Number of kernels this library has launched in this process (contraction kernel plus its
  * conversion / reduction helpers), for launch accounting. */
 long long nml_launch_count(void);

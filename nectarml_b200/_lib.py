@@ -49,6 +49,7 @@ SYMBOLS = {
     "nml_linear_backward_data": (_I, [C.POINTER(LinearDesc), _VP, _VP, _VP, _VP, _SZ, _VP]),
     "nml_linear_backward_weight": (_I, [C.POINTER(LinearDesc), _VP, _VP, _VP, _VP, _VP, _SZ, _VP]),
     "nml_init": (_I, []),
+    "nml_set_sm_limit": (_I, [_I]),
     "nml_device_status": (_I, [C.POINTER(_I)]),
     "nml_launch_count": (C.c_longlong, []),
     "nml_profile_begin": (_I, [_I]),

@@ -257,20 +257,26 @@ static int device_state(DeviceState** out) {
     return NML_OK;
 }
 
+// Upper bound on the SMs a launch may occupy (nml_set_sm_limit); 0 = all of them.
+static std::atomic<int> g_sm_limit{0};
+static inline int limited(int sms) {
+    const int lim = g_sm_limit.load(std::memory_order_relaxed);
+    return (lim > 0 && lim < sms) ? lim : sms;
+}
 // SM count the planner assumes: the current device's, or a B200's 148 where no device is present
 // (workspace-size queries work on a machine without a GPU).
 static int planning_sms() {
     static std::atomic<int> cached{0};
     int v = cached.load();
-    if (v > 0) return v;
+    if (v > 0) return limited(v);
     int dev = 0, sms = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
         sms <= 0) {
         (void)cudaGetLastError();
-        return 148;
+        return limited(148);
     }
     cached.store(sms);
-    return sms;
+    return limited(sms);
 }
 
 struct MathInfo {
@@ -501,7 +507,7 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st, int* open
         P.ring_bytes = P.stages * w_stage;
         {
             const long long run = 1ll * P.c_patch * P.n_taps * (P.kw_pack ? P.kw_count : 1);
-            P.w_coalesce = (tune().wcoal && 32 * run * 4 <= P.ring_bytes && P.num_tiles <= ds->sms) ? 1 : 0;
+            P.w_coalesce = (tune().wcoal && 32 * run * 4 <= P.ring_bytes && P.num_tiles <= limited(ds->sms)) ? 1 : 0;
         }
         smem = static_cast<size_t>(P.ring_bytes) + P.epi_warps * P.stg_bufs * kStagingBufBytes + fixed;
     } else if (P.patch) {
@@ -558,7 +564,7 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st, int* open
     }
     smem = std::max<size_t>(smem, 120 * 1024);  // one CTA per SM: each allocates its own TMEM
     P.err = ds->err;
-    int grid = P.pair ? 2 * std::min(P.num_tiles, ds->sms / 2) : std::min(P.num_tiles, ds->sms);
+    int grid = P.pair ? 2 * std::min(P.num_tiles, limited(ds->sms) / 2) : std::min(P.num_tiles, limited(ds->sms));
     if (grid <= 0) return NML_OK;
     P.wait_limit_ns = g_dbg_wait_limit_ns;
     int rec_slot = -1;
@@ -758,7 +764,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     int z_cap = 1;
     if (may_split) {
         const long long tiles_lb = 1ll * ((out_pixels + 127) / 128) * ceil_div(N, 256);
-        const int sms = ds ? ds->sms : planning_sms();
+        const int sms = ds ? limited(ds->sms) : planning_sms();
         z_cap = static_cast<int>(std::max<long long>(1, std::min<long long>(sms / tiles_lb, 1ll * (mi.planes == 2 ? 3 : 1) * T * c_blocks / 4)));
     }
     float* split_acc = may_split ? static_cast<float*>(ws.take(static_cast<size_t>(z_cap) * out_pixels * N * sizeof(float))) : nullptr;
@@ -940,7 +946,7 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
             int nt = ceil_div(N, cand[i]);
             int bn = static_cast<int>(round_up(ceil_div(N, nt), b_mn_major ? 64 : (forced == 16 ? 16 : 32)));
             if (bn > 256) continue;
-            double rounds = static_cast<double>(ceil_div(static_cast<int>(std::min<long long>(m_tiles_all * nt, 1 << 30)), ds->sms));
+            double rounds = static_cast<double>(ceil_div(static_cast<int>(std::min<long long>(m_tiles_all * nt, 1 << 30)), limited(ds->sms)));
             double t = rounds * bn * (bn > 128 ? cost[0] : bn > 64 ? cost[1] : cost[2]);
             if (best < 0 || t < best * 0.97) {  // prefer the wider tile unless the gain is clear
                 best = t;
@@ -1000,9 +1006,9 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
     for (int p = 0; p < n_phases; ++p)
         tiles_single += 1ll * ceil_div(P.phases[p].wq, 1 << P.wb_log2) * ceil_div(P.phases[p].hq, 1 << P.hb_log2) *
                         ceil_div(f.batch, 1 << P.nb_log2) * P.n_tiles;
-    const bool will_split = may_split && !P.patch && tiles_single * 2 <= ds->sms && k_iters_min >= 8;
+    const bool will_split = may_split && !P.patch && tiles_single * 2 <= limited(ds->sms) && k_iters_min >= 8;
     P.pair = (tune().pair && !P.patch && !will_split && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) && k_iters_min >= 4 &&
-              (P.out_mode == OUT_NHWC_TMA || P.out_mode == OUT_NCHW_TMA || P.out_mode == OUT_NCHW) && ds->sms >= 2) ? 1 : 0;
+              (P.out_mode == OUT_NHWC_TMA || P.out_mode == OUT_NCHW_TMA || P.out_mode == OUT_NCHW) && limited(ds->sms) >= 2) ? 1 : 0;
     int tiles = 0;
     for (int p = 0; p < n_phases; ++p) {
         Phase& ph = P.phases[p];
@@ -1028,11 +1034,11 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         P.fastdiv = (2ll * tiles < (1ll << 23) && 2ll * tiles * dmax < (1ll << 40)) ? 1 : 0;
     }
     P.fsplit = 1;
-    if (may_split && !P.pair && !P.patch && tiles * 2 <= ds->sms) {
+    if (may_split && !P.pair && !P.patch && tiles * 2 <= limited(ds->sms)) {
         int k_min = k_iters_min;
         for (int p = 0; p < n_phases; ++p)
             if (P.phases[p].tap_count > 0) k_min = std::min(k_min, P.passes * P.c_blocks * P.phases[p].tap_count);
-        const int z = std::min(z_cap, std::min(ds->sms / tiles, k_min / 4));  // at least 4 K iterations per slice
+        const int z = std::min(z_cap, std::min(limited(ds->sms) / tiles, k_min / 4));  // at least 4 K iterations per slice
         if (z >= 2) {
             P.fsplit = z;
             P.num_tiles = tiles * z;
@@ -1149,7 +1155,7 @@ static int run_wgrad_like(const WgradLike& g, Bump& ws, cudaStream_t st) {
         int rc = device_state(&ds);
         if (rc) return rc;
     }
-    const int sms = ds ? ds->sms : planning_sms();
+    const int sms = ds ? limited(ds->sms) : planning_sms();
     const void* pa[2] = {nullptr, nullptr};
     const void* pb[2];
     int cpa = 0, cpb = 0;
@@ -1645,6 +1651,12 @@ int nml_linear_backward_weight(const nml_linear_desc* d, const void* x, const vo
     if (!d || !x || !dy || !dw) return NML_ERR_INVALID;
     Bump ws{static_cast<uint8_t*>(workspace), 0, workspace ? workspace_bytes : 0, false};
     return linear_pass(d, NML_PASS_BACKWARD_WEIGHT, x, dy, nullptr, dw, db, ws, static_cast<cudaStream_t>(stream));
+}
+
+int nml_set_sm_limit(int sms) {
+    if (sms < 0) return NML_ERR_INVALID;
+    g_sm_limit.store(sms);
+    return NML_OK;
 }
 
 int nml_init(void) {

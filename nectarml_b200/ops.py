@@ -261,6 +261,11 @@ def device_status() -> int:
     return 0
 
 
+def set_sm_limit(sms: int) -> None:
+    """Caps the SMs later launches occupy (0: all); used while a collective shares the GPU."""
+    check(_lib.load().nml_set_sm_limit(int(sms)))
+
+
 def launch_count() -> int:
     return int(_lib.load().nml_launch_count())
 
