@@ -424,6 +424,78 @@ def measure(wl, args, peaks, sampler, torch, dist, steps, per_layer):
     return out
 
 
+TRAIN_NAMES = {
+    "resnet50_step": ("ResNet-50 training step (bottleneck blocks [3,4,6,3], BatchNorm, ReLU, 1000-way Linear head), fp16 AMP with "
+                      "fp32 master weights, synthetic 224x224x3 images ~N(0,1), uniform labels, global batch 2048 sharded over the "
+                      "GPUs in micro-batches of at most 256, all-reduce of the flat weight-gradient buffer, fused SGD-momentum update"),
+    "pix2pix_step": ("Pix2Pix U-Net generator training step (8 Conv2d + 8 ConvTranspose2d 4x4 s2 p1, skip concatenation, BatchNorm + "
+                     "LeakyReLU(0.2) / ReLU, tanh), fp16 AMP, synthetic 256x256x3 inputs U[-1,1], L1 loss against a synthetic target, "
+                     "global batch 64 sharded over the GPUs, all-reduce of the flat weight-gradient buffer, fused SGD-momentum update"),
+}
+
+
+def measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world):
+    """img/s of one of the two conv-net training steps at a FIXED global batch (strong scaling)."""
+    from nectarml_b200 import ops, train
+    torch.manual_seed(4321 + rank)
+    if kind == "resnet50_step":
+        net, global_batch, hw, loss = train.ResNet50(dev), 2048, 224, "cross_entropy"
+        per_gpu = global_batch // world
+        micro = min(per_gpu, int(os.environ.get("NML_BENCH_MICRO_BATCH", "256")))
+    else:
+        net, global_batch, hw, loss = train.Pix2PixGenerator(dev), 64, 256, "l1"
+        per_gpu = global_batch // world
+        micro = per_gpu
+    net.init(seed=11)
+    n_micro = per_gpu // micro
+    step = train.TrainStep(net, loss, lr=0.01 if kind == "resnet50_step" else 2e-4, momentum=0.9, weight_decay=1e-4)
+    x = (torch.randn(micro, hw, hw, 3, device=dev) if loss == "cross_entropy" else torch.rand(micro, hw, hw, 3, device=dev) * 2 - 1).half()
+    target = torch.randint(0, 1000, (micro,), device=dev) if loss == "cross_entropy" else (torch.rand(micro, hw, hw, 3, device=dev) * 2 - 1).half()
+    count = global_batch if loss == "cross_entropy" else global_batch * hw * hw * 3
+    use_graphs = os.environ.get("NML_BENCH_GRAPHS", "1") != "0"
+    net.store.flops = 0.0
+    step.micro_batch(x, target, count, first=True, last=False)   # eager once: counts the algorithmic FLOPs, sizes the workspaces
+    flops_micro = net.store.flops
+    ops.device_status()
+    graphs = step.capture(x, target, count, accumulate_variants=(False, True) if n_micro > 1 else (False,)) if use_graphs else None
+
+    def one_step():
+        # (synthetic data: every micro-batch reuses the same resident tensors, as the static inputs of a graph do)
+        if graphs:
+            for i in range(n_micro):
+                graphs[i > 0][0].replay()
+            step.exchange_all()
+        else:
+            for i in range(n_micro):
+                step.micro_batch(x, target, count, first=(i == 0), last=(i == n_micro - 1))
+            net.store.wait_exchange()
+        step.optimizer_step()
+
+    for _ in range(2):
+        one_step()
+    ops.device_status()
+    steps = max(2, min(args.steps, 4 if kind == "resnet50_step" else 10))
+    torch.cuda.synchronize()
+    time.sleep(args.idle_s)
+    launches0 = ops.launch_count()
+    t0 = time.time()
+    ms = time_steps(torch, dist, world, dev, one_step, steps)
+    t1 = time.time()
+    launches = (ops.launch_count() - launches0) if not graphs else None
+    ops.device_status()
+    clocks = sampler.window(t0, t1) if sampler else None
+    step_flops = flops_micro * n_micro * world
+    achieved = step_flops * steps / (ms * 1e-3) / 1e12
+    return {"value": global_batch * steps / (ms * 1e-3), "unit": "img/s", "img_s": global_batch * steps / (ms * 1e-3),
+            "ms_per_step": ms / steps, "steps": steps, "global_batch": global_batch, "per_gpu_batch": per_gpu,
+            "micro_batch": micro, "scaling": "strong", "cuda_graphs": bool(graphs),
+            "contraction_tflops": achieved, "contraction_gflop_per_image": step_flops / global_batch / 1e9,
+            "frac_of_measured_tensor_peak": achieved / world / peaks["tflops"], "gpu_launches": launches, "clocks": clocks,
+            "found_inf": int(net.store.found_inf), "workload": TRAIN_NAMES[kind],
+            "note": "whole step: forward, backward, gradient exchange, finiteness check, SGD-momentum update; contraction_tflops "
+                    "counts only the Conv2d / ConvTranspose2d / Linear passes' algorithmic FLOPs over the whole step time"}
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -529,6 +601,9 @@ def run_gpu(args):
             if rank == 0 and world == 1 and not args.no_cpu_baseline:
                 others[label]["cpu_baseline"] = cpu_baseline(key, budget_s=4.0)
             del w2
+            torch.cuda.empty_cache()
+        for kind in ("resnet50_step", "pix2pix_step"):
+            others[kind] = measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world)
             torch.cuda.empty_cache()
     if sampler:
         sampler.stop()

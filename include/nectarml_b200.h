@@ -187,6 +187,43 @@ long long nml_launch_count(void);
 int nml_profile_begin(int max_records);
 int nml_profile_end(float* ms_out, int capacity, int* count);
 
+/* ---- neighbours of the contraction in a training step (fp16 NHWC = row-major [rows][channels]) ----
+ * Batch normalisation over the rows of a [rows][channels] fp16 matrix (N*H*W pixels of an NHWC
+ * tensor), fused with what follows it:  y = act(gamma * (x - mean) * rstd + beta [+ residual]),
+ * act 0 = none, 1 = ReLU, 2 = LeakyReLU(slope).  mean and rstd = 1/sqrt(biased variance + eps)
+ * (fp32, [channels]) are outputs of the forward and inputs of the backward.  Replaces the
+ * reference's fp32-NCHW kernels compute_mean_var_welford / normalize / batch_norm_backward
+ * (nectarml/csrc/kernels/tensor/fused/norm.cu; Python side nectarml/cuda/tensor/fused/batch_norm.py:10-99)
+ * and the activation and residual-add passes around them.  channels: multiple of 8, at most 2048;
+ * pointers 16-byte aligned; gamma / beta / residual may be NULL.  Reductions are two-stage in a
+ * fixed order: bitwise repeatable.  The workspace holds the partial sums. */
+int nml_bn_workspace_size(long long rows, int channels, size_t* bytes);
+int nml_bn_forward(const void* x, long long rows, int channels, const float* gamma, const float* beta,
+                   const void* residual, int act, float slope, float eps, void* y, float* mean, float* rstd,
+                   void* workspace, size_t workspace_bytes, void* stream);
+/* With dz = dy * act'(y): dbeta = sum dz, dgamma = sum dz * xhat,
+ * dx = gamma * rstd * (dz - dbeta/rows - xhat * dgamma/rows); dres (optional, fp16) = dz, the
+ * gradient of the residual input.  y is the forward's output (needed when act != 0). */
+int nml_bn_backward(const void* dy, const void* y, const void* x, long long rows, int channels,
+                    const float* gamma, const float* mean, const float* rstd, int act, float slope, void* dx,
+                    void* dres, float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
+                    void* stream);
+
+/* Gradient plumbing over ONE flat fp32 buffer holding every parameter's gradient (the buffer the
+ * weight-gradient entry points wrote into and NCCL all-reduced).  nml_grads_check sets *found_inf
+ * (device int) to 1 if any grad * inv_scale is not finite, else 0: one launch, no allocation, no
+ * read-back (the reference unscales parameter by parameter with a cudaMalloc and a blocking copy
+ * each, nectarml/csrc/ops/amp/amp.cpp:18-37).  nml_sgd_momentum_step applies
+ *   g = grad * inv_scale + weight_decay * p;  v = momentum * v + (1 - dampening) * g;  p -= lr * v
+ * (nectarml/optim/sgd.py:60-72, nectarml/csrc/kernels/optim/sgd.cu) to the whole buffer in one
+ * launch, refreshes the fp16 copy of the parameters (params_f16, may be NULL) and does nothing at
+ * all when *found_inf is set.  n: multiple of 4. */
+int nml_grads_check(const float* grads, size_t n, float inv_scale, int* found_inf, void* stream);
+int nml_sgd_momentum_step(float* params, const float* grads, float* velocity, void* params_f16, size_t n,
+                          float lr, float momentum, float dampening, float weight_decay, float inv_scale,
+                          const int* found_inf, void* stream);
+long long nml_layers_launch_count(void);
+
 /* ---- reference-shaped entry points ------------------------------------------------------
  * Same argument lists as the reference's host ops, which its pybind module registers as
  * `_nectarml.tensor.conv.*` and `_nectarml.tensor.matmul`

@@ -52,6 +52,12 @@ SYMBOLS = {
     "nml_set_sm_limit": (_I, [_I]),
     "nml_device_status": (_I, [C.POINTER(_I)]),
     "nml_launch_count": (C.c_longlong, []),
+    "nml_layers_launch_count": (C.c_longlong, []),
+    "nml_bn_workspace_size": (_I, [C.c_longlong, _I, C.POINTER(_SZ)]),
+    "nml_bn_forward": (_I, [_VP, C.c_longlong, _I, _VP, _VP, _VP, _I, C.c_float, C.c_float, _VP, _VP, _VP, _VP, _SZ, _VP]),
+    "nml_bn_backward": (_I, [_VP, _VP, _VP, C.c_longlong, _I, _VP, _VP, _VP, _I, C.c_float, _VP, _VP, _VP, _VP, _VP, _SZ, _VP]),
+    "nml_grads_check": (_I, [_VP, _SZ, C.c_float, _VP, _VP]),
+    "nml_sgd_momentum_step": (_I, [_VP, _VP, _VP, _VP, _SZ, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, _VP, _VP]),
     "nml_profile_begin": (_I, [_I]),
     "nml_profile_end": (_I, [C.POINTER(C.c_float), _I, C.POINTER(_I)]),
     # conv2d: ... dilation_w, groups, dtype, half_precision, result

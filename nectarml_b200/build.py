@@ -1,7 +1,7 @@
 """In-tree build of the CUDA library (nvcc, sm_100a only).
 
-``python -m nectarml_b200.build`` compiles ``csrc/nml_api.cu`` (which includes the kernels)
-into ``nectarml_b200/libnectarml_b200.so``.  nvcc cross-compiles without a GPU.
+``python -m nectarml_b200.build`` compiles ``csrc/nml_api.cu`` (which includes the contraction
+kernels) and ``csrc/nml_layers.cu`` (normalisation / optimizer kernels of the training step) into ``nectarml_b200/libnectarml_b200.so``.  nvcc cross-compiles without a GPU.
 """
 from __future__ import annotations
 
@@ -10,7 +10,7 @@ import subprocess
 import sys
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-SOURCES = [os.path.join(_HERE, "csrc", "nml_api.cu")]
+SOURCES = [os.path.join(_HERE, "csrc", "nml_api.cu"), os.path.join(_HERE, "csrc", "nml_layers.cu")]
 HEADERS = [os.path.join(_HERE, "csrc", n) for n in ("nml_ptx.cuh", "nml_umma.cuh", "nml_prepass.cuh")] + [
     os.path.join(os.path.dirname(_HERE), "include", "nectarml_b200.h")]
 OUTPUT = os.path.join(_HERE, "libnectarml_b200.so")

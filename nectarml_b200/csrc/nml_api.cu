@@ -1687,7 +1687,7 @@ int nml_device_status(int* code) {
     return read_status_word(ds->err, code);
 }
 
-long long nml_launch_count(void) { return g_launches.load(); }
+long long nml_launch_count(void) { return g_launches.load() + nml_layers_launch_count(); }
 
 int nml_profile_begin(int max_records) {
     if (max_records <= 0 || max_records > 1 << 16) return NML_ERR_INVALID;

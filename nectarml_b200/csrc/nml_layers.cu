@@ -1,0 +1,373 @@
+// Memory-bound neighbours of the contraction path in a training step, on the layout the contraction
+// kernels keep between layers (fp16 NHWC, i.e. a row-major [pixels][channels] matrix):
+//   * batch normalisation fused with the activation and the residual add that follow it, forward and
+//     backward (replaces the reference's fp32-NCHW Welford / normalize / backward kernels,
+//     nectarml/csrc/kernels/tensor/fused/norm.cu, and the separate ReLU / LeakyReLU / add passes
+//     around them);
+//   * one unscale + finiteness check and one SGD-momentum update over a FLAT parameter buffer
+//     (replaces one unscale launch + cudaMalloc + blocking read-back per parameter,
+//     nectarml/csrc/ops/amp/amp.cpp:18-37, and one update launch per parameter,
+//     nectarml/optim/sgd.py:75-90, nectarml/csrc/kernels/optim/sgd.cu).
+// Every reduction is two-stage with a fixed order (no atomics): results are bitwise repeatable.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+#include "../../include/nectarml_b200.h"
+
+namespace nml_layers {
+
+#define NMLL_CUDA(expr)                              \
+    do {                                             \
+        cudaError_t e_ = (expr);                     \
+        if (e_ != cudaSuccess) return NML_ERR_CUDA;  \
+    } while (0)
+
+static inline size_t round_up(size_t v, size_t m) { return (v + m - 1) / m * m; }
+static std::atomic<long long> g_layer_launches{0};
+
+__device__ __forceinline__ void unpack8(const uint4& v, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float2 t = __half22float2(h[j]);
+        f[2 * j] = t.x;
+        f[2 * j + 1] = t.y;
+    }
+}
+__device__ __forceinline__ uint4 pack8(const float (&f)[8]) {
+    uint4 v;
+    __half2* h = reinterpret_cast<__half2*>(&v);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) h[j] = __floats2half2_rn(f[2 * j], f[2 * j + 1]);
+    return v;
+}
+// derivative of the activation, read off the activation's OUTPUT: 0 none, 1 ReLU, 2 LeakyReLU(slope)
+__device__ __forceinline__ float act_grad(int act, float slope, float y) {
+    return act == 0 ? 1.f : (y > 0.f ? 1.f : (act == 1 ? 0.f : slope));
+}
+
+// Thread layout shared by the kernels below: the matrix is [M][C] fp16 with C a multiple of 8, a
+// vector is 8 adjacent channels (16 bytes), cpr = C / 8 vectors per row.  A block has
+// (256 / cpr) * cpr threads; thread t owns vector column t % cpr for good (its per-channel
+// constants sit in registers) and walks rows t / cpr, + rows-per-pass, ...: consecutive threads read
+// consecutive 16-byte vectors, so every access is fully coalesced whatever C is.
+
+// First stage of a per-channel reduction over rows.  kBackward == false: a = sum x, b = sum x^2.
+// kBackward == true: with dz = dy * act'(y) and xhat = (x - mean) * rstd: a = sum dz, b = sum dz * xhat.
+// Block p writes its sums to partial[p][0..C) and partial[p][C..2C).
+template <bool kBackward>
+__global__ void __launch_bounds__(256) bn_reduce_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy,
+                                                        const uint4* __restrict__ y, const float* __restrict__ mean,
+                                                        const float* __restrict__ rstd, int act, float slope,
+                                                        float* __restrict__ partial, size_t M, int C) {
+    __shared__ float sm[256][17];
+    const int cpr = C >> 3;
+    const int rpb = blockDim.x / cpr;
+    const int col = threadIdx.x % cpr, rsub = threadIdx.x / cpr;
+    float a[8], b[8], mu[8], rs[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        a[j] = b[j] = 0.f;
+        mu[j] = kBackward ? mean[col * 8 + j] : 0.f;
+        rs[j] = kBackward ? rstd[col * 8 + j] : 0.f;
+    }
+    for (size_t row = static_cast<size_t>(blockIdx.x) * rpb + rsub; row < M; row += static_cast<size_t>(gridDim.x) * rpb) {
+        const size_t v = row * cpr + col;
+        float xf[8];
+        unpack8(__ldg(x + v), xf);
+        if (!kBackward) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                a[j] += xf[j];
+                b[j] += xf[j] * xf[j];
+            }
+        } else {
+            float df[8], yf[8];
+            unpack8(__ldg(dy + v), df);
+            if (act != 0) unpack8(__ldg(y + v), yf);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float dz = df[j] * (act != 0 ? act_grad(act, slope, yf[j]) : 1.f);
+                a[j] += dz;
+                b[j] += dz * (xf[j] - mu[j]) * rs[j];
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        sm[threadIdx.x][j] = a[j];
+        sm[threadIdx.x][8 + j] = b[j];
+    }
+    __syncthreads();
+    if (threadIdx.x < cpr) {  // fixed order over the block's row lanes
+        float* out = partial + static_cast<size_t>(blockIdx.x) * 2 * C;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float sa = 0.f, sb = 0.f;
+            for (int r = 0; r < rpb; ++r) {
+                sa += sm[r * cpr + threadIdx.x][j];
+                sb += sm[r * cpr + threadIdx.x][8 + j];
+            }
+            out[threadIdx.x * 8 + j] = sa;
+            out[C + threadIdx.x * 8 + j] = sb;
+        }
+    }
+}
+
+// Second stage: adds the P rows of partial sums in a fixed order (eight interleaved running sums in double,
+// then those eight in order).  mode 0: out0 = mean, out1 = 1 / sqrt(biased variance + eps).
+// mode 1: out0 = sum a (d beta), out1 = sum b (d gamma).  blockDim = (32, 8).
+__global__ void __launch_bounds__(256) bn_finish_kernel(const float* __restrict__ partial, int P, int C, int mode, double inv_M,
+                                                        float eps, float* __restrict__ out0, float* __restrict__ out1) {
+    __shared__ double pa[8][33], pb[8][33];
+    const int c = blockIdx.x * 32 + threadIdx.x;
+    double sa = 0.0, sb = 0.0;
+    if (c < C) {
+#pragma unroll 4
+        for (int p = threadIdx.y; p < P; p += 8) {
+            sa += static_cast<double>(__ldg(partial + static_cast<size_t>(p) * 2 * C + c));
+            sb += static_cast<double>(__ldg(partial + static_cast<size_t>(p) * 2 * C + C + c));
+        }
+    }
+    pa[threadIdx.y][threadIdx.x] = sa;
+    pb[threadIdx.y][threadIdx.x] = sb;
+    __syncthreads();
+    if (threadIdx.y == 0 && c < C) {
+        double ta = 0.0, tb = 0.0;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            ta += pa[k][threadIdx.x];
+            tb += pb[k][threadIdx.x];
+        }
+        if (mode == 0) {
+            const double m = ta * inv_M;
+            double var = tb * inv_M - m * m;
+            if (var < 0.0) var = 0.0;
+            out0[c] = static_cast<float>(m);
+            out1[c] = static_cast<float>(1.0 / sqrt(var + static_cast<double>(eps)));
+        } else {
+            out0[c] = static_cast<float>(ta);
+            out1[c] = static_cast<float>(tb);
+        }
+    }
+}
+
+// y = act(gamma * (x - mean) * rstd + beta [+ residual]), fp16 in and out.
+__global__ void __launch_bounds__(256) bn_apply_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res,
+                                                       uint4* __restrict__ y, const float* __restrict__ gamma,
+                                                       const float* __restrict__ beta, const float* __restrict__ mean,
+                                                       const float* __restrict__ rstd, int act, float slope, size_t M, int C) {
+    const int cpr = C >> 3;
+    const int rpb = blockDim.x / cpr;
+    const int col = threadIdx.x % cpr, rsub = threadIdx.x / cpr;
+    float sc[8], sh[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int c = col * 8 + j;
+        sc[j] = (gamma ? gamma[c] : 1.f) * rstd[c];
+        sh[j] = (beta ? beta[c] : 0.f) - mean[c] * sc[j];
+    }
+    for (size_t row = static_cast<size_t>(blockIdx.x) * rpb + rsub; row < M; row += static_cast<size_t>(gridDim.x) * rpb) {
+        const size_t v = row * cpr + col;
+        float xf[8], rf[8];
+        unpack8(__ldg(x + v), xf);
+        if (res) unpack8(__ldg(res + v), rf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            float t = xf[j] * sc[j] + sh[j];
+            if (res) t += rf[j];
+            if (act != 0 && t < 0.f) t = (act == 1) ? 0.f : t * slope;
+            xf[j] = t;
+        }
+        y[v] = pack8(xf);
+    }
+}
+
+// dx = gamma * rstd * (dz - dbeta / M - xhat * dgamma / M) with dz = dy * act'(y); optionally dres = dz
+// (the gradient of the residual input that was added before the activation).
+__global__ void __launch_bounds__(256) bn_dx_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy,
+                                                    const uint4* __restrict__ y, uint4* __restrict__ dx, uint4* __restrict__ dres,
+                                                    const float* __restrict__ gamma, const float* __restrict__ mean,
+                                                    const float* __restrict__ rstd, const float* __restrict__ dbeta,
+                                                    const float* __restrict__ dgamma, int act, float slope, float inv_M,
+                                                    size_t M, int C) {
+    const int cpr = C >> 3;
+    const int rpb = blockDim.x / cpr;
+    const int col = threadIdx.x % cpr, rsub = threadIdx.x / cpr;
+    float mu[8], rs[8], k0[8], k1[8], k2[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        const int c = col * 8 + j;
+        mu[j] = mean[c];
+        rs[j] = rstd[c];
+        k0[j] = (gamma ? gamma[c] : 1.f) * rs[j];
+        k1[j] = dbeta[c] * inv_M;
+        k2[j] = dgamma[c] * inv_M;
+    }
+    for (size_t row = static_cast<size_t>(blockIdx.x) * rpb + rsub; row < M; row += static_cast<size_t>(gridDim.x) * rpb) {
+        const size_t v = row * cpr + col;
+        float xf[8], df[8], yf[8];
+        unpack8(__ldg(x + v), xf);
+        unpack8(__ldg(dy + v), df);
+        if (act != 0) unpack8(__ldg(y + v), yf);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const float dz = df[j] * (act != 0 ? act_grad(act, slope, yf[j]) : 1.f);
+            df[j] = dz;
+            xf[j] = k0[j] * (dz - k1[j] - (xf[j] - mu[j]) * rs[j] * k2[j]);
+        }
+        dx[v] = pack8(xf);
+        if (dres) dres[v] = pack8(df);
+    }
+}
+
+// any(!isfinite(g * inv_scale)) over a flat fp32 buffer -> *found (set, never cleared, here)
+__global__ void __launch_bounds__(256) grads_check_kernel(const float4* __restrict__ g, size_t n4, float inv_scale, int* found) {
+    bool bad = false;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n4; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const float4 v = __ldg(g + i);
+        bad |= !isfinite(v.x * inv_scale) | !isfinite(v.y * inv_scale) | !isfinite(v.z * inv_scale) | !isfinite(v.w * inv_scale);
+    }
+    if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) *found = 1;  // every writer writes the same value
+}
+
+// One SGD-momentum update over the whole flat buffer: g = grad * inv_scale + wd * p; v = momentum * v +
+// (1 - dampening) * g; p -= lr * v; and the fp16 copy of p the next forward reads.  Skipped as a whole
+// when *found_inf is set (the GradScaler rule: an overflowed step leaves the parameters alone).
+__global__ void __launch_bounds__(256) sgd_momentum_kernel(float4* __restrict__ p, const float4* __restrict__ g, float4* __restrict__ vel,
+                                                           uint2* __restrict__ p16, size_t n4, float lr, float momentum, float dampening,
+                                                           float wd, float inv_scale, const int* __restrict__ found_inf) {
+    if (found_inf && *found_inf) return;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n4; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float4 pv = p[i], vv = vel[i];
+        const float4 gv = __ldg(g + i);
+        float* pp = reinterpret_cast<float*>(&pv);
+        float* vp = reinterpret_cast<float*>(&vv);
+        const float* gp = reinterpret_cast<const float*>(&gv);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float gg = gp[j] * inv_scale + wd * pp[j];
+            vp[j] = momentum * vp[j] + (1.f - dampening) * gg;
+            pp[j] -= lr * vp[j];
+        }
+        p[i] = pv;
+        vel[i] = vv;
+        if (p16) {
+            uint2 h;
+            *reinterpret_cast<__half2*>(&h.x) = __floats2half2_rn(pp[0], pp[1]);
+            *reinterpret_cast<__half2*>(&h.y) = __floats2half2_rn(pp[2], pp[3]);
+            p16[i] = h;
+        }
+    }
+}
+
+static int bn_grid(long long M, int C, int* threads) {
+    const int cpr = C / 8;
+    *threads = (256 / cpr) * cpr;
+    const int rpb = *threads / cpr;
+    const long long want = (M + rpb - 1) / rpb;
+    return static_cast<int>(want < 148 * 4 ? want : 148 * 4);
+}
+static bool bn_shape_ok(long long M, int C) { return M > 0 && C > 0 && C % 8 == 0 && C <= 2048; }
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace nml_layers
+
+using namespace nml_layers;
+
+extern "C" {
+
+int nml_bn_workspace_size(long long rows, int channels, size_t* bytes) {
+    if (!bytes || !bn_shape_ok(rows, channels)) return NML_ERR_INVALID;
+    int threads;
+    const int P = bn_grid(rows, channels, &threads);
+    *bytes = round_up(static_cast<size_t>(P) * 2 * channels * sizeof(float), 256);
+    return NML_OK;
+}
+
+int nml_bn_forward(const void* x, long long rows, int channels, const float* gamma, const float* beta, const void* residual,
+                   int act, float slope, float eps, void* y, float* mean, float* rstd, void* workspace,
+                   size_t workspace_bytes, void* stream) {
+    if (!x || !y || !mean || !rstd || act < 0 || act > 2) return NML_ERR_INVALID;
+    if (!bn_shape_ok(rows, channels)) return NML_ERR_UNSUPPORTED;
+    if (!aligned16(x) || !aligned16(y) || (residual && !aligned16(residual))) return NML_ERR_INVALID;
+    size_t need = 0;
+    nml_bn_workspace_size(rows, channels, &need);
+    if (!workspace || workspace_bytes < need) return NML_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int threads;
+    const int P = bn_grid(rows, channels, &threads);
+    float* partial = static_cast<float*>(workspace);
+    bn_reduce_kernel<false><<<P, threads, 0, st>>>(static_cast<const uint4*>(x), nullptr, nullptr, nullptr, nullptr, 0, 0.f,
+                                                   partial, static_cast<size_t>(rows), channels);
+    bn_finish_kernel<<<(channels + 31) / 32, dim3(32, 8), 0, st>>>(partial, P, channels, 0, 1.0 / static_cast<double>(rows), eps,
+                                                                  mean, rstd);
+    bn_apply_kernel<<<P, threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(residual),
+                                           static_cast<uint4*>(y), gamma, beta, mean, rstd, act, slope,
+                                           static_cast<size_t>(rows), channels);
+    NMLL_CUDA(cudaGetLastError());
+    g_layer_launches += 3;
+    return NML_OK;
+}
+
+int nml_bn_backward(const void* dy, const void* y, const void* x, long long rows, int channels, const float* gamma,
+                    const float* mean, const float* rstd, int act, float slope, void* dx, void* dres, float* dgamma,
+                    float* dbeta, void* workspace, size_t workspace_bytes, void* stream) {
+    if (!dy || !x || !mean || !rstd || !dx || !dgamma || !dbeta || act < 0 || act > 2 || (act != 0 && !y)) return NML_ERR_INVALID;
+    if (!bn_shape_ok(rows, channels)) return NML_ERR_UNSUPPORTED;
+    if (!aligned16(dy) || !aligned16(x) || !aligned16(dx) || (y && !aligned16(y)) || (dres && !aligned16(dres))) return NML_ERR_INVALID;
+    size_t need = 0;
+    nml_bn_workspace_size(rows, channels, &need);
+    if (!workspace || workspace_bytes < need) return NML_ERR_WORKSPACE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    int threads;
+    const int P = bn_grid(rows, channels, &threads);
+    float* partial = static_cast<float*>(workspace);
+    bn_reduce_kernel<true><<<P, threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(dy),
+                                                  static_cast<const uint4*>(y), mean, rstd, act, slope, partial,
+                                                  static_cast<size_t>(rows), channels);
+    bn_finish_kernel<<<(channels + 31) / 32, dim3(32, 8), 0, st>>>(partial, P, channels, 1, 0.0, 0.f, dbeta, dgamma);
+    bn_dx_kernel<<<P, threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(dy), static_cast<const uint4*>(y),
+                                        static_cast<uint4*>(dx), static_cast<uint4*>(dres), gamma, mean, rstd, dbeta, dgamma, act,
+                                        slope, static_cast<float>(1.0 / static_cast<double>(rows)), static_cast<size_t>(rows),
+                                        channels);
+    NMLL_CUDA(cudaGetLastError());
+    g_layer_launches += 3;
+    return NML_OK;
+}
+
+long long nml_layers_launch_count(void) { return g_layer_launches.load(); }
+
+int nml_grads_check(const float* grads, size_t n, float inv_scale, int* found_inf, void* stream) {
+    if (!grads || !found_inf || n % 4 || !aligned16(grads)) return NML_ERR_INVALID;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    NMLL_CUDA(cudaMemsetAsync(found_inf, 0, sizeof(int), st));
+    const size_t n4 = n / 4;
+    const int blocks = static_cast<int>(n4 / 256 + 1 < 148 * 8 ? n4 / 256 + 1 : 148 * 8);
+    grads_check_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<const float4*>(grads), n4, inv_scale, found_inf);
+    NMLL_CUDA(cudaGetLastError());
+    ++g_layer_launches;
+    return NML_OK;
+}
+
+int nml_sgd_momentum_step(float* params, const float* grads, float* velocity, void* params_f16, size_t n, float lr,
+                          float momentum, float dampening, float weight_decay, float inv_scale, const int* found_inf,
+                          void* stream) {
+    if (!params || !grads || !velocity || n % 4 || !aligned16(params) || !aligned16(grads) || !aligned16(velocity) ||
+        (params_f16 && (reinterpret_cast<uintptr_t>(params_f16) & 7)))
+        return NML_ERR_INVALID;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const size_t n4 = n / 4;
+    const int blocks = static_cast<int>(n4 / 256 + 1 < 148 * 8 ? n4 / 256 + 1 : 148 * 8);
+    sgd_momentum_kernel<<<blocks, 256, 0, st>>>(reinterpret_cast<float4*>(params), reinterpret_cast<const float4*>(grads),
+                                                reinterpret_cast<float4*>(velocity), static_cast<uint2*>(params_f16), n4, lr,
+                                                momentum, dampening, weight_decay, inv_scale, found_inf);
+    NMLL_CUDA(cudaGetLastError());
+    ++g_layer_launches;
+    return NML_OK;
+}
+
+}  // extern "C"
