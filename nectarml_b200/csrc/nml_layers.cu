@@ -117,17 +117,18 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(const uint4* __restrict_
     }
 }
 
-// Second stage: adds the P rows of partial sums in a fixed order (eight interleaved running sums in double,
-// then those eight in order).  mode 0: out0 = mean, out1 = 1 / sqrt(biased variance + eps).
-// mode 1: out0 = sum a (d beta), out1 = sum b (d gamma).  blockDim = (32, 8).
-__global__ void __launch_bounds__(256) bn_finish_kernel(const float* __restrict__ partial, int P, int C, int mode, double inv_M,
+// Second stage: adds the P rows of partial sums in a fixed order (32 interleaved running sums in double,
+// then those 32 in order).  mode 0: out0 = mean, out1 = 1 / sqrt(biased variance + eps).
+// mode 1: out0 = sum a (d beta), out1 = sum b (d gamma).  blockDim = (32, 32): the pass is a chain of load
+// latencies, so it is spread over as many threads as a block has.
+__global__ void __launch_bounds__(1024) bn_finish_kernel(const float* __restrict__ partial, int P, int C, int mode, double inv_M,
                                                         float eps, float* __restrict__ out0, float* __restrict__ out1) {
-    __shared__ double pa[8][33], pb[8][33];
+    __shared__ double pa[32][33], pb[32][33];
     const int c = blockIdx.x * 32 + threadIdx.x;
     double sa = 0.0, sb = 0.0;
     if (c < C) {
 #pragma unroll 4
-        for (int p = threadIdx.y; p < P; p += 8) {
+        for (int p = threadIdx.y; p < P; p += 32) {
             sa += static_cast<double>(__ldg(partial + static_cast<size_t>(p) * 2 * C + c));
             sb += static_cast<double>(__ldg(partial + static_cast<size_t>(p) * 2 * C + C + c));
         }
@@ -138,7 +139,7 @@ __global__ void __launch_bounds__(256) bn_finish_kernel(const float* __restrict_
     if (threadIdx.y == 0 && c < C) {
         double ta = 0.0, tb = 0.0;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
+        for (int k = 0; k < 32; ++k) {
             ta += pa[k][threadIdx.x];
             tb += pb[k][threadIdx.x];
         }
@@ -271,6 +272,12 @@ static int bn_grid(long long M, int C, int* threads) {
     const long long want = (M + rpb - 1) / rpb;
     return static_cast<int>(want < 148 * 4 ? want : 148 * 4);
 }
+static int bn_grid_elementwise(long long M, int C) {  // no partial sums behind these: as many blocks as keep HBM busy
+    const int cpr = C / 8;
+    const int rpb = ((256 / cpr) * cpr) / cpr;
+    const long long want = (M + rpb - 1) / rpb;
+    return static_cast<int>(want < 148 * 16 ? want : 148 * 16);
+}
 static bool bn_shape_ok(long long M, int C) { return M > 0 && C > 0 && C % 8 == 0 && C <= 2048; }
 static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
@@ -303,9 +310,9 @@ int nml_bn_forward(const void* x, long long rows, int channels, const float* gam
     float* partial = static_cast<float*>(workspace);
     bn_reduce_kernel<false><<<P, threads, 0, st>>>(static_cast<const uint4*>(x), nullptr, nullptr, nullptr, nullptr, 0, 0.f,
                                                    partial, static_cast<size_t>(rows), channels);
-    bn_finish_kernel<<<(channels + 31) / 32, dim3(32, 8), 0, st>>>(partial, P, channels, 0, 1.0 / static_cast<double>(rows), eps,
+    bn_finish_kernel<<<(channels + 31) / 32, dim3(32, 32), 0, st>>>(partial, P, channels, 0, 1.0 / static_cast<double>(rows), eps,
                                                                   mean, rstd);
-    bn_apply_kernel<<<P, threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(residual),
+    bn_apply_kernel<<<bn_grid_elementwise(rows, channels), threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(residual),
                                            static_cast<uint4*>(y), gamma, beta, mean, rstd, act, slope,
                                            static_cast<size_t>(rows), channels);
     NMLL_CUDA(cudaGetLastError());
@@ -329,8 +336,8 @@ int nml_bn_backward(const void* dy, const void* y, const void* x, long long rows
     bn_reduce_kernel<true><<<P, threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(dy),
                                                   static_cast<const uint4*>(y), mean, rstd, act, slope, partial,
                                                   static_cast<size_t>(rows), channels);
-    bn_finish_kernel<<<(channels + 31) / 32, dim3(32, 8), 0, st>>>(partial, P, channels, 1, 0.0, 0.f, dbeta, dgamma);
-    bn_dx_kernel<<<P, threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(dy), static_cast<const uint4*>(y),
+    bn_finish_kernel<<<(channels + 31) / 32, dim3(32, 32), 0, st>>>(partial, P, channels, 1, 0.0, 0.f, dbeta, dgamma);
+    bn_dx_kernel<<<bn_grid_elementwise(rows, channels), threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(dy), static_cast<const uint4*>(y),
                                         static_cast<uint4*>(dx), static_cast<uint4*>(dres), gamma, mean, rstd, dbeta, dgamma, act,
                                         slope, static_cast<float>(1.0 / static_cast<double>(rows)), static_cast<size_t>(rows),
                                         channels);
