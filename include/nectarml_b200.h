@@ -209,6 +209,16 @@ int nml_bn_backward(const void* dy, const void* y, const void* x, long long rows
                     void* dres, float* dgamma, float* dbeta, void* workspace, size_t workspace_bytes,
                     void* stream);
 
+/* Max pooling of an NHWC fp16 tensor (channels a multiple of 8), output size (h + 2 pad - k)/stride + 1.
+ * The forward also writes one byte per output value naming the window tap that won (`index`,
+ * batch * ho * wo * channels bytes); the backward gathers dy through it, writes every element of
+ * dx exactly once and uses no atomics.  Replaces the reference's max-pool kernels on this layout
+ * (nectarml/csrc/kernels/tensor/pooling.cu) between the stem and the first residual block. */
+int nml_maxpool_forward(const void* x, int batch, int h, int w, int channels, int k, int stride, int pad,
+                        void* y, void* index, void* stream);
+int nml_maxpool_backward(const void* dy, const void* index, int batch, int h, int w, int channels, int k,
+                         int stride, int pad, void* dx, void* stream);
+
 /* Gradient plumbing over ONE flat fp32 buffer holding every parameter's gradient (the buffer the
  * weight-gradient entry points wrote into and NCCL all-reduced).  nml_grads_check sets *found_inf
  * (device int) to 1 if any grad * inv_scale is not finite, else 0: one launch, no allocation, no

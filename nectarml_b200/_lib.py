@@ -56,6 +56,8 @@ SYMBOLS = {
     "nml_bn_workspace_size": (_I, [C.c_longlong, _I, C.POINTER(_SZ)]),
     "nml_bn_forward": (_I, [_VP, C.c_longlong, _I, _VP, _VP, _VP, _I, C.c_float, C.c_float, _VP, _VP, _VP, _VP, _SZ, _VP]),
     "nml_bn_backward": (_I, [_VP, _VP, _VP, C.c_longlong, _I, _VP, _VP, _VP, _I, C.c_float, _VP, _VP, _VP, _VP, _VP, _SZ, _VP]),
+    "nml_maxpool_forward": (_I, [_VP, _I, _I, _I, _I, _I, _I, _I, _VP, _VP, _VP]),
+    "nml_maxpool_backward": (_I, [_VP, _VP, _I, _I, _I, _I, _I, _I, _I, _VP, _VP]),
     "nml_grads_check": (_I, [_VP, _SZ, C.c_float, _VP, _VP]),
     "nml_sgd_momentum_step": (_I, [_VP, _VP, _VP, _VP, _SZ, C.c_float, C.c_float, C.c_float, C.c_float, C.c_float, _VP, _VP]),
     "nml_profile_begin": (_I, [_I]),

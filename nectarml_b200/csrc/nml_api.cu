@@ -734,14 +734,14 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         w_planes[1] = p1;
         if (!ws.dry) {
             if (!ws.fits()) return NML_ERR_WORKSPACE;
-            size_t total = static_cast<size_t>(N) * T * kp;
-            int blocks = static_cast<int>(std::min<size_t>((total + 255) / 256, 148 * 8));
+            // out[n][t][k] = w[...]: a swap of the two inner dimensions of [B][R][Cc] (see repack_weight_kernel)
+            const int rB = f.k_is_dim0 ? 1 : f.d0, rR = f.k_is_dim0 ? f.d0 : f.d1, rC = f.k_is_dim0 ? f.d1 * T : T;
+            if (rB > 65535) return NML_ERR_UNSUPPORTED;
+            const dim3 grid(ceil_div(rC, 32), ceil_div(kp, 32), rB);
             if (f.w_dtype == NML_F32)
-                { repack_weight_kernel<float><<<blocks, 256, 0, st>>>(static_cast<const float*>(f.w), p0, p1, mi.enc,
-                                                                   f.d0, f.d1, T, f.k_is_dim0, kp); ++g_launches; }
+                { repack_weight_kernel<float><<<grid, dim3(32, 8), 0, st>>>(static_cast<const float*>(f.w), p0, p1, mi.enc, rR, rC, kp); ++g_launches; }
             else
-                { repack_weight_kernel<__half><<<blocks, 256, 0, st>>>(static_cast<const __half*>(f.w), p0, p1, mi.enc,
-                                                                    f.d0, f.d1, T, f.k_is_dim0, kp); ++g_launches; }
+                { repack_weight_kernel<__half><<<grid, dim3(32, 8), 0, st>>>(static_cast<const __half*>(f.w), p0, p1, mi.enc, rR, rC, kp); ++g_launches; }
             NML_CUDA(cudaGetLastError());
         }
     }

@@ -265,6 +265,85 @@ __global__ void __launch_bounds__(256) sgd_momentum_kernel(float4* __restrict__ 
     }
 }
 
+// Max pooling over NHWC fp16, 8 channels per thread.  Forward also records, per output value, which tap of
+// the window won (kh * k + kw, one byte); backward is a GATHER over the <= ceil(k/s)^2 windows that cover an
+// input pixel -- no atomics, so it is bitwise repeatable, and every input gradient is written exactly once
+// (no zero-fill pass).  Out-of-image taps are skipped (i.e. padded with -inf).
+__global__ void __launch_bounds__(256) maxpool_fwd_kernel(const uint4* __restrict__ x, uint4* __restrict__ y, uint2* __restrict__ idx,
+                                                          int N, int H, int W, int C, int k, int s, int p, int Ho, int Wo) {
+    const int cpr = C >> 3;
+    const size_t total = static_cast<size_t>(N) * Ho * Wo * cpr;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int cv = static_cast<int>(i % cpr);
+        size_t r = i / cpr;
+        const int ow = static_cast<int>(r % Wo);
+        r /= Wo;
+        const int oh = static_cast<int>(r % Ho);
+        const int n = static_cast<int>(r / Ho);
+        float best[8];
+        unsigned char who[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            best[j] = -INFINITY;
+            who[j] = 0;
+        }
+        for (int kh = 0; kh < k; ++kh) {
+            const int ih = oh * s - p + kh;
+            if (ih < 0 || ih >= H) continue;
+            for (int kw = 0; kw < k; ++kw) {
+                const int iw = ow * s - p + kw;
+                if (iw < 0 || iw >= W) continue;
+                float f[8];
+                unpack8(__ldg(x + ((static_cast<size_t>(n) * H + ih) * W + iw) * cpr + cv), f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (f[j] > best[j]) {
+                        best[j] = f[j];
+                        who[j] = static_cast<unsigned char>(kh * k + kw);
+                    }
+            }
+        }
+        y[i] = pack8(best);
+        uint2 w2;
+        w2.x = who[0] | (who[1] << 8) | (who[2] << 16) | (who[3] << 24);
+        w2.y = who[4] | (who[5] << 8) | (who[6] << 16) | (who[7] << 24);
+        idx[i] = w2;
+    }
+}
+
+__global__ void __launch_bounds__(256) maxpool_bwd_kernel(const uint4* __restrict__ dy, const uint2* __restrict__ idx, uint4* __restrict__ dx,
+                                                          int N, int H, int W, int C, int k, int s, int p, int Ho, int Wo) {
+    const int cpr = C >> 3;
+    const size_t total = static_cast<size_t>(N) * H * W * cpr;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total; i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        const int cv = static_cast<int>(i % cpr);
+        size_t r = i / cpr;
+        const int iw = static_cast<int>(r % W);
+        r /= W;
+        const int ih = static_cast<int>(r % H);
+        const int n = static_cast<int>(r / H);
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        // windows (oh, ow) with 0 <= ih + p - oh * s < k
+        const int oh_hi = min((ih + p) / s, Ho - 1), ow_hi = min((iw + p) / s, Wo - 1);
+        for (int oh = oh_hi; oh >= 0 && ih + p - oh * s < k; --oh) {
+            const int kh = ih + p - oh * s;
+            for (int ow = ow_hi; ow >= 0 && iw + p - ow * s < k; --ow) {
+                const int me = kh * k + (iw + p - ow * s);
+                const size_t o = ((static_cast<size_t>(n) * Ho + oh) * Wo + ow) * cpr + cv;
+                const uint2 w2 = __ldg(idx + o);
+                float g[8];
+                unpack8(__ldg(dy + o), g);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const unsigned who = ((j < 4 ? w2.x : w2.y) >> (8 * (j & 3))) & 0xffu;
+                    if (who == static_cast<unsigned>(me)) acc[j] += g[j];
+                }
+            }
+        }
+        dx[i] = pack8(acc);
+    }
+}
+
 static int bn_grid(long long M, int C, int* threads) {
     const int cpr = C / 8;
     *threads = (256 / cpr) * cpr;
@@ -347,6 +426,42 @@ int nml_bn_backward(const void* dy, const void* y, const void* x, long long rows
 }
 
 long long nml_layers_launch_count(void) { return g_layer_launches.load(); }
+
+int nml_maxpool_forward(const void* x, int batch, int h, int w, int channels, int k, int stride, int pad, void* y,
+                        void* index, void* stream) {
+    if (!x || !y || !index || batch <= 0 || h <= 0 || w <= 0 || k <= 0 || k > 15 || stride <= 0 || pad < 0 || pad >= k)
+        return NML_ERR_INVALID;
+    if (channels <= 0 || channels % 8) return NML_ERR_UNSUPPORTED;
+    if (!aligned16(x) || !aligned16(y) || (reinterpret_cast<uintptr_t>(index) & 7)) return NML_ERR_INVALID;
+    const int ho = (h + 2 * pad - k) / stride + 1, wo = (w + 2 * pad - k) / stride + 1;
+    if (ho <= 0 || wo <= 0) return NML_ERR_INVALID;
+    const size_t total = static_cast<size_t>(batch) * ho * wo * (channels / 8);
+    const int blocks = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    maxpool_fwd_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(x), static_cast<uint4*>(y),
+                                                                             static_cast<uint2*>(index), batch, h, w, channels, k,
+                                                                             stride, pad, ho, wo);
+    NMLL_CUDA(cudaGetLastError());
+    ++g_layer_launches;
+    return NML_OK;
+}
+
+int nml_maxpool_backward(const void* dy, const void* index, int batch, int h, int w, int channels, int k, int stride, int pad,
+                         void* dx, void* stream) {
+    if (!dy || !dx || !index || batch <= 0 || h <= 0 || w <= 0 || k <= 0 || k > 15 || stride <= 0 || pad < 0 || pad >= k)
+        return NML_ERR_INVALID;
+    if (channels <= 0 || channels % 8) return NML_ERR_UNSUPPORTED;
+    if (!aligned16(dy) || !aligned16(dx) || (reinterpret_cast<uintptr_t>(index) & 7)) return NML_ERR_INVALID;
+    const int ho = (h + 2 * pad - k) / stride + 1, wo = (w + 2 * pad - k) / stride + 1;
+    if (ho <= 0 || wo <= 0) return NML_ERR_INVALID;
+    const size_t total = static_cast<size_t>(batch) * h * w * (channels / 8);
+    const int blocks = static_cast<int>((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
+    maxpool_bwd_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(dy), static_cast<const uint2*>(index),
+                                                                             static_cast<uint4*>(dx), batch, h, w, channels, k, stride,
+                                                                             pad, ho, wo);
+    NMLL_CUDA(cudaGetLastError());
+    ++g_layer_launches;
+    return NML_OK;
+}
 
 int nml_grads_check(const float* grads, size_t n, float inv_scale, int* found_inf, void* stream) {
     if (!grads || !found_inf || n % 4 || !aligned16(grads)) return NML_ERR_INVALID;

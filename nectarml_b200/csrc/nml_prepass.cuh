@@ -181,26 +181,26 @@ __global__ void __launch_bounds__(256) colsum_rows_f16x8_kernel(const __half* __
 // Weights [D0][D1][T] -> K-major operand dst[n][t][kp]:
 //   k_is_dim0 == 0 : n = D0 index, k = D1 index   (Conv2d forward, ConvTranspose2d dgrad)
 //   k_is_dim0 == 1 : n = D1 index, k = D0 index   (Conv2d dgrad, ConvTranspose2d forward)
-// k is zero-padded to kp per tap so that no K block straddles two taps.
+// k is zero-padded to kp per tap so that no K block straddles two taps.  Both cases swap the two inner
+// dimensions of a [B][R][Cc] array: out[b][c][r] = in[b][r][c], rows padded to Rp --
+//   k_is_dim0 == 0 : B = D0, R = D1 (k), Cc = T          k_is_dim0 == 1 : B = 1, R = D0 (k), Cc = D1 * T
+// -- so one tiled transpose through shared memory serves them, with coalesced reads AND writes (a gather
+// with one side strided moved a 32-byte sector per 2-byte element).  grid (ceil(Cc/32), ceil(Rp/32), B),
+// block (32, 8).
 template <typename TIn>
-__global__ void __launch_bounds__(256) repack_weight_kernel(const TIn* __restrict__ w, void* out0,
-                                                            void* out1, int enc, int D0, int D1, int T,
-                                                            int k_is_dim0, int kp) {
-    const int NN = k_is_dim0 ? D1 : D0;
-    const int KK = k_is_dim0 ? D0 : D1;
-    size_t total = static_cast<size_t>(NN) * T * kp;
-    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < total;
-         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
-        int k = static_cast<int>(i % kp);
-        size_t r = i / kp;
-        int t = static_cast<int>(r % T);
-        int n = static_cast<int>(r / T);
-        float v = 0.f;
-        if (k < KK) {
-            size_t d0 = k_is_dim0 ? k : n, d1 = k_is_dim0 ? n : k;
-            v = load_as_float(w, (d0 * D1 + d1) * T + t);
-        }
-        store_enc(enc, out0, out1, i, v);
+__global__ void __launch_bounds__(256) repack_weight_kernel(const TIn* __restrict__ w, void* out0, void* out1, int enc,
+                                                            int R, int Cc, int Rp) {
+    __shared__ float tile[32][33];
+    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+    const size_t b = blockIdx.z;
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int r = r0 + j, c = c0 + threadIdx.x;
+        tile[j][threadIdx.x] = (r < R && c < Cc) ? load_as_float(w, (b * R + r) * Cc + c) : 0.f;
+    }
+    __syncthreads();
+    for (int j = threadIdx.y; j < 32; j += 8) {
+        const int c = c0 + j, r = r0 + threadIdx.x;
+        if (c < Cc && r < Rp) store_enc(enc, out0, out1, (b * Cc + c) * Rp + r, tile[threadIdx.x][j]);
     }
 }
 

@@ -231,6 +231,36 @@ class _BnActFn(torch.autograd.Function):
         return dx, dres, None, None, None
 
 
+class _MaxPoolFn(torch.autograd.Function):
+    """Max pooling on NHWC fp16 (window winners recorded in the forward, gathered in the backward)."""
+
+    @staticmethod
+    def forward(ctx, x, k, stride, pad):
+        n, h, w, c = x.shape
+        ho, wo = (h + 2 * pad - k) // stride + 1, (w + 2 * pad - k) // stride + 1
+        y = torch.empty(n, ho, wo, c, dtype=x.dtype, device=x.device)
+        index = torch.empty(n, ho, wo, c, dtype=torch.uint8, device=x.device)
+        _lib.check(_lib.load().nml_maxpool_forward(x.data_ptr(), n, h, w, c, k, stride, pad, y.data_ptr(), index.data_ptr(),
+                                                   torch.cuda.current_stream().cuda_stream))
+        ctx.geom = (n, h, w, c, k, stride, pad)
+        ctx.save_for_backward(index)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (index,) = ctx.saved_tensors
+        n, h, w, c, k, stride, pad = ctx.geom
+        dy = dy.contiguous()
+        dx = torch.empty(n, h, w, c, dtype=dy.dtype, device=dy.device)
+        _lib.check(_lib.load().nml_maxpool_backward(dy.data_ptr(), index.data_ptr(), n, h, w, c, k, stride, pad, dx.data_ptr(),
+                                                    torch.cuda.current_stream().cuda_stream))
+        return dx, None, None, None
+
+
+def max_pool(x, k, stride, pad):
+    return _MaxPoolFn.apply(x, k, stride, pad)
+
+
 # ------------------------------------------------------------------ layers --
 class _Layer:
     """A parameterised layer: two parameter slots (weight-like, bias-like) in the ParamStore."""
@@ -372,7 +402,7 @@ class ResNet50(_Net):
         """x: [N, H, W, 3] fp16 NHWC -> logits [N, classes] fp16."""
         t = self.token
         x = self.stem_bn(self.stem(x, t), t, ACT_RELU)
-        x = self.store.record(torch.nn.functional.max_pool2d(x.permute(0, 3, 1, 2), 3, 2, 1).permute(0, 2, 3, 1).contiguous())
+        x = self.store.record(max_pool(x, 3, 2, 1))
         for blk in self.blocks:
             idn = x
             y = blk["b1"](blk["c1"](x, t), t, ACT_RELU)

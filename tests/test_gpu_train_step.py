@@ -185,6 +185,22 @@ def test_unet_step_matches_the_fp32_composition():
     print(f"worst gradient error {worst:.3e}")
 
 
+def test_max_pool_matches_torch():
+    gen = torch.Generator(device=DEV).manual_seed(4)
+    for (n, h, w, c, k, s_, p) in ((2, 13, 10, 16, 3, 2, 1), (1, 8, 8, 64, 2, 2, 0), (3, 7, 9, 8, 3, 1, 1), (2, 12, 12, 24, 5, 3, 2)):
+        x = torch.randn(n, h, w, c, device=DEV, generator=gen).half().requires_grad_(True)
+        y = train.max_pool(x, k, s_, p)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+        xr = x.detach().float().permute(0, 3, 1, 2).requires_grad_(True)
+        yr = F.max_pool2d(xr, k, s_, p)
+        yr.backward(dy.float().permute(0, 3, 1, 2))
+        assert torch.equal(y.float(), yr.permute(0, 2, 3, 1))
+        # (random fp16 inputs: ties inside a window are rare but exist; both sides then pick the first tap)
+        assert torch.allclose(x.grad.float(), xr.grad.permute(0, 2, 3, 1), rtol=1e-3, atol=1e-3)
+    ops.device_status()
+
+
 def test_bn_act_kernels_match_torch_and_repeat_bitwise():
     """nml_bn_forward / nml_bn_backward on their own: all three activations, with and without a residual."""
     import ctypes as C
