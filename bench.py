@@ -438,13 +438,16 @@ def measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world):
     """img/s of one of the two conv-net training steps at a FIXED global batch (strong scaling)."""
     from nectarml_b200 import ops, train
     torch.manual_seed(4321 + rank)
+    # NML_BENCH_SHARD_OF=N times one GPU's share of an N-GPU run (no exchange): the per-GPU shapes of a larger run
+    # can be checked and timed on a single GPU
+    shard_of = max(world, int(os.environ.get("NML_BENCH_SHARD_OF", "1"))) if world == 1 else world
     if kind == "resnet50_step":
         net, global_batch, hw, loss = train.ResNet50(dev), 2048, 224, "cross_entropy"
-        per_gpu = global_batch // world
+        per_gpu = global_batch // shard_of
         micro = min(per_gpu, int(os.environ.get("NML_BENCH_MICRO_BATCH", "256")))
     else:
         net, global_batch, hw, loss = train.Pix2PixGenerator(dev), 64, 256, "l1"
-        per_gpu = global_batch // world
+        per_gpu = global_batch // shard_of
         micro = per_gpu
     net.init(seed=11)
     n_micro = per_gpu // micro
@@ -454,8 +457,10 @@ def measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world):
     count = global_batch if loss == "cross_entropy" else global_batch * hw * hw * 3
     use_graphs = os.environ.get("NML_BENCH_GRAPHS", "1") != "0"
     net.store.flops = 0.0
+    launches_before = ops.launch_count()
     step.micro_batch(x, target, count, first=True, last=False)   # eager once: counts the algorithmic FLOPs, sizes the workspaces
     flops_micro = net.store.flops
+    launches_micro = ops.launch_count() - launches_before        # this library's kernels in one micro-batch
     ops.device_status()
     graphs = step.capture(x, target, count, accumulate_variants=(False, True) if n_micro > 1 else (False,)) if use_graphs else None
 
@@ -481,11 +486,14 @@ def measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world):
     t0 = time.time()
     ms = time_steps(torch, dist, world, dev, one_step, steps)
     t1 = time.time()
-    launches = (ops.launch_count() - launches0) if not graphs else None
+    # (a replayed graph does not pass through the library's counter: its launches are those of the captured micro-batch)
+    launches = (ops.launch_count() - launches0) + (launches_micro * n_micro * steps if graphs else 0)
     ops.device_status()
     clocks = sampler.window(t0, t1) if sampler else None
     step_flops = flops_micro * n_micro * world
     achieved = step_flops * steps / (ms * 1e-3) / 1e12
+    if shard_of != world:
+        global_batch = per_gpu  # a single GPU's share was timed
     return {"value": global_batch * steps / (ms * 1e-3), "unit": "img/s", "img_s": global_batch * steps / (ms * 1e-3),
             "ms_per_step": ms / steps, "steps": steps, "global_batch": global_batch, "per_gpu_batch": per_gpu,
             "micro_batch": micro, "scaling": "strong", "cuda_graphs": bool(graphs),
@@ -513,7 +521,11 @@ def run_gpu(args):
         # NCCL takes is one of theirs (NVSwitch keeps the all-reduce fast at a few CTAs)
         os.environ.setdefault("NCCL_MAX_CTAS", os.environ.get("NML_BENCH_NCCL_CTAS", "8"))
         dist.init_process_group("nccl", device_id=dev)
-    build.build()
+        if local == 0:  # one rank (re)builds a stale library, the others wait for it
+            build.build()
+        dist.barrier()
+    else:
+        build.build()
     peaks = measured_peaks()
     sampler = ClockSampler(local) if rank == 0 else None
     if sampler:

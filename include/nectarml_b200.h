@@ -238,9 +238,12 @@ long long nml_layers_launch_count(void);
  * Same argument lists as the reference's host ops, which its pybind module registers as
  * `_nectarml.tensor.conv.*` and `_nectarml.tensor.matmul`
  * (nectarml/csrc/python/ops/tensor/conv.h:71-150, matmul.h:10-16, bindings.cpp:41-51).
- * Pointers travel as integers; *result receives a device pointer obtained from cudaMalloc that
- * the caller releases with cudaFree (the reference's `free_cuda` path ends in cudaFree,
- * nectarml/csrc/pool/allocator_pool.cpp:75-96).  dtype uses the NML_F32 / NML_F16 values.
+ * Pointers travel as integers; *result receives a device pointer from the device's stream-ordered
+ * memory pool (cudaMallocAsync on the legacy default stream; plain cudaMalloc where a device has no
+ * pools) that the caller releases with nml_ref_free -- or with cudaFree, which accepts such pointers:
+ * the reference's `free_cuda` path ends in cudaFree (nectarml/csrc/pool/allocator_pool.cpp:75-96).
+ * Unlike the reference's raw cudaMalloc / cudaFree per result (its pool is disabled in these
+ * translation units, allocator_pool.h:38), this does not synchronise the device on every call.  dtype uses the NML_F32 / NML_F16 values.
  * Like the reference these run on the legacy default stream and are ordered by it.
  * With half_precision != 0 the tensors are fp32 in memory, the contraction runs on fp16
  * operands and the fp32 result holds fp16-rounded values (conv2d.cpp:415-435); otherwise fp32
@@ -306,8 +309,8 @@ int nml_ref_conv_transpose1d_backward_weight(uintptr_t out_grad_ptr, uintptr_t i
 int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_rank,
                    const int* b_shape, int b_rank, int dtype, uintptr_t* result);
 
-/* Releases a pointer returned through *result above (cudaFree); the counterpart of the
- * reference's `_nectarml.free_cuda` (nectarml/csrc/ops/system/memory.cpp:33-39). */
+/* Releases a pointer returned through *result above (back to the pool, in stream order); the
+ * counterpart of the reference's `_nectarml.free_cuda` (nectarml/csrc/ops/system/memory.cpp:33-39). */
 int nml_ref_free(uintptr_t ptr);
 
 /* ---- test support ----------------------------------------------------------------------

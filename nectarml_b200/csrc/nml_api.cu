@@ -1531,6 +1531,41 @@ static int ref_workspace(size_t need, void** out) {
     return NML_OK;
 }
 
+// Results of the reference-shaped entry points come from the device's stream-ordered pool
+// (cudaMallocAsync on the legacy default stream the entry points run on): no device-wide
+// synchronisation per call, freed memory is kept for the next result (release threshold = never).
+// cudaFree accepts such pointers, so the reference's own `free_cuda` path keeps working; where a
+// device has no memory pools the plain cudaMalloc / cudaFree pair is used.
+static bool g_pool_ready[64] = {false};
+static bool g_pool_usable[64] = {false};
+static int ref_alloc(void** out, size_t bytes) {
+    int dev = 0;
+    NML_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return NML_ERR_INVALID;
+    {
+        std::lock_guard<std::mutex> lock(g_dev_mutex);
+        if (!g_pool_ready[dev]) {
+            int supported = 0;
+            cudaMemPool_t pool;
+            if (cudaDeviceGetAttribute(&supported, cudaDevAttrMemoryPoolsSupported, dev) == cudaSuccess && supported &&
+                cudaDeviceGetDefaultMemPool(&pool, dev) == cudaSuccess) {
+                unsigned long long keep = ~0ull;
+                g_pool_usable[dev] = cudaMemPoolSetAttribute(pool, cudaMemPoolAttrReleaseThreshold, &keep) == cudaSuccess;
+            }
+            (void)cudaGetLastError();
+            g_pool_ready[dev] = true;
+        }
+    }
+    if (g_pool_usable[dev]) NML_CUDA(cudaMallocAsync(out, bytes ? bytes : 1, cudaStreamLegacy));
+    else NML_CUDA(cudaMalloc(out, bytes ? bytes : 1));
+    return NML_OK;
+}
+static void ref_release(void* p) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && g_pool_usable[dev]) cudaFreeAsync(p, cudaStreamLegacy);
+    else cudaFree(p);
+}
+
 __global__ void tma_box_probe_kernel(const __grid_constant__ CUtensorMap tm, int c0, int c1, int c2, int c3,
                                      uint32_t bytes, uint8_t* out, int* err) {
     extern __shared__ __align__(1024) uint8_t box_smem[];
@@ -1804,11 +1839,12 @@ static int ref_run_conv(nml_conv_desc* d, int pass, const void* in0, const void*
     rc = ref_workspace(need, &ws);
     if (rc) return rc;
     void* out = nullptr;
-    NML_CUDA(cudaMalloc(&out, out_bytes ? out_bytes : 1));
+    rc = ref_alloc(&out, out_bytes);
+    if (rc) return rc;
     Bump b{static_cast<uint8_t*>(ws), 0, need, false};
     rc = conv_pass(d, pass, in0, in1, bias, out, nullptr, b, nullptr);
     if (rc) {
-        cudaFree(out);
+        ref_release(out);
         return rc;
     }
     *result = reinterpret_cast<uintptr_t>(out);
@@ -1994,7 +2030,8 @@ int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_r
     rc = ref_workspace(need, &ws);
     if (rc) return rc;
     void* out = nullptr;
-    NML_CUDA(cudaMalloc(&out, batch * M * N * es));
+    rc = ref_alloc(&out, batch * M * N * es);
+    if (rc) return rc;
     for (size_t b = 0; b < batch; ++b) {
         const uint8_t* A = reinterpret_cast<const uint8_t*>(a_ptr) + b * M * K * es;
         const uint8_t* Bm = reinterpret_cast<const uint8_t*>(b_ptr) + (b_batch == 1 ? 0 : b) * K * N * es;
@@ -2002,7 +2039,7 @@ int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_r
         Bump bump{static_cast<uint8_t*>(ws), 0, need, false};
         rc = linear_pass(&d, NML_PASS_BACKWARD_DATA, A, Bm, nullptr, C, nullptr, bump, nullptr);
         if (rc) {
-            cudaFree(out);
+            ref_release(out);
             return rc;
         }
     }
@@ -2011,7 +2048,8 @@ int nml_ref_matmul(uintptr_t a_ptr, uintptr_t b_ptr, const int* a_shape, int a_r
 }
 
 int nml_ref_free(uintptr_t ptr) {
-    if (ptr) NML_CUDA(cudaFree(reinterpret_cast<void*>(ptr)));
+    if (ptr) ref_release(reinterpret_cast<void*>(ptr));
+    NML_CUDA(cudaGetLastError());
     return NML_OK;
 }
 

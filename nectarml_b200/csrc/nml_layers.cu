@@ -56,28 +56,23 @@ __device__ __forceinline__ float act_grad(int act, float slope, float y) {
 // consecutive 16-byte vectors, so every access is fully coalesced whatever C is.
 
 // First stage of a per-channel reduction over rows.  kBackward == false: a = sum x, b = sum x^2.
-// kBackward == true: with dz = dy * act'(y) and xhat = (x - mean) * rstd: a = sum dz, b = sum dz * xhat.
-// Block p writes its sums to partial[p][0..C) and partial[p][C..2C).
+// kBackward == true: with dz = dy * act'(y): a = sum dz, b = sum dz * x (the second stage turns b into
+// d gamma = rstd * (b - mean * a), so this pass needs no per-channel constants).  Two rows are in flight
+// per thread.  Block p writes its sums to partial[p][0..C) and partial[p][C..2C).
 template <bool kBackward>
 __global__ void __launch_bounds__(256) bn_reduce_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy,
-                                                        const uint4* __restrict__ y, const float* __restrict__ mean,
-                                                        const float* __restrict__ rstd, int act, float slope,
+                                                        const uint4* __restrict__ y, int act, float slope,
                                                         float* __restrict__ partial, size_t M, int C) {
     __shared__ float sm[256][17];
     const int cpr = C >> 3;
     const int rpb = blockDim.x / cpr;
     const int col = threadIdx.x % cpr, rsub = threadIdx.x / cpr;
-    float a[8], b[8], mu[8], rs[8];
+    float a[8], b[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        a[j] = b[j] = 0.f;
-        mu[j] = kBackward ? mean[col * 8 + j] : 0.f;
-        rs[j] = kBackward ? rstd[col * 8 + j] : 0.f;
-    }
-    for (size_t row = static_cast<size_t>(blockIdx.x) * rpb + rsub; row < M; row += static_cast<size_t>(gridDim.x) * rpb) {
-        const size_t v = row * cpr + col;
+    for (int j = 0; j < 8; ++j) a[j] = b[j] = 0.f;
+    auto add = [&](const uint4& xv, const uint4& dv, const uint4& yv) {
         float xf[8];
-        unpack8(__ldg(x + v), xf);
+        unpack8(xv, xf);
         if (!kBackward) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
@@ -86,15 +81,30 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(const uint4* __restrict_
             }
         } else {
             float df[8], yf[8];
-            unpack8(__ldg(dy + v), df);
-            if (act != 0) unpack8(__ldg(y + v), yf);
+            unpack8(dv, df);
+            if (act != 0) unpack8(yv, yf);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 const float dz = df[j] * (act != 0 ? act_grad(act, slope, yf[j]) : 1.f);
                 a[j] += dz;
-                b[j] += dz * (xf[j] - mu[j]) * rs[j];
+                b[j] += dz * xf[j];
             }
         }
+    };
+    const size_t stride = static_cast<size_t>(gridDim.x) * rpb;
+    size_t row = static_cast<size_t>(blockIdx.x) * rpb + rsub;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (; row + stride < M; row += 2 * stride) {
+        const size_t v0 = row * cpr + col, v1 = (row + stride) * cpr + col;
+        const uint4 x0 = __ldg(x + v0), x1 = __ldg(x + v1);
+        const uint4 d0 = kBackward ? __ldg(dy + v0) : zero, d1 = kBackward ? __ldg(dy + v1) : zero;
+        const uint4 y0 = (kBackward && act != 0) ? __ldg(y + v0) : zero, y1 = (kBackward && act != 0) ? __ldg(y + v1) : zero;
+        add(x0, d0, y0);
+        add(x1, d1, y1);
+    }
+    if (row < M) {
+        const size_t v0 = row * cpr + col;
+        add(__ldg(x + v0), kBackward ? __ldg(dy + v0) : zero, (kBackward && act != 0) ? __ldg(y + v0) : zero);
     }
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
@@ -119,10 +129,11 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(const uint4* __restrict_
 
 // Second stage: adds the P rows of partial sums in a fixed order (32 interleaved running sums in double,
 // then those 32 in order).  mode 0: out0 = mean, out1 = 1 / sqrt(biased variance + eps).
-// mode 1: out0 = sum a (d beta), out1 = sum b (d gamma).  blockDim = (32, 32): the pass is a chain of load
-// latencies, so it is spread over as many threads as a block has.
+// mode 1: out0 = sum a (d beta), out1 = rstd * (sum b - mean * sum a) (d gamma).  blockDim = (32, 32): the
+// pass is a chain of load latencies, so it is spread over as many threads as a block has.
 __global__ void __launch_bounds__(1024) bn_finish_kernel(const float* __restrict__ partial, int P, int C, int mode, double inv_M,
-                                                        float eps, float* __restrict__ out0, float* __restrict__ out1) {
+                                                        float eps, const float* __restrict__ mean, const float* __restrict__ rstd,
+                                                        float* __restrict__ out0, float* __restrict__ out1) {
     __shared__ double pa[32][33], pb[32][33];
     const int c = blockIdx.x * 32 + threadIdx.x;
     double sa = 0.0, sb = 0.0;
@@ -151,12 +162,12 @@ __global__ void __launch_bounds__(1024) bn_finish_kernel(const float* __restrict
             out1[c] = static_cast<float>(1.0 / sqrt(var + static_cast<double>(eps)));
         } else {
             out0[c] = static_cast<float>(ta);
-            out1[c] = static_cast<float>(tb);
+            out1[c] = static_cast<float>(static_cast<double>(rstd[c]) * (tb - static_cast<double>(mean[c]) * ta));
         }
     }
 }
 
-// y = act(gamma * (x - mean) * rstd + beta [+ residual]), fp16 in and out.
+// y = act(gamma * (x - mean) * rstd + beta [+ residual]), fp16 in and out; two rows in flight per thread.
 __global__ void __launch_bounds__(256) bn_apply_kernel(const uint4* __restrict__ x, const uint4* __restrict__ res,
                                                        uint4* __restrict__ y, const float* __restrict__ gamma,
                                                        const float* __restrict__ beta, const float* __restrict__ mean,
@@ -171,11 +182,10 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const uint4* __restrict__
         sc[j] = (gamma ? gamma[c] : 1.f) * rstd[c];
         sh[j] = (beta ? beta[c] : 0.f) - mean[c] * sc[j];
     }
-    for (size_t row = static_cast<size_t>(blockIdx.x) * rpb + rsub; row < M; row += static_cast<size_t>(gridDim.x) * rpb) {
-        const size_t v = row * cpr + col;
+    auto one = [&](const uint4& xv, const uint4& rv) -> uint4 {
         float xf[8], rf[8];
-        unpack8(__ldg(x + v), xf);
-        if (res) unpack8(__ldg(res + v), rf);
+        unpack8(xv, xf);
+        if (res) unpack8(rv, rf);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             float t = xf[j] * sc[j] + sh[j];
@@ -183,12 +193,27 @@ __global__ void __launch_bounds__(256) bn_apply_kernel(const uint4* __restrict__
             if (act != 0 && t < 0.f) t = (act == 1) ? 0.f : t * slope;
             xf[j] = t;
         }
-        y[v] = pack8(xf);
+        return pack8(xf);
+    };
+    const size_t stride = static_cast<size_t>(gridDim.x) * rpb;
+    size_t row = static_cast<size_t>(blockIdx.x) * rpb + rsub;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (; row + stride < M; row += 2 * stride) {
+        const size_t v0 = row * cpr + col, v1 = (row + stride) * cpr + col;
+        const uint4 x0 = __ldg(x + v0), x1 = __ldg(x + v1);
+        const uint4 r0 = res ? __ldg(res + v0) : zero, r1 = res ? __ldg(res + v1) : zero;
+        y[v0] = one(x0, r0);
+        y[v1] = one(x1, r1);
+    }
+    if (row < M) {
+        const size_t v0 = row * cpr + col;
+        y[v0] = one(__ldg(x + v0), res ? __ldg(res + v0) : zero);
     }
 }
 
-// dx = gamma * rstd * (dz - dbeta / M - xhat * dgamma / M) with dz = dy * act'(y); optionally dres = dz
-// (the gradient of the residual input that was added before the activation).
+// dx = gamma * rstd * (dz - dbeta / M - xhat * dgamma / M) with dz = dy * act'(y), folded into
+// dx = A * dz + B * x + C per channel; optionally dres = dz (the gradient of the residual input that was
+// added before the activation).  Two rows in flight per thread.
 __global__ void __launch_bounds__(256) bn_dx_kernel(const uint4* __restrict__ x, const uint4* __restrict__ dy,
                                                     const uint4* __restrict__ y, uint4* __restrict__ dx, uint4* __restrict__ dres,
                                                     const float* __restrict__ gamma, const float* __restrict__ mean,
@@ -198,30 +223,50 @@ __global__ void __launch_bounds__(256) bn_dx_kernel(const uint4* __restrict__ x,
     const int cpr = C >> 3;
     const int rpb = blockDim.x / cpr;
     const int col = threadIdx.x % cpr, rsub = threadIdx.x / cpr;
-    float mu[8], rs[8], k0[8], k1[8], k2[8];
+    float ka[8], kb[8], kc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
         const int c = col * 8 + j;
-        mu[j] = mean[c];
-        rs[j] = rstd[c];
-        k0[j] = (gamma ? gamma[c] : 1.f) * rs[j];
-        k1[j] = dbeta[c] * inv_M;
-        k2[j] = dgamma[c] * inv_M;
+        const float rs = rstd[c], mu = mean[c];
+        const float k0 = (gamma ? gamma[c] : 1.f) * rs, k1 = dbeta[c] * inv_M, k2 = dgamma[c] * inv_M;
+        ka[j] = k0;
+        kb[j] = -k0 * rs * k2;
+        kc[j] = k0 * (mu * rs * k2 - k1);
     }
-    for (size_t row = static_cast<size_t>(blockIdx.x) * rpb + rsub; row < M; row += static_cast<size_t>(gridDim.x) * rpb) {
-        const size_t v = row * cpr + col;
+    auto one = [&](const uint4& xv, const uint4& dv, const uint4& yv, uint4& dz_out) -> uint4 {
         float xf[8], df[8], yf[8];
-        unpack8(__ldg(x + v), xf);
-        unpack8(__ldg(dy + v), df);
-        if (act != 0) unpack8(__ldg(y + v), yf);
+        unpack8(xv, xf);
+        unpack8(dv, df);
+        if (act != 0) unpack8(yv, yf);
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const float dz = df[j] * (act != 0 ? act_grad(act, slope, yf[j]) : 1.f);
             df[j] = dz;
-            xf[j] = k0[j] * (dz - k1[j] - (xf[j] - mu[j]) * rs[j] * k2[j]);
+            xf[j] = ka[j] * dz + kb[j] * xf[j] + kc[j];
         }
-        dx[v] = pack8(xf);
-        if (dres) dres[v] = pack8(df);
+        dz_out = pack8(df);
+        return pack8(xf);
+    };
+    const size_t stride = static_cast<size_t>(gridDim.x) * rpb;
+    size_t row = static_cast<size_t>(blockIdx.x) * rpb + rsub;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    for (; row + stride < M; row += 2 * stride) {
+        const size_t v0 = row * cpr + col, v1 = (row + stride) * cpr + col;
+        const uint4 x0 = __ldg(x + v0), x1 = __ldg(x + v1), d0 = __ldg(dy + v0), d1 = __ldg(dy + v1);
+        const uint4 y0 = act != 0 ? __ldg(y + v0) : zero, y1 = act != 0 ? __ldg(y + v1) : zero;
+        uint4 z0, z1;
+        dx[v0] = one(x0, d0, y0, z0);
+        dx[v1] = one(x1, d1, y1, z1);
+        if (dres) {
+            dres[v0] = z0;
+            dres[v1] = z1;
+        }
+    }
+    if (row < M) {
+        const size_t v0 = row * cpr + col;
+        uint4 z0;
+        dx[v0] = one(__ldg(x + v0), __ldg(dy + v0), act != 0 ? __ldg(y + v0) : zero, z0);
+        if (dres) dres[v0] = z0;
     }
 }
 
@@ -387,10 +432,10 @@ int nml_bn_forward(const void* x, long long rows, int channels, const float* gam
     int threads;
     const int P = bn_grid(rows, channels, &threads);
     float* partial = static_cast<float*>(workspace);
-    bn_reduce_kernel<false><<<P, threads, 0, st>>>(static_cast<const uint4*>(x), nullptr, nullptr, nullptr, nullptr, 0, 0.f,
-                                                   partial, static_cast<size_t>(rows), channels);
+    bn_reduce_kernel<false><<<P, threads, 0, st>>>(static_cast<const uint4*>(x), nullptr, nullptr, 0, 0.f, partial,
+                                                   static_cast<size_t>(rows), channels);
     bn_finish_kernel<<<(channels + 31) / 32, dim3(32, 32), 0, st>>>(partial, P, channels, 0, 1.0 / static_cast<double>(rows), eps,
-                                                                  mean, rstd);
+                                                                   nullptr, nullptr, mean, rstd);
     bn_apply_kernel<<<bn_grid_elementwise(rows, channels), threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(residual),
                                            static_cast<uint4*>(y), gamma, beta, mean, rstd, act, slope,
                                            static_cast<size_t>(rows), channels);
@@ -413,9 +458,9 @@ int nml_bn_backward(const void* dy, const void* y, const void* x, long long rows
     const int P = bn_grid(rows, channels, &threads);
     float* partial = static_cast<float*>(workspace);
     bn_reduce_kernel<true><<<P, threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(dy),
-                                                  static_cast<const uint4*>(y), mean, rstd, act, slope, partial,
+                                                  static_cast<const uint4*>(y), act, slope, partial,
                                                   static_cast<size_t>(rows), channels);
-    bn_finish_kernel<<<(channels + 31) / 32, dim3(32, 32), 0, st>>>(partial, P, channels, 1, 0.0, 0.f, dbeta, dgamma);
+    bn_finish_kernel<<<(channels + 31) / 32, dim3(32, 32), 0, st>>>(partial, P, channels, 1, 0.0, 0.f, mean, rstd, dbeta, dgamma);
     bn_dx_kernel<<<bn_grid_elementwise(rows, channels), threads, 0, st>>>(static_cast<const uint4*>(x), static_cast<const uint4*>(dy), static_cast<const uint4*>(y),
                                         static_cast<uint4*>(dx), static_cast<uint4*>(dres), gamma, mean, rstd, dbeta, dgamma, act,
                                         slope, static_cast<float>(1.0 / static_cast<double>(rows)), static_cast<size_t>(rows),

@@ -87,3 +87,60 @@ def test_bucket_without_process_group_is_a_noop():
     b.view(0).fill_(1.0)
     assert b.all_reduce() is None
     assert float(b.view(0).sum()) == 12.0 and b.view(1).shape == (5,)
+
+
+def _store_worker(rank, world, port, ret):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nectarml_b200 import train
+        store = train.ParamStore("cpu")
+        layers = [train._Layer(store, (40, 8, 3, 3), None), train._Layer(store, (16,), (16,)),
+                  train._Layer(store, (100, 40), (100,)), train._Layer(store, (7, 5, 1, 1), (7,))]
+        store.finalize(n_buckets=3)
+        assert store.bucket_bounds[0] == 0 and store.bucket_bounds[-1] == store.n
+        assert all(b in [store.offsets[l.ia] for l in layers] + [store.n] for b in store.bucket_bounds[1:])
+        # second micro-batch of a step: gradients add to the flat buffer and the buckets leave as they complete
+        store.grad.fill_(1.0)
+        store.accumulate = True
+        store.begin_backward(last_micro_batch=True)
+        issued = []
+        for l in reversed(layers):  # the backward pass completes the layers last to first
+
+            def run(dw, db, l=l):
+                dw.fill_(float(rank + 1))
+                if db is not None:
+                    db.fill_(10.0 * (rank + 1))
+            l.weight_gradient(run)
+            issued.append(len(store.pending))
+        store.wait_exchange()
+        store.accumulate = False
+        want_w = sum(1.0 + (r + 1) for r in range(world))
+        want_b = sum(1.0 + 10.0 * (r + 1) for r in range(world))
+        ok = all(bool((store.g32(l.ia) == want_w).all()) for l in layers)
+        ok = ok and all(bool((store.g32(l.ib) == want_b).all()) for l in layers if l.ib is not None)
+        if rank == 0:
+            ret["ok"] = ok
+            ret["issued"] = issued
+            ret["buckets"] = len(store.bucket_bounds) - 1
+    finally:
+        dist.destroy_process_group()
+
+
+def test_param_store_buckets_leave_as_the_backward_pass_completes_them():
+    """Host logic of the training step's gradient exchange on two gloo ranks: flat buffer, bucket cuts at
+    layer boundaries, accumulation of a later micro-batch, one all-reduce per bucket issued when the
+    bucket's last layer reports in, sums equal over the ranks."""
+    ctx = mp.get_context("spawn")
+    with ctx.Manager() as mgr:
+        ret = mgr.dict()
+        port = _free_port()
+        procs = [ctx.Process(target=_store_worker, args=(r, 2, port, ret)) for r in range(2)]
+        for p in procs:
+            p.start()
+        for p in procs:
+            p.join(120)
+            assert p.exitcode == 0
+        assert ret["ok"]
+        assert ret["issued"][-1] == ret["buckets"] and sorted(ret["issued"]) == list(ret["issued"])
