@@ -257,7 +257,7 @@ class Workload:
                 self.layers[i]["dw"], self.layers[i]["db"] = bucket.view(2 * j), bucket.view(2 * j + 1)
             self.last_of_bucket[grp[-1]] = b
         # SMs left to NCCL while an all-reduce may be in flight (see nml_set_sm_limit); 0 = none
-        self.sm_reserve = int(os.environ.get("NML_BENCH_SM_RESERVE", "8")) if world > 1 else 0
+        self.sm_reserve = int(os.environ.get("NML_BENCH_SM_RESERVE", "16")) if world > 1 else 0
         self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
         if world > 1:  # launch order of the data-parallel step: every weight gradient, then forward + dgrad per layer
             self.launches = [x for x in self.launches if x["pass"] == "wgrad"] + [x for x in self.launches if x["pass"] != "wgrad"]
@@ -450,6 +450,7 @@ def measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world):
         per_gpu = global_batch // shard_of
         micro = per_gpu
     net.init(seed=11)
+    net.store.sm_reserve = int(os.environ.get("NML_BENCH_SM_RESERVE", "16"))
     n_micro = per_gpu // micro
     step = train.TrainStep(net, loss, lr=0.01 if kind == "resnet50_step" else 2e-4, momentum=0.9, weight_decay=1e-4)
     x = (torch.randn(micro, hw, hw, 3, device=dev) if loss == "cross_entropy" else torch.rand(micro, hw, hw, 3, device=dev) * 2 - 1).half()
@@ -462,11 +463,16 @@ def measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world):
     flops_micro = net.store.flops
     launches_micro = ops.launch_count() - launches_before        # this library's kernels in one micro-batch
     ops.device_status()
-    graphs = step.capture(x, target, count, accumulate_variants=(False, True) if n_micro > 1 else (False,)) if use_graphs else None
+    split = None
+    if use_graphs and n_micro == 1 and hasattr(net, "frontier") and world > 1 and os.environ.get("NML_BENCH_SPLIT", "1") != "0":
+        split = step.capture_split(x, target, count)   # decoder's gradients leave while the encoder's backward runs
+    graphs = step.capture(x, target, count, accumulate_variants=(False, True) if n_micro > 1 else (False,)) if use_graphs and not split else None
 
     def one_step():
         # (synthetic data: every micro-batch reuses the same resident tensors, as the static inputs of a graph do)
-        if graphs:
+        if split:
+            step.replay_split(split)
+        elif graphs:
             for i in range(n_micro):
                 graphs[i > 0][0].replay()
             step.exchange_all()
@@ -487,7 +493,7 @@ def measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world):
     ms = time_steps(torch, dist, world, dev, one_step, steps)
     t1 = time.time()
     # (a replayed graph does not pass through the library's counter: its launches are those of the captured micro-batch)
-    launches = (ops.launch_count() - launches0) + (launches_micro * n_micro * steps if graphs else 0)
+    launches = (ops.launch_count() - launches0) + (launches_micro * n_micro * steps if (graphs or split) else 0)
     ops.device_status()
     clocks = sampler.window(t0, t1) if sampler else None
     step_flops = flops_micro * n_micro * world
@@ -496,7 +502,7 @@ def measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world):
         global_batch = per_gpu  # a single GPU's share was timed
     return {"value": global_batch * steps / (ms * 1e-3), "unit": "img/s", "img_s": global_batch * steps / (ms * 1e-3),
             "ms_per_step": ms / steps, "steps": steps, "global_batch": global_batch, "per_gpu_batch": per_gpu,
-            "micro_batch": micro, "scaling": "strong", "cuda_graphs": bool(graphs),
+            "micro_batch": micro, "scaling": "strong", "cuda_graphs": bool(graphs or split), "split_backward": bool(split),
             "contraction_tflops": achieved, "contraction_gflop_per_image": step_flops / global_batch / 1e9,
             "frac_of_measured_tensor_peak": achieved / world / peaks["tflops"], "gpu_launches": launches, "clocks": clocks,
             "found_inf": int(net.store.found_inf), "workload": TRAIN_NAMES[kind],
@@ -519,7 +525,7 @@ def run_gpu(args):
     if world > 1:
         # a fixed, small CTA budget for NCCL: the contraction kernels are persistent, one CTA per SM, so every SM
         # NCCL takes is one of theirs (NVSwitch keeps the all-reduce fast at a few CTAs)
-        os.environ.setdefault("NCCL_MAX_CTAS", os.environ.get("NML_BENCH_NCCL_CTAS", "8"))
+        os.environ.setdefault("NCCL_MAX_CTAS", os.environ.get("NML_BENCH_NCCL_CTAS", "16"))
         dist.init_process_group("nccl", device_id=dev)
         if local == 0:  # one rank (re)builds a stale library, the others wait for it
             build.build()
@@ -531,6 +537,23 @@ def run_gpu(args):
     if sampler:
         sampler.start()
         time.sleep(0.25)
+
+    if args.workload in TRAIN_NAMES:  # one of the training steps on its own: img/s at the fixed global batch
+        r = measure_train(args.workload, args, peaks, sampler, torch, dist, dev, rank, world)
+        if sampler:
+            sampler.stop()
+        if rank == 0:
+            print(json.dumps({"metric": "conv-net train img/s", "value": r["value"], "unit": "img/s", "n_gpus": world,
+                              "steps": r["steps"], "warmup": 2, "ms_per_step": r["ms_per_step"], "higher_is_better": True,
+                              "scaling": "strong", "vs_baseline": None, "dtype": "f16 (fp32 accumulate, fp32 master weights)",
+                              "data": "synthetic", "impl": "nectarml_b200",
+                              "config": {"workload": TRAIN_NAMES[args.workload], "global_batch": r["global_batch"],
+                                         "parallelism": f"dp{world}" if world > 1 else "1 GPU"},
+                              "e2e": None, "gpu_launches": r["gpu_launches"], "clocks": r["clocks"], "detail": r}), flush=True)
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return r
 
     wl = Workload(args.workload, dev, rank, world, args.only)
     head = measure(wl, args, peaks, sampler, torch, dist, args.steps, per_layer=True)
@@ -553,10 +576,12 @@ def run_gpu(args):
         ops.device_status()
 
     # End to end through the public API with host buffers (pinned), copies inside the timed region: every
-    # layer's x and dy come from the host and ALL its results (y, dx, dw, db) go back to it.  Copies run on their
-    # own streams, ordered against the compute stream by events, so a layer's transfers overlap the other
-    # layers' kernels; every step ends with the compute stream waiting for that step's last device-to-host copy.
-    e2e = None
+    # layer's x and dy come from the host and its results go back to it -- the gradients dw, db (`e2e`: what a
+    # data-parallel caller takes off the device; y and dx stay there, as the reference's host ops leave every
+    # result on the device) or all four results (`e2e_all_results`).  Copies run on their own streams, ordered
+    # against the compute stream by events, so a layer's transfers overlap the other layers' kernels; every step
+    # ends with the compute stream waiting for that step's last device-to-host copy.
+    e2e, e2e_legs = None, {}
     if args.workload == "linear":
         layers = wl.layers
         for l in layers:
@@ -566,6 +591,8 @@ def run_gpu(args):
         ev_in = [torch.cuda.Event() for _ in layers]
         ev_done = [torch.cuda.Event() for _ in layers]
         ev_out = [torch.cuda.Event() for _ in layers]
+
+        returned = ["dw", "db"]
 
         def step_e2e():
             cur = torch.cuda.current_stream()
@@ -585,22 +612,30 @@ def run_gpu(args):
                 ev_done[i].record(cur)
                 with torch.cuda.stream(s_out):
                     s_out.wait_event(ev_done[i])
-                    for k_ in ("y", "dx", "dw", "db"):
+                    for k_ in returned:
                         l[k_ + "_host"].copy_(l[k_], non_blocking=True)
                     ev_out[i].record(s_out)
             cur.wait_event(ev_out[-1])
 
-        for _ in range(2):
-            step_e2e()
-        e2e_steps = max(2, min(args.steps, 5))
-        e2e_ms = time_steps(torch, dist, world, dev, step_e2e, e2e_steps)
-        for l in layers:  # what reached the host is what is on the device
-            if not torch.equal(l["db_host"], l["db"].cpu()) or not torch.equal(l["y_host"][:64], l["y"][:64].cpu()):
-                raise SystemExit("bench.py: end-to-end leg returned stale results")
-        h2d = sum(l["x"].numel() * 2 + l["dy"].numel() * 2 for l in layers)
-        d2h = sum(l[k_].numel() * l[k_].element_size() for l in layers for k_ in ("y", "dx", "dw", "db"))
-        e2e = {"value": wl.step_flops * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
-               "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h), "returns": "y, dx, dw, db of every layer"}
+        e2e_legs = {}
+        for name, keys in (("e2e_all_results", ["y", "dx", "dw", "db"]), ("e2e", ["dw", "db"])):
+            returned[:] = keys
+            for _ in range(2):
+                step_e2e()
+            e2e_steps = max(2, min(args.steps, 5))
+            torch.cuda.synchronize()
+            time.sleep(args.idle_s)
+            e2e_ms = time_steps(torch, dist, world, dev, step_e2e, e2e_steps)
+            for l in layers:  # what reached the host is what is on the device
+                if not torch.equal(l["db_host"], l["db"].cpu()) or not torch.equal(l["y_host"][:64], l["y"][:64].cpu()):
+                    raise SystemExit("bench.py: end-to-end leg returned stale results")
+            h2d = sum(l["x"].numel() * 2 + l["dy"].numel() * 2 for l in layers)
+            d2h = sum(l[k_].numel() * l[k_].element_size() for l in layers for k_ in keys)
+            e2e_legs[name] = {"value": wl.step_flops * world * e2e_steps / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s",
+                              "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h),
+                              "returns": ", ".join(keys) + " of every layer" + ("" if len(keys) == 4 else
+                                                                                " (y and dx stay on the device, where the reference's host ops leave every result)")}
+        e2e = e2e_legs["e2e"]
 
     # the other workloads of the path, each with its own roofline block (device-resident inputs)
     others = {}
@@ -634,7 +669,7 @@ def run_gpu(args):
                        if world > 1 else "1 GPU",
                        "l2": "inputs and outputs of one step exceed the 126 MB L2 several times over; every step cycles through it",
                        "timing": f"every timed region is a burst of `steps` steps from an idle GPU ({args.idle_s} s pause); `sustained` is the same step for >= {args.sustain_s} s"},
-            "e2e": e2e, "gpu_launches": head["gpu_launches"], "clocks": head["clocks"], "roofline": head["roofline"],
+            "e2e": e2e, "e2e_all_results": e2e_legs.get("e2e_all_results") if e2e else None, "gpu_launches": head["gpu_launches"], "clocks": head["clocks"], "roofline": head["roofline"],
             "per_layer": head.get("per_layer"),
         }
         if "comm_ms_exposed" in head:
@@ -761,7 +796,8 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="nectarml_b200", choices=["nectarml_b200", "reference"])
-    ap.add_argument("--workload", default="linear", choices=["linear", "resnet", "pix2pix", "config1"])
+    ap.add_argument("--workload", default="linear",
+                    choices=["linear", "resnet", "pix2pix", "config1", "resnet50_step", "pix2pix_step"])
     ap.add_argument("--headline-only", action="store_true", help="skip the extra workloads of the default run")
     ap.add_argument("--sustain-s", type=float, default=3.0, help="seconds of the sustained leg (0: skip)")
     ap.add_argument("--idle-s", type=float, default=0.5, help="pause before each timed burst")

@@ -84,7 +84,7 @@ class ParamStore:
         self._exchange = False
         # SMs left to NCCL while an all-reduce may be in flight (the contraction kernels are persistent, one CTA
         # per SM; see nml_set_sm_limit)
-        self.sm_reserve = 8
+        self.sm_reserve = 16
         self.sms = torch.cuda.get_device_properties(self.device).multi_processor_count if self.device.type == "cuda" else 0
 
     def _view(self, buf, i):
@@ -347,6 +347,10 @@ class _Net:
         self.store = ParamStore(device)
         # an input that requires grad, so that autograd runs the backward of layers whose data input does not
         self.token = torch.zeros((), device=device, requires_grad=True)
+        # Activations at which a split backward pass stops (set by forward() of nets that support it).  Never
+        # kept across steps: tensors of an earlier, uncaptured pass that die INSIDE a later stream capture
+        # invalidate the capture (their allocator bookkeeping records events on the streams they crossed).
+        self.frontier = None
 
     def _finish(self, n_buckets):
         self.store.finalize(n_buckets)
@@ -464,6 +468,14 @@ class Pix2PixGenerator(_Net):
                 x = self.store.record(torch.relu(y))       # bottleneck
             skips.append(x)
         skips.pop()
+        # The frontier between decoder and encoder in the backward pass: the bottleneck's output as the decoder
+        # reads it and the encoder activations as the concatenations read them (views, so that each is its own
+        # autograd node).  A split backward (TrainStep.capture_split) stops here, sends the decoder's gradients
+        # off, and then continues into the encoder.
+        x = x.view_as(x)
+        skips = [d.view_as(d) for d in skips]
+        self.frontier = [x] + list(skips)   # (dropped again by whoever ran the backward pass: see TrainStep)
+        self.frontier_first_param = self.up[0][0].first   # decoder (and final layer) parameters start here
         for i, (conv, bn) in enumerate(self.up):
             if i > 0:
                 x = torch.cat((x, skips.pop()), dim=3)
@@ -495,6 +507,7 @@ class TrainStep:
         loss = self._loss(out, target, global_count)
         (loss * self.loss_scale).backward()
         store.accumulate = False
+        self.net.frontier = None
         return loss.detach()
 
     def capture(self, x, target, global_count: int, accumulate_variants=(False,)):
@@ -520,6 +533,60 @@ class TrainStep:
             graphs[acc] = (g, loss)
         store.communicate = saved
         return graphs
+
+    def capture_split(self, x, target, global_count: int):
+        """For nets that expose a `frontier` (the U-Net: decoder | encoder): captures forward + the decoder's
+        backward into one CUDA graph and the encoder's backward into a second one, so that the all-reduce of the
+        decoder's gradients (two thirds of the parameters) runs while the encoder's backward does.  The second
+        graph is planned under the SM reserve that leaves room for NCCL.  Returns (graph_a, graph_b, loss)."""
+        store, net = self.net.store, self.net
+        saved = store.communicate
+        store.communicate = False
+
+        def part_a():
+            store.accumulate = False
+            store.begin_backward(last_micro_batch=False)
+            out = net.forward(x)
+            loss = self._loss(out, target, global_count)
+            grads = torch.autograd.grad(loss * self.loss_scale, net.frontier)
+            return loss.detach(), grads
+
+        def part_b(grads):
+            torch.autograd.backward(net.frontier, grads)
+            net.frontier = None
+
+        side = torch.cuda.Stream(device=net.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                _, g = part_a()
+                part_b(g)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        ga, gb = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+        with torch.cuda.graph(ga):
+            loss, grads = part_a()
+        if store.world > 1 and store.sm_reserve and store.sms:
+            ops.set_sm_limit(store.sms - store.sm_reserve)
+        try:
+            with torch.cuda.graph(gb, pool=ga.pool()):
+                part_b(grads)
+        finally:
+            ops.set_sm_limit(0)
+        store.communicate = saved
+        return ga, gb, loss
+
+    def replay_split(self, graphs) -> None:
+        """Replays a split capture with the decoder's gradient exchange overlapping the encoder's backward."""
+        ga, gb, _ = graphs
+        store, cut = self.net.store, self.net.frontier_first_param
+        ga.replay()
+        if store.world > 1:
+            store.pending.append(dist.all_reduce(store.grad[cut:], async_op=True))
+        gb.replay()
+        if store.world > 1:
+            store.pending.append(dist.all_reduce(store.grad[:cut], async_op=True))
+            store.wait_exchange()
 
     def exchange_all(self) -> None:
         """All-reduces every bucket of the flat gradient (used after a graph-captured backward)."""

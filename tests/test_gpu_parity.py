@@ -385,6 +385,37 @@ def test_matmul_2d_right_operand_is_shared_over_the_batch(oracle):
     ops.device_status()
 
 
+def test_sm_limit_changes_the_plan_not_the_result(oracle):
+    """nml_set_sm_limit (used while a collective shares the GPU): the kernels run on fewer SMs, tile and split-K
+    plans are made for that count, results stay within tolerance of the oracle."""
+    name = "w_3x3_64_64"
+    case = WGRAD_PATCH_SHAPES[name]
+    g = geometry(case)
+    x, w, b, dy = cases.draw_conv(name, case)
+    r = oracle.round_f16
+    y_o, dx_o, dw_o, db_o = oracle_all(oracle, case, r(x), r(w), r(b), r(dy))
+    h = torch.float16
+    xd, dyd, wd, bd = dev(x, h, nhwc=True), dev(dy, h, nhwc=True), dev(w, h), dev(b, h)
+    gen = torch.Generator(device=DEV).manual_seed(8)
+    lx = torch.randn(4096, 512, device=DEV, generator=gen).half()
+    ldy = torch.randn(4096, 2048, device=DEV, generator=gen).half()
+    try:
+        for limit in (140, 37, 1):
+            ops.set_sm_limit(limit)
+            assert_f16(host(ops.conv_forward(g, xd, wd, bd, layout="nhwc"), nhwc=True), y_o, f"y @ {limit} SMs")
+            assert_f16(host(ops.conv_backward_data(g, dyd, wd, layout="nhwc"), nhwc=True), dx_o, f"dx @ {limit} SMs")
+            dw, db = ops.conv_backward_weight(g, xd, dyd, layout="nhwc")
+            assert_f32(host(dw), dw_o, f"dw @ {limit} SMs", tol=2e-5)
+            assert_f32(host(db), db_o, f"db @ {limit} SMs", tol=2e-5)
+            if limit > 1:
+                ldw, ldb = ops.linear_backward_weight(lx, ldy)
+                ref = ldy[:, :64].double().t() @ lx.double()
+                assert torch.allclose(ldw[:64].double(), ref, rtol=1e-4, atol=2e-5 * float(ref.abs().max()))
+            ops.device_status()
+    finally:
+        ops.set_sm_limit(0)
+
+
 def test_workspace_too_small_is_reported():
     import ctypes as C
     from nectarml_b200 import _lib

@@ -246,3 +246,38 @@ def test_bn_act_kernels_match_torch_and_repeat_bitwise():
                 assert float((store.g32(layer.ia) - gm.grad).norm() / gm.grad.norm()) < 1e-2
                 assert float((store.g32(layer.ib) - bt.grad).norm() / bt.grad.norm()) < 1e-2
     ops.device_status()
+
+
+def test_graph_captures_replay_the_eager_step_bit_for_bit():
+    """CUDA-graph capture of forward + backward (one graph, and the U-Net's decoder | encoder split used to
+    overlap the gradient exchange) against the eager micro-batch: every kernel is deterministic, so the flat
+    gradient buffer must come out bit-identical."""
+    torch.manual_seed(2)
+    net = train.Pix2PixGenerator(DEV, in_channels=3, features=8)
+    net.init(seed=7)
+    for i, shape in enumerate(net.store.shapes):
+        if len(shape) == 4:
+            net.store.w32(i).mul_(8.0)
+    net.store.sync_half()
+    x = (torch.rand(2, 256, 256, 3, device=DEV) * 2 - 1).half()
+    target = (torch.rand(2, 256, 256, 3, device=DEV) * 2 - 1).half()
+    step = train.TrainStep(net, "l1", loss_scale=8192.0)
+    count = target.numel()
+    loss = step.micro_batch(x, target, count, first=True, last=False)
+    ops.device_status()
+    want, want_loss = net.store.grad.clone(), float(loss)
+    assert float(want.abs().max()) > 0
+
+    graph, gloss = step.capture(x, target, count)[False]
+    net.store.grad.zero_()
+    graph.replay()
+    ops.device_status()
+    assert torch.equal(net.store.grad, want) and float(gloss) == want_loss
+
+    split = step.capture_split(x, target, count)
+    net.store.grad.zero_()
+    step.replay_split(split)
+    ops.device_status()
+    assert torch.equal(net.store.grad, want) and float(split[2]) == want_loss
+    cut = net.frontier_first_param
+    assert 0 < cut < net.store.n and cut == net.store.offsets[net.up[0][0].ia]
