@@ -510,6 +510,25 @@ def measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world):
                     "counts only the Conv2d / ConvTranspose2d / Linear passes' algorithmic FLOPs over the whole step time"}
 
 
+def pin_to_gpu_numa_node(index: int):
+    """Binds this process to the CPUs NVML lists as local to GPU `index` (a read-only NVML query), so that the
+    pinned host buffers of the end-to-end leg are allocated on, and driven from, the GPU's own NUMA node.
+    Returns the number of CPUs bound to, or None when NVML has nothing to say."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, m in enumerate(words) for b in range(64) if (m >> b) & 1}
+        cpus &= set(os.sched_getaffinity(0))
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -522,6 +541,7 @@ def run_gpu(args):
         raise SystemExit("bench.py needs a CUDA device: this path has no CPU fallback")
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
+    numa = pin_to_gpu_numa_node(local) if world > 1 else None
     if world > 1:
         # a fixed, small CTA budget for NCCL: the contraction kernels are persistent, one CTA per SM, so every SM
         # NCCL takes is one of theirs (NVSwitch keeps the all-reduce fast at a few CTAs)
@@ -667,6 +687,7 @@ def run_gpu(args):
                        "parallelism": (f"dp{world} (rows / batch sharded, NCCL all-reduce of {head['buckets']} flat dW/db buckets, "
                                        f"NCCL_MAX_CTAS={os.environ.get('NCCL_MAX_CTAS')}, {head['sm_reserve']} SMs left to it while in flight)")
                        if world > 1 else "1 GPU",
+                       "host_cpus_bound": numa,
                        "l2": "inputs and outputs of one step exceed the 126 MB L2 several times over; every step cycles through it",
                        "timing": f"every timed region is a burst of `steps` steps from an idle GPU ({args.idle_s} s pause); `sustained` is the same step for >= {args.sustain_s} s"},
             "e2e": e2e, "e2e_all_results": e2e_legs.get("e2e_all_results") if e2e else None, "gpu_launches": head["gpu_launches"], "clocks": head["clocks"], "roofline": head["roofline"],
