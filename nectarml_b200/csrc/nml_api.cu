@@ -217,7 +217,8 @@ static int load_helper_kernels() {
         (const void*)convert_rows_kernel<float>, (const void*)convert_rows_kernel<__half>,
         (const void*)colsum_rows_kernel<float>, (const void*)colsum_rows_kernel<__half>,
         (const void*)colsum_rows_f16x8_kernel,
-        (const void*)repack_weight_kernel<float>, (const void*)repack_weight_kernel<__half>,
+        (const void*)repack_weight_tile_kernel<float>, (const void*)repack_weight_tile_kernel<__half>,
+        (const void*)repack_weight_rows_kernel<float>, (const void*)repack_weight_rows_kernel<__half>,
         (const void*)pad_pack_c8_kernel<float>, (const void*)pad_pack_c8_kernel<__half>,
         (const void*)repack_weight_c8_kernel<float>, (const void*)repack_weight_c8_kernel<__half>,
         (const void*)finish_rows_kernel<float>, (const void*)finish_rows_kernel<__half>,
@@ -734,14 +735,21 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         w_planes[1] = p1;
         if (!ws.dry) {
             if (!ws.fits()) return NML_ERR_WORKSPACE;
-            // out[n][t][k] = w[...]: a swap of the two inner dimensions of [B][R][Cc] (see repack_weight_kernel)
+            // out[n][t][k] = w[...]: a swap of the two inner dimensions of [B][R][Cc] (see repack_weight_*_kernel)
             const int rB = f.k_is_dim0 ? 1 : f.d0, rR = f.k_is_dim0 ? f.d0 : f.d1, rC = f.k_is_dim0 ? f.d1 * T : T;
             if (rB > 65535) return NML_ERR_UNSUPPORTED;
-            const dim3 grid(ceil_div(rC, 32), ceil_div(kp, 32), rB);
-            if (f.w_dtype == NML_F32)
-                { repack_weight_kernel<float><<<grid, dim3(32, 8), 0, st>>>(static_cast<const float*>(f.w), p0, p1, mi.enc, rR, rC, kp); ++g_launches; }
-            else
-                { repack_weight_kernel<__half><<<grid, dim3(32, 8), 0, st>>>(static_cast<const __half*>(f.w), p0, p1, mi.enc, rR, rC, kp); ++g_launches; }
+#define NML_REPACK(T)                                                                                                           \
+    do {                                                                                                                        \
+        if (rC <= 64)                                                                                                           \
+            repack_weight_rows_kernel<T><<<dim3(ceil_div(kp, 64), rB), 256, 0, st>>>(static_cast<const T*>(f.w), p0, p1, mi.enc, \
+                                                                                     rR, rC, kp);                               \
+        else                                                                                                                    \
+            repack_weight_tile_kernel<T><<<dim3(ceil_div(rC, 64), ceil_div(kp, 64), rB), 256, 0, st>>>(                          \
+                static_cast<const T*>(f.w), p0, p1, mi.enc, rR, rC, kp);                                                         \
+    } while (0)
+            if (f.w_dtype == NML_F32) NML_REPACK(float); else NML_REPACK(__half);
+#undef NML_REPACK
+            ++g_launches;
             NML_CUDA(cudaGetLastError());
         }
     }

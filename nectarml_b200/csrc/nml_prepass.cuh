@@ -184,23 +184,59 @@ __global__ void __launch_bounds__(256) colsum_rows_f16x8_kernel(const __half* __
 // k is zero-padded to kp per tap so that no K block straddles two taps.  Both cases swap the two inner
 // dimensions of a [B][R][Cc] array: out[b][c][r] = in[b][r][c], rows padded to Rp --
 //   k_is_dim0 == 0 : B = D0, R = D1 (k), Cc = T          k_is_dim0 == 1 : B = 1, R = D0 (k), Cc = D1 * T
-// -- so one tiled transpose through shared memory serves them, with coalesced reads AND writes (a gather
-// with one side strided moved a 32-byte sector per 2-byte element).  grid (ceil(Cc/32), ceil(Rp/32), B),
-// block (32, 8).
+// -- so a tiled transpose through shared memory serves them, with coalesced reads AND writes (a gather
+// with one side strided moved a 32-byte sector per 2-byte element).  Two kernels by the width of the
+// source rows:
+//   repack_weight_tile_kernel  Cc > 64: 64 x 64 tiles, two elements per thread on both sides.
+//                              grid (ceil(Cc/64), ceil(Rp/64), B), 256 threads.
+//   repack_weight_rows_kernel  Cc <= 64 (the taps of one kernel): 64 source rows are one contiguous run of
+//                              64 * Cc elements, read linearly.  grid (ceil(Rp/64), B), 256 threads.
+__device__ __forceinline__ void store_enc2(int enc, void* out0, void* out1, size_t i, float a, float b) {
+    if (enc == ENC_F16) {
+        *reinterpret_cast<__half2*>(reinterpret_cast<__half*>(out0) + i) = __floats2half2_rn(a, b);  // i is even
+    } else {
+        store_enc(enc, out0, out1, i, a);
+        store_enc(enc, out0, out1, i + 1, b);
+    }
+}
+
 template <typename TIn>
-__global__ void __launch_bounds__(256) repack_weight_kernel(const TIn* __restrict__ w, void* out0, void* out1, int enc,
-                                                            int R, int Cc, int Rp) {
-    __shared__ float tile[32][33];
-    const int c0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+__global__ void __launch_bounds__(256) repack_weight_tile_kernel(const TIn* __restrict__ w, void* out0, void* out1, int enc,
+                                                                 int R, int Cc, int Rp) {
+    __shared__ float tile[64][65];  // [r][c]
+    const int c0 = blockIdx.x * 64, r0 = blockIdx.y * 64;
     const size_t b = blockIdx.z;
-    for (int j = threadIdx.y; j < 32; j += 8) {
-        const int r = r0 + j, c = c0 + threadIdx.x;
-        tile[j][threadIdx.x] = (r < R && c < Cc) ? load_as_float(w, (b * R + r) * Cc + c) : 0.f;
+    const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+    for (int j = ty; j < 64; j += 8) {
+        const int r = r0 + j, c = c0 + 2 * tx;
+        const size_t src = (b * R + r) * Cc + c;
+        tile[j][2 * tx] = (r < R && c < Cc) ? load_as_float(w, src) : 0.f;
+        tile[j][2 * tx + 1] = (r < R && c + 1 < Cc) ? load_as_float(w, src + 1) : 0.f;
     }
     __syncthreads();
-    for (int j = threadIdx.y; j < 32; j += 8) {
-        const int c = c0 + j, r = r0 + threadIdx.x;
-        if (c < Cc && r < Rp) store_enc(enc, out0, out1, (b * Cc + c) * Rp + r, tile[threadIdx.x][j]);
+    for (int j = ty; j < 64; j += 8) {
+        const int c = c0 + j, r = r0 + 2 * tx;  // Rp is a multiple of the K block, so r + 1 < Rp whenever r < Rp
+        if (c < Cc && r < Rp) store_enc2(enc, out0, out1, (b * Cc + c) * Rp + r, tile[2 * tx][j], tile[2 * tx + 1][j]);
+    }
+}
+
+template <typename TIn>
+__global__ void __launch_bounds__(256) repack_weight_rows_kernel(const TIn* __restrict__ w, void* out0, void* out1, int enc,
+                                                                 int R, int Cc, int Rp) {
+    __shared__ float tile[64][65];  // [c][r]
+    const int r0 = blockIdx.x * 64;
+    const size_t b = blockIdx.y;
+    const int rows = min(64, R - r0);  // may be <= 0: a block of pure padding
+    const int n_valid = rows > 0 ? rows * Cc : 0;
+    const size_t base = (b * R + r0) * Cc;
+    for (int i = threadIdx.x; i < 64 * Cc; i += 256) {
+        const int r = i / Cc, c = i - r * Cc;
+        tile[c][r] = (i < n_valid) ? load_as_float(w, base + i) : 0.f;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < Cc * 32; idx += 256) {
+        const int c = idx >> 5, r = (idx & 31) * 2;
+        if (r0 + r < Rp) store_enc2(enc, out0, out1, (b * Cc + c) * Rp + r0 + r, tile[c][r], tile[c][r + 1]);
     }
 }
 
