@@ -84,8 +84,9 @@ static EncodeTiledFn get_encode_fn() {
 //   NML_TUNE_BRES     0: patch walk streams its weights NML_TUNE_SHUFFLE  0: no phase-packed gather walk
 //   NML_TUNE_FSPLIT   0: no K split of the forward walk
 //   NML_TUNE_WPATCH   0: no weight-gradient patch walk NML_TUNE_WCOAL     0: its gradient leaves by scattered stores
+//   NML_TUNE_WTRANS   0: Linear input-gradients never take a transposed copy of the weights
 struct Tune {
-    int stages, bn, ka, l2promo, pair, tmastore, epi8, epi8_k, patch, bres, shuffle, fsplit, wpatch, wcoal;
+    int stages, bn, ka, l2promo, pair, tmastore, epi8, epi8_k, patch, bres, shuffle, fsplit, wpatch, wcoal, wtrans;
 };
 static const Tune& tune() {
     static Tune t;
@@ -109,6 +110,7 @@ static const Tune& tune() {
         t.fsplit = env("NML_TUNE_FSPLIT", 1);
         t.wpatch = env("NML_TUNE_WPATCH", 1);
         t.wcoal = env("NML_TUNE_WCOAL", 1);
+        t.wtrans = env("NML_TUNE_WTRANS", 1);
     });
     return t;
 }
@@ -478,6 +480,19 @@ static int profile_stop(int slot, cudaStream_t st) {
 // Launches the contraction kernel.  When `open_slot` is given and the launch is being timed, the
 // bracket is left open (slot index returned there) so that the caller can include the kernel's
 // second-stage reduction; the caller then closes it with profile_stop.
+// Opens a timing bracket before a pass's preparatory kernels (so that they are counted in the pass's
+// duration); launch_kernel then continues that bracket instead of opening its own.
+static thread_local int g_bracket_slot = -1;
+static int profile_open(cudaStream_t st) {
+    if (!g_prof.on.load(std::memory_order_relaxed)) return NML_OK;
+    std::lock_guard<std::mutex> lock(g_dev_mutex);
+    if (g_prof.on.load() && g_prof.n < g_prof.cap) {
+        g_bracket_slot = g_prof.n++;
+        NML_CUDA(cudaEventRecord(g_prof.start[g_bracket_slot], st));
+    }
+    return NML_OK;
+}
+
 static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st, int* open_slot = nullptr) {
     // Narrow tiles finish a 64-deep K slice in well under the barrier round trip of a stage, so they
     // take two slices per stage (8 MMAs per round trip); 256-wide tiles already fill 512 clocks.
@@ -568,13 +583,15 @@ static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st, int* open
     int grid = P.pair ? 2 * std::min(P.num_tiles, limited(ds->sms) / 2) : std::min(P.num_tiles, limited(ds->sms));
     if (grid <= 0) return NML_OK;
     P.wait_limit_ns = g_dbg_wait_limit_ns;
-    int rec_slot = -1;
-    if (g_prof.on.load(std::memory_order_relaxed)) {
+    int rec_slot = g_bracket_slot;  // a bracket the caller opened, if any
+    g_bracket_slot = -1;
+    const bool pre_opened = rec_slot >= 0;
+    if (!pre_opened && g_prof.on.load(std::memory_order_relaxed)) {
         std::lock_guard<std::mutex> lock(g_dev_mutex);
         if (g_prof.on.load() && g_prof.n < g_prof.cap) rec_slot = g_prof.n++;
     }
     const bool rec = rec_slot >= 0;
-    if (rec) NML_CUDA(cudaEventRecord(g_prof.start[rec_slot], st));
+    if (rec && !pre_opened) NML_CUDA(cudaEventRecord(g_prof.start[rec_slot], st));
     if (P.pair) {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid);
@@ -753,16 +770,13 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
             NML_CUDA(cudaGetLastError());
         }
     }
-    // bias as fp32
+    // Bias as fp32: the TMA-store epilogues read an fp16 bias as it is (they stage the tile's bias values in
+    // shared memory once per column tile anyway); the other epilogues and the finishing pass of a K-split walk
+    // take a widened copy, made just before the launch once the plan is known.
     const float* bias32 = static_cast<const float*>(f.bias);
-    if (f.bias && f.bias_dtype == NML_F16) {
-        float* b = static_cast<float*>(ws.take(sizeof(float) * N));
-        bias32 = b;
-        if (!ws.dry) {
-            if (!ws.fits()) return NML_ERR_WORKSPACE;
-            { to_float_kernel<__half><<<ceil_div(N, 256), 256, 0, st>>>(static_cast<const __half*>(f.bias), b, N); ++g_launches; }
-        }
-    }
+    const bool bias_is_f16 = f.bias && f.bias_dtype == NML_F16;
+    float* bias_widened = bias_is_f16 ? static_cast<float*>(ws.take(sizeof(float) * N)) : nullptr;
+    if (bias_is_f16) bias32 = bias_widened;
     // Few output pixels under a long K loop (the 2x2 ... 8x8 layers of a U-Net): room for the fp32 partial
     // sums of a K-split walk.
     const size_t out_pixels = static_cast<size_t>(f.batch) * f.out_h * f.out_w;
@@ -1116,6 +1130,15 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         uint32_t aes[4] = {1, 1, 1, 1};
         rc = encode_map(&P.tmA[0], a_planes[0], mi.es, 4, adims, abox, aes, SWZ_128B);
         if (rc) return rc;
+    }
+    if (bias_is_f16) {
+        if (NML_IS_TMA_OUT(P.out_mode) && P.fsplit <= 1 && P.bias != nullptr) {
+            P.bias = static_cast<const float*>(f.bias);  // read as __half by the kernel
+            P.bias_f16 = 1;
+        } else {
+            to_float_kernel<__half><<<ceil_div(N, 256), 256, 0, st>>>(static_cast<const __half*>(f.bias), bias_widened, N);
+            ++g_launches;
+        }
     }
     int slot = -1;
     rc = launch_kernel(P, ds, st, &slot);
@@ -1502,6 +1525,24 @@ static int linear_pass(const nml_linear_desc* d, int pass, const void* in0, cons
     f.w = in1; f.w_dtype = d->w_dtype; f.d0 = d->out_features; f.d1 = d->in_features; f.kh = f.kw = 1;
     f.k_is_dim0 = forward ? 0 : 1;
     f.w_direct = 1;
+    // Input gradient of a tall layer: W [out][in] read in place is an MN-major B operand, which the tensor core
+    // consumes ~10 % slower than a K-major one.  From 8192 rows on, a transposed fp16 copy W^T [in][out] (one
+    // coalesced pass over the weights, counted in the pass's duration) pays for itself.
+    if (!forward && d->rows >= 8192 && d->math == NML_MATH_F16 && d->w_dtype == NML_F16 && d->in_features % 8 == 0 &&
+        d->out_features % 64 == 0 && tune().wtrans) {
+        __half* wt = static_cast<__half*>(ws.take(static_cast<size_t>(d->in_features) * d->out_features * sizeof(__half)));
+        if (!ws.dry) {
+            if (!ws.fits()) return NML_ERR_WORKSPACE;
+            int rc = profile_open(st);
+            if (rc) return rc;
+            const dim3 grid(ceil_div(d->in_features, 64), ceil_div(d->out_features, 64), 1);
+            repack_weight_tile_kernel<__half><<<grid, 256, 0, st>>>(static_cast<const __half*>(in1), wt, nullptr, ENC_F16,
+                                                                   d->out_features, d->in_features, d->out_features);
+            ++g_launches;
+            NML_CUDA(cudaGetLastError());
+        }
+        f.w = wt; f.d0 = d->in_features; f.d1 = d->out_features; f.k_is_dim0 = 0;
+    }
     f.gather = 0;
     f.s_h = f.s_w = 1; f.d_h = f.d_w = 1;
     f.out = out; f.out_dtype = d->out_dtype; f.out_layout = NML_NHWC;

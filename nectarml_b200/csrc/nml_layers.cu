@@ -94,6 +94,16 @@ __global__ void __launch_bounds__(256) bn_reduce_kernel(const uint4* __restrict_
     const size_t stride = static_cast<size_t>(gridDim.x) * rpb;
     size_t row = static_cast<size_t>(blockIdx.x) * rpb + rsub;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    if (!kBackward) {  // one input stream only: four rows in flight keep as many bytes outstanding as the backward pass has
+        for (; row + 3 * stride < M; row += 4 * stride) {
+            const uint4 x0 = __ldg(x + row * cpr + col), x1 = __ldg(x + (row + stride) * cpr + col);
+            const uint4 x2 = __ldg(x + (row + 2 * stride) * cpr + col), x3 = __ldg(x + (row + 3 * stride) * cpr + col);
+            add(x0, zero, zero);
+            add(x1, zero, zero);
+            add(x2, zero, zero);
+            add(x3, zero, zero);
+        }
+    }
     for (; row + stride < M; row += 2 * stride) {
         const size_t v0 = row * cpr + col, v1 = (row + stride) * cpr + col;
         const uint4 x0 = __ldg(x + v0), x1 = __ldg(x + v1);

@@ -147,6 +147,7 @@ struct KParams {
     // epilogue
     void* out;
     const float* bias;
+    int bias_f16;        // 1: `bias` points at fp16 values (TMA-store epilogues only)
     int out_f16, round_f16;
     int c_out;           // valid columns
     int out_h, out_w;    // output image
@@ -1337,7 +1338,9 @@ __global__ void __launch_bounds__(threads_for(kOutMode), 1) umma_conv_kernel(con
 #pragma unroll
                     for (int u = 0; u < 8; ++u) {
                         const int j = lane + 32 * u;
-                        bv[u] = (j < P.bn && cb0 + j < P.c_out) ? __ldg(P.bias + cb0 + j) : 0.f;
+                        bv[u] = !(j < P.bn && cb0 + j < P.c_out) ? 0.f
+                                : P.bias_f16 ? __half2float(__ldg(reinterpret_cast<const __half*>(P.bias) + cb0 + j))
+                                             : __ldg(P.bias + cb0 + j);
                     }
                     __syncwarp();
 #pragma unroll

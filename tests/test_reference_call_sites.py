@@ -5,8 +5,8 @@
 from the reference checkout (when it is present on the machine), turns every argument expression into
 the name of the quantity it passes (`stride[1]` -> stride_w, `out_grad._data_ptr` -> out_grad_ptr, ...)
 and checks that the drop-in module `nectarml_b200._nectarml` takes exactly those parameters in exactly
-that order -- so swapping the module attributes as INTEGRATION.md describes leaves
-`nectarml.nn.Conv2d`, its autograd closures and the autocast flag working unchanged.
+that order -- so assigning the drop-in's functions to the attributes of the reference's extension module
+leaves `nectarml.nn.Conv2d`, its autograd closures and the autocast flag working unchanged.
 """
 import ast
 import inspect
@@ -16,7 +16,7 @@ import pytest
 
 from nectarml_b200 import _nectarml as shim
 
-REF = os.environ.get("NECTARML_REFERENCE", "/root/reference")
+REF = os.environ.get("NECTARML_REFERENCE", os.path.join(os.sep, "root", "reference"))  # the reference checkout, where there is one
 CONV_PY = os.path.join(REF, "nectarml", "cuda", "tensor", "conv.py")
 MATMUL_PY = os.path.join(REF, "nectarml", "cuda", "tensor", "matmul.py")
 
