@@ -308,6 +308,49 @@ class Workload:
             if p is not None:
                 p.wait()
 
+    def capture(self, communicate=True):
+        """The launches of one step as CUDA graphs: the C ABI neither allocates nor synchronises, so its calls
+        record as they are (tensor maps travel as kernel parameters).  Returns (replay function, launches recorded).
+        The all-reduces stay OUTSIDE the graphs: the data-parallel step is cut into one graph per gradient bucket
+        (the weight gradients that fill it) and one for the forward and input-gradient passes, and each bucket's
+        all-reduce is issued between two replays, exactly where the eager step issues it."""
+        torch, ops = self.torch, self.ops
+
+        def record(fn):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            return g
+
+        n0 = ops.launch_count()
+        if self.world == 1 or not communicate:
+            g = record(lambda: self.step(False))
+            return g.replay, ops.launch_count() - n0
+        segments, first = [], 0
+        for i in range(len(self.layers)):
+            if i in self.last_of_bucket:
+                span = range(first, i + 1)
+                segments.append((record(lambda: [self.wgrad(self.layers[j]) for j in span]), self.last_of_bucket[i]))
+                first = i + 1
+                if self.sm_reserve:  # planned into every kernel recorded from here on
+                    ops.set_sm_limit(self.sms - self.sm_reserve)
+        tail = list(range(first, len(self.layers)))
+        segments.append((record(lambda: [self.wgrad(self.layers[j]) for j in tail] +
+                                        [self.forward_and_dgrad(l) for l in self.layers]), None))
+        if self.sm_reserve:
+            ops.set_sm_limit(0)
+
+        def replay():
+            pending = []
+            for g, bucket in segments:
+                g.replay()
+                if bucket is not None:
+                    pending.append(self.buckets[bucket].all_reduce(async_op=True))
+            for p in pending:
+                if p is not None:
+                    p.wait()
+        return replay, ops.launch_count() - n0
+
 
 def time_steps(torch, dist, world, dev, fn, steps):
     """Times `steps` calls on the device between barriers; returns max-over-ranks milliseconds."""
@@ -326,6 +369,11 @@ def time_steps(torch, dist, world, dev, fn, steps):
     if world > 1:
         dist.all_reduce(ms, op=dist.ReduceOp.MAX)
     return float(ms.item())
+
+
+def graph_wanted(world):
+    """Whether the timed step of the kernel sweeps is replayed from a CUDA graph (NML_BENCH_GRAPH=0: eager)."""
+    return os.environ.get("NML_BENCH_GRAPH", "1") != "0"
 
 
 def measure(wl, args, peaks, sampler, torch, dist, steps, per_layer):
@@ -356,18 +404,29 @@ def measure(wl, args, peaks, sampler, torch, dist, steps, per_layer):
     per_launch_ms = ops.profile_end(n_rec)
     clocks_launches = sampler.window(t0, time.time()) if sampler else None
 
+    # The timed step: the launches of one step recorded once into a CUDA graph and replayed (one host call per
+    # step instead of one per kernel; the kernels, their order and their arguments are those of the eager step).
+    step, step_nocomm, per_step_launches = wl.step, (lambda: wl.step(communicate=False)), None
+    graphed = graph_wanted(world)
+    if graphed:
+        step, per_step_launches = wl.capture(True)
+        if world > 1:
+            step_nocomm, _ = wl.capture(False)
+        for _ in range(2):
+            step()
+    wl.timed_step, wl.graphed = step, graphed
     settle()
     launches0 = ops.launch_count()
     t0 = time.time()
-    ms_total = time_steps(torch, dist, world, dev, wl.step, steps)
+    ms_total = time_steps(torch, dist, world, dev, step, steps)
     t1 = time.time()
-    launches = ops.launch_count() - launches0
+    launches = per_step_launches * steps if graphed else ops.launch_count() - launches0
     clocks = sampler.window(t0, t1) if sampler else None
     ops.device_status()
     comm_ms_exposed = None
     if world > 1:  # the same step without its all-reduces: the difference is what the exchange costs the step
         settle()
-        ms_nocomm = time_steps(torch, dist, world, dev, lambda: wl.step(communicate=False), steps)
+        ms_nocomm = time_steps(torch, dist, world, dev, step_nocomm, steps)
         comm_ms_exposed = (ms_total - ms_nocomm) / steps
     reps = len(per_launch_ms) // n1 if n1 else 0
     mean = [sum(per_launch_ms[i:reps * n1:n1]) / reps for i in range(n1)] if reps else []
@@ -415,7 +474,9 @@ def measure(wl, args, peaks, sampler, torch, dist, steps, per_layer):
                                          "launches": sum(1 for r in table if r["bound"] == "tensor")}
     out = {"value": wl.step_flops * world * steps / (ms_total * 1e-3) / 1e12, "unit": "TFLOP/s",
            "ms_per_step": ms_total / steps, "steps": steps, "gpu_launches": int(launches), "clocks": clocks,
-           "roofline": roof, "workload": WORKLOAD_NAMES[wl.key], "buckets": len(wl.buckets), "sm_reserve": wl.sm_reserve}
+           "roofline": roof, "workload": WORKLOAD_NAMES[wl.key], "buckets": len(wl.buckets), "sm_reserve": wl.sm_reserve,
+           "launch": ("CUDA graph replay of the step's kernels" + (", all-reduces issued between the graphs of the buckets" if world > 1 else ""))
+           if graphed else "one host call per kernel"}
     if comm_ms_exposed is not None:
         out["comm_ms_exposed"] = comm_ms_exposed
         out["roofline"]["achieved_scope"] = "rank 0's GPU, all-reduces in flight"
@@ -585,7 +646,7 @@ def run_gpu(args):
         est_ms = max(head["ms_per_step"], 1e-3)
         n = max(10, int(args.sustain_s * 1e3 / est_ms))
         t0 = time.time()
-        ms = time_steps(torch, dist, world, dev, wl.step, n)
+        ms = time_steps(torch, dist, world, dev, wl.timed_step, n)
         t1 = time.time()
         ck = sampler.window(t0 + 0.5, t1) if sampler else None
         sustained = {"value": wl.step_flops * world * n / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "seconds": ms * 1e-3,
@@ -687,7 +748,7 @@ def run_gpu(args):
                        "parallelism": (f"dp{world} (rows / batch sharded, NCCL all-reduce of {head['buckets']} flat dW/db buckets, "
                                        f"NCCL_MAX_CTAS={os.environ.get('NCCL_MAX_CTAS')}, {head['sm_reserve']} SMs left to it while in flight)")
                        if world > 1 else "1 GPU",
-                       "host_cpus_bound": numa,
+                       "host_cpus_bound": numa, "launch": head["launch"],
                        "l2": "inputs and outputs of one step exceed the 126 MB L2 several times over; every step cycles through it",
                        "timing": f"every timed region is a burst of `steps` steps from an idle GPU ({args.idle_s} s pause); `sustained` is the same step for >= {args.sustain_s} s"},
             "e2e": e2e, "e2e_all_results": e2e_legs.get("e2e_all_results") if e2e else None, "gpu_launches": head["gpu_launches"], "clocks": head["clocks"], "roofline": head["roofline"],
