@@ -416,6 +416,39 @@ def test_sm_limit_changes_the_plan_not_the_result(oracle):
         ops.set_sm_limit(0)
 
 
+def test_weight_gradient_call_keeps_stream_order_and_records_into_a_graph():
+    """A consumer queued on the caller's stream right after a weight-gradient call (no host synchronisation)
+    sees the finished db, the call can be recorded into a CUDA graph, and repeated calls give the same bits."""
+    gen = torch.Generator(device=DEV).manual_seed(21)
+    x = torch.randn(4096, 512, device=DEV, generator=gen).half()
+    dy = torch.randn(4096, 2048, device=DEV, generator=gen).half()
+    want = dy.double().sum(0)
+    dw = torch.empty(2048, 512, device=DEV)
+    db = torch.empty(2048, device=DEV)
+    stream = torch.cuda.Stream()
+    stream.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(stream):
+        copies = []
+        for _ in range(3):
+            db.fill_(float("nan"))
+            ops.linear_backward_weight(x, dy, dw=dw, db=db)
+            copies.append(db.clone())          # queued behind the call on the same stream
+        stream.synchronize()
+    for c in copies:
+        assert torch.allclose(c.double(), want, rtol=1e-5, atol=1e-3)
+        assert torch.equal(c, copies[0])
+    torch.cuda.current_stream().wait_stream(stream)
+    graph = torch.cuda.CUDAGraph()
+    db.fill_(float("nan"))
+    with torch.cuda.graph(graph):
+        ops.linear_backward_weight(x, dy, dw=dw, db=db)
+    db.fill_(float("nan"))
+    graph.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(db, copies[0])
+    ops.device_status()
+
+
 def test_workspace_too_small_is_reported():
     import ctypes as C
     from nectarml_b200 import _lib
