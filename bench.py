@@ -20,6 +20,7 @@ threads) on a bounded sample of the same workload.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import re
@@ -315,10 +316,11 @@ class Workload:
         (the weight gradients that fill it) and one for the forward and input-gradient passes, and each bucket's
         all-reduce is issued between two replays, exactly where the eager step issues it."""
         torch, ops = self.torch, self.ops
+        from nectarml_b200.train import capture_into
 
         def record(fn):
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with capture_into(g):  # (garbage collector held off, capture errors checked per thread)
                 fn()
             return g
 
@@ -721,14 +723,18 @@ def run_gpu(args):
     # the other workloads of the path, each with its own roofline block (device-resident inputs)
     others = {}
     if args.workload == "linear" and not args.only and not args.headline_only:
+        wl.timed_step = None   # (its graphs go with it now, not at some later garbage collection)
         del wl
+        gc.collect()
         torch.cuda.empty_cache()
         for key, label in (("resnet", "resnet_conv"), ("pix2pix", "pix2pix_conv"), ("config1", "config1_fp32_3xtf32")):
             w2 = Workload(key, dev, rank, world)
             others[label] = measure(w2, args, peaks, sampler, torch, dist, max(3, min(args.steps, 20)), per_layer=True)
             if rank == 0 and world == 1 and not args.no_cpu_baseline:
                 others[label]["cpu_baseline"] = cpu_baseline(key, budget_s=4.0)
+            w2.timed_step = None
             del w2
+            gc.collect()
             torch.cuda.empty_cache()
         for kind in ("resnet50_step", "pix2pix_step"):
             others[kind] = measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world)

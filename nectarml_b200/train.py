@@ -18,7 +18,9 @@ layer, so the exchange starts as early as it can).
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes as C
+import gc
 from typing import List, Optional, Sequence, Tuple
 
 import torch
@@ -28,6 +30,28 @@ from . import _lib, ops
 from .ops import ConvGeometry
 
 ACT_NONE, ACT_RELU, ACT_LEAKY = 0, 1, 2
+
+# Stream captures here are checked per thread: the capturing thread issues only capture-safe calls, while the
+# NCCL watchdog thread of torch.distributed polls the events of earlier collectives whenever it likes, which a
+# capture in "global" mode takes for an error (the capture is then invalidated, every so many runs).
+CAPTURE_MODE = "thread_local"
+
+
+@contextlib.contextmanager
+def capture_into(graph, pool=None):
+    """torch.cuda.graph with the garbage collector held off: a dead reference cycle that owns an older
+    CUDAGraph would otherwise be collected at some allocation inside the capture, and destroying a graph
+    while a stream is capturing invalidates the capture."""
+    gc.collect()
+    was_enabled = gc.isenabled()
+    gc.disable()
+    try:
+        kw = {"pool": pool} if pool is not None else {}
+        with torch.cuda.graph(graph, capture_error_mode=CAPTURE_MODE, **kw):
+            yield
+    finally:
+        if was_enabled:
+            gc.enable()
 
 
 # ------------------------------------------------------------------ parameters --
@@ -528,7 +552,7 @@ class TrainStep:
         graphs = {}
         for acc in accumulate_variants:
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with capture_into(g):
                 loss = self.micro_batch(x, target, global_count, first=not acc, last=False)
             graphs[acc] = (g, loss)
         store.communicate = saved
@@ -564,12 +588,12 @@ class TrainStep:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         ga, gb = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
-        with torch.cuda.graph(ga):
+        with capture_into(ga):
             loss, grads = part_a()
         if store.world > 1 and store.sm_reserve and store.sms:
             ops.set_sm_limit(store.sms - store.sm_reserve)
         try:
-            with torch.cuda.graph(gb, pool=ga.pool()):
+            with capture_into(gb, pool=ga.pool()):
                 part_b(grads)
         finally:
             ops.set_sm_limit(0)
