@@ -440,7 +440,8 @@ def test_weight_gradient_call_keeps_stream_order_and_records_into_a_graph():
     torch.cuda.current_stream().wait_stream(stream)
     graph = torch.cuda.CUDAGraph()
     db.fill_(float("nan"))
-    with torch.cuda.graph(graph):
+    from nectarml_b200.train import capture_into
+    with capture_into(graph):
         ops.linear_backward_weight(x, dy, dw=dw, db=db)
     db.fill_(float("nan"))
     graph.replay()
