@@ -88,56 +88,82 @@ def profiled_traffic(workload: str):
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while a timed region runs."""
+    """Samples SM clocks and throttle reasons while a timed region runs: NVML read-only queries every few
+    milliseconds from a thread of this process (a 50 ms burst then holds ten samples), or `nvidia-smi -lms`
+    when the NVML binding is missing.  Nothing is ever set."""
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    # nvmlClocksEventReason* bits (nvml.h)
+    REASON_BITS = (("sw_power_cap", 0x4), ("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40))
 
-    def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+    def __init__(self, index: int, uuid: str = ""):
+        self.index, self.uuid, self.proc, self.samples = index, uuid, None, []  # samples: (time, sm MHz, max MHz, reasons)
+        self.nvml, self.handle, self.running, self.source = None, None, False, None
 
     def start(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            if self.uuid:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(self.uuid if self.uuid.startswith("GPU-") else "GPU-" + self.uuid)
+            else:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM))
+            self.nvml, self.running, self.source = pynvml, True, "nvml"
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return
+        except Exception:  # no binding, no library, or the device is not visible to NVML under this id
+            self.nvml = None
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.QUERY}",
                                           "--format=csv,noheader,nounits", "-lms", "25"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.source = "nvidia-smi"
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
 
+    def _poll_nvml(self):
+        nv = self.nvml
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+        while self.running:
+            try:
+                mhz = float(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = int(reasons_fn(self.handle))
+                self.samples.append((time.time(), mhz, self.max_mhz, tuple(n for n, b in self.REASON_BITS if mask & b)))
+            except Exception:
+                pass
+            time.sleep(0.004)
+
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append((time.time(), line.strip()))
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                mhz, mx = float(parts[0]), float(parts[1])
+            except ValueError:
+                continue
+            names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+            self.samples.append((time.time(), mhz, mx, tuple(n for n, v in zip(names, parts[2:6]) if v.lower().startswith("active"))))
 
     def window(self, t0: float, t1: float):
         """Clock summary of the samples taken between t0 and t1 (the sampler keeps running)."""
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        sm, mx, reasons = [], [], set()
-        for ts, line in list(self.lines):
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6 or not (t0 - 0.05 <= ts <= t1 + 0.15):
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), parts[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:  # timed region shorter than one sample: fall back to every sample taken
-            for _, line in list(self.lines):
-                parts = [p.strip() for p in line.split(",")]
-                try:
-                    sm.append(float(parts[0]))
-                    mx.append(float(parts[1]))
-                except (ValueError, IndexError):
-                    pass
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        if self.source is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source (NVML binding and nvidia-smi unavailable)"]}
+        slack = (0.0, 0.0) if self.source == "nvml" else (0.05, 0.15)
+        inside = [x for x in list(self.samples) if t0 - slack[0] <= x[0] <= t1 + slack[1]]
+        if not inside:  # timed region shorter than one sample: the samples nearest to it
+            inside = sorted(list(self.samples), key=lambda x: abs(x[0] - 0.5 * (t0 + t1)))[:3]
+        reasons = sorted({r for x in inside for r in x[3]})
+        return {"sm_mhz": statistics.median(x[1] for x in inside) if inside else None,
+                "sm_max_mhz": max(x[2] for x in inside) if inside else None,
+                "reasons": reasons, "samples": len(inside), "source": self.source}
 
     def stop(self):
+        self.running = False
         if self.proc is None:
             return
         self.proc.terminate()
@@ -616,7 +642,7 @@ def run_gpu(args):
     else:
         build.build()
     peaks = measured_peaks()
-    sampler = ClockSampler(local) if rank == 0 else None
+    sampler = ClockSampler(local, str(getattr(torch.cuda.get_device_properties(dev), "uuid", "") or "")) if rank == 0 else None
     if sampler:
         sampler.start()
         time.sleep(0.25)
