@@ -85,8 +85,9 @@ static EncodeTiledFn get_encode_fn() {
 //   NML_TUNE_FSPLIT   0: no K split of the forward walk
 //   NML_TUNE_WPATCH   0: no weight-gradient patch walk NML_TUNE_WCOAL     0: its gradient leaves by scattered stores
 //   NML_TUNE_WTRANS   0: Linear input-gradients never take a transposed copy of the weights
+//   NML_TUNE_PAIR128  0: CTA pairs only for 256-column tiles
 struct Tune {
-    int stages, bn, ka, l2promo, pair, tmastore, epi8, epi8_k, patch, bres, shuffle, fsplit, wpatch, wcoal, wtrans;
+    int stages, bn, ka, l2promo, pair, tmastore, epi8, epi8_k, patch, bres, shuffle, fsplit, wpatch, wcoal, wtrans, pair128;
 };
 static const Tune& tune() {
     static Tune t;
@@ -111,6 +112,7 @@ static const Tune& tune() {
         t.wpatch = env("NML_TUNE_WPATCH", 1);
         t.wcoal = env("NML_TUNE_WCOAL", 1);
         t.wtrans = env("NML_TUNE_WTRANS", 1);
+        t.pair128 = env("NML_TUNE_PAIR128", 1);
     });
     return t;
 }
@@ -496,7 +498,7 @@ static int profile_open(cudaStream_t st) {
 static int launch_kernel(KParams& P, DeviceState* ds, cudaStream_t st, int* open_slot = nullptr) {
     // Narrow tiles finish a 64-deep K slice in well under the barrier round trip of a stage, so they
     // take two slices per stage (8 MMAs per round trip); 256-wide tiles already fill 512 clocks.
-    P.ka = P.pair ? 1 : std::max(1, std::min(2, tune().ka ? tune().ka : (P.bn >= 192 ? 1 : 2)));
+    P.ka = (P.pair && P.bn == 256) ? 1 : std::max(1, std::min(2, tune().ka ? tune().ka : (P.bn >= 192 ? 1 : 2)));
     const int stage_bytes = P.ka * (kStageABytes + (P.pair ? P.bn / 2 : P.bn) * 128);
     // Shared memory: the operand ring, then the epilogue's staging buffers (two per warp if that does not
     // cost a ring stage, else one), the per-warp bias tiles, and the barriers.
@@ -1029,7 +1031,14 @@ static int run_fprop_like(const FpropLike& f, Bump& ws, cudaStream_t st) {
         tiles_single += 1ll * ceil_div(P.phases[p].wq, 1 << P.wb_log2) * ceil_div(P.phases[p].hq, 1 << P.hb_log2) *
                         ceil_div(f.batch, 1 << P.nb_log2) * P.n_tiles;
     const bool will_split = may_split && !P.patch && tiles_single * 2 <= limited(ds->sms) && k_iters_min >= 8;
-    P.pair = (tune().pair && !P.patch && !will_split && P.bn == 256 && (!b_mn_major || N % mi.kb == 0) && k_iters_min >= 4 &&
+    // 128-column tiles pair up too (two K slices per stage, see launch_kernel) where every phase has a K loop
+    // of at least four slices and the tiles fill most of the GPU: measured 5-15 % on such layers, a loss on
+    // the short phases of strided gathers and on few-tile problems.
+    int k_iters_all = k_iters_min;
+    for (int p = 0; p < n_phases; ++p)
+        if (P.phases[p].tap_count > 0) k_iters_all = std::min(k_iters_all, P.passes * P.c_blocks * P.phases[p].tap_count);
+    const bool pair_width = P.bn == 256 || (tune().pair128 && P.bn == 128 && k_iters_all >= 4 && tiles_single * 4 >= 3ll * limited(ds->sms));
+    P.pair = (tune().pair && !P.patch && !will_split && pair_width && (!b_mn_major || N % mi.kb == 0) && k_iters_min >= 4 &&
               (P.out_mode == OUT_NHWC_TMA || P.out_mode == OUT_NCHW_TMA || P.out_mode == OUT_NCHW) && limited(ds->sms) >= 2) ? 1 : 0;
     int tiles = 0;
     for (int p = 0; p < n_phases; ++p) {
