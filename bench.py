@@ -553,7 +553,7 @@ def measure_train(kind, args, peaks, sampler, torch, dist, dev, rank, world):
     launches_micro = ops.launch_count() - launches_before        # this library's kernels in one micro-batch
     ops.device_status()
     split = None
-    if use_graphs and n_micro == 1 and hasattr(net, "frontier") and world > 1 and os.environ.get("NML_BENCH_SPLIT", "1") != "0":
+    if use_graphs and n_micro == 1 and net.split_backward and world > 1 and os.environ.get("NML_BENCH_SPLIT", "1") != "0":
         split = step.capture_split(x, target, count)   # decoder's gradients leave while the encoder's backward runs
     graphs = step.capture(x, target, count, accumulate_variants=(False, True) if n_micro > 1 else (False,)) if use_graphs and not split else None
 

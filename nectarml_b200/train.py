@@ -366,6 +366,8 @@ class BatchNormAct(_Layer):
 
 # ------------------------------------------------------------------ models --
 class _Net:
+    split_backward = False   # True for nets whose forward() sets `frontier` (see TrainStep.capture_split)
+
     def __init__(self, device):
         self.device = torch.device(device)
         self.store = ParamStore(device)
@@ -446,6 +448,8 @@ class Pix2PixGenerator(_Net):
     """U-Net generator: 8 x (Conv2d 4x4 s2 p1) down to 1x1, 8 x (ConvTranspose2d 4x4 s2 p1) up with the encoder
     activations concatenated in (examples/pix2pix/generator.py:54-170); BatchNorm + LeakyReLU(0.2) down, BatchNorm +
     ReLU up, tanh on the 3-channel output."""
+
+    split_backward = True
 
     def __init__(self, device, in_channels=3, features=64):
         super().__init__(device)
@@ -564,6 +568,8 @@ class TrainStep:
         decoder's gradients (two thirds of the parameters) runs while the encoder's backward does.  The second
         graph is planned under the SM reserve that leaves room for NCCL.  Returns (graph_a, graph_b, loss)."""
         store, net = self.net.store, self.net
+        if not net.split_backward:
+            raise ValueError("capture_split needs a net whose forward() marks a frontier (split_backward)")
         saved = store.communicate
         store.communicate = False
 

@@ -144,3 +144,11 @@ def test_param_store_buckets_leave_as_the_backward_pass_completes_them():
             assert p.exitcode == 0
         assert ret["ok"]
         assert ret["issued"][-1] == ret["buckets"] and sorted(ret["issued"]) == list(ret["issued"])
+
+
+def test_only_nets_that_mark_a_frontier_offer_the_split_backward():
+    """The data-parallel bench captures the backward pass in two graphs only for nets whose forward() marks
+    a frontier; with one micro-batch per GPU (ResNet-50 on 8 GPUs) the other nets take the single graph."""
+    from nectarml_b200 import train
+    assert train.Pix2PixGenerator.split_backward and not train.ResNet50.split_backward
+    assert not train._Net.split_backward
