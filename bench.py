@@ -194,6 +194,23 @@ def pass_bytes(n_x, n_w, n_y, es):
 
 
 # ------------------------------------------------------------------ workloads --
+def bucket_groups(numel, ratio=0.5, min_bytes=8 << 20):
+    """Cuts layers (fp32 gradient elements per layer, in execution order) into consecutive buckets: a bucket is
+    closed once it holds at least `ratio` times what is still to come and `min_bytes`, so the early buckets are
+    large (their all-reduce overlaps the remaining layers) and the last, exposed one is small."""
+    groups, cur, acc = [], [], 0
+    for i, n_ in enumerate(numel):
+        cur.append(i)
+        acc += n_
+        rest = sum(numel[i + 1:])
+        if rest and acc >= ratio * rest and acc * 4 >= min_bytes:
+            groups.append(cur)
+            cur, acc = [], 0
+    if cur:
+        groups.append(cur)
+    return groups
+
+
 class Workload:
     """Tensors of one workload on one GPU, its step, and the algorithmic work of every contraction launch."""
 
@@ -266,16 +283,7 @@ class Workload:
         # buckets are large and overlap the remaining layers while the last, exposed one is small.
         ratio = float(os.environ.get("NML_BENCH_BUCKET_RATIO", "0.5"))
         numel = [int(np.prod(shapes[2 * i])) + int(np.prod(shapes[2 * i + 1])) for i in range(len(self.layers))]
-        groups, cur, acc = [], [], 0
-        for i, n_ in enumerate(numel):
-            cur.append(i)
-            acc += n_
-            rest = sum(numel[i + 1:])
-            if rest and acc >= ratio * rest and acc * 4 >= (8 << 20):
-                groups.append(cur)
-                cur, acc = [], 0
-        if cur:
-            groups.append(cur)
+        groups = bucket_groups(numel, ratio)
         self.buckets, self.last_of_bucket = [], {}
         for b, grp in enumerate(groups):
             bucket = GradientBucket([sh for i in grp for sh in (shapes[2 * i], shapes[2 * i + 1])], dev)

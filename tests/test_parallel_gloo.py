@@ -152,3 +152,25 @@ def test_only_nets_that_mark_a_frontier_offer_the_split_backward():
     from nectarml_b200 import train
     assert train.Pix2PixGenerator.split_backward and not train.ResNet50.split_backward
     assert not train._Net.split_backward
+
+
+def test_bench_gradient_buckets_are_consecutive_and_front_loaded():
+    """The data-parallel sweeps cut their layers into flat gradient buckets in execution order: every layer in
+    exactly one bucket, buckets consecutive, each closed bucket at least 8 MB and at least half of what follows
+    it, so that the exchange still exposed after the last layer is the smallest one."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    # the Linear sweep under data parallelism: largest gradients first (d = 2048, 2048, 1024, 1024, 512, 512)
+    numel = [4 * d * d + 4 * d for d in (2048, 2048, 1024, 1024, 512, 512)]
+    groups = bench.bucket_groups(numel, 0.5)
+    assert [i for g in groups for i in g] == list(range(len(numel)))
+    sizes = [sum(numel[i] for i in g) for g in groups]
+    for k, sz in enumerate(sizes[:-1]):
+        assert sz * 4 >= (8 << 20) and sz >= 0.5 * sum(sizes[k + 1:])
+    assert sizes[-1] == min(sizes) and len(groups) >= 3
+    assert bench.bucket_groups([10], 0.5) == [[0]]
+    assert bench.bucket_groups([], 0.5) == []
+    # tiny layers never close a bucket on their own
+    assert bench.bucket_groups([100, 100, 100], 0.5) == [[0, 1, 2]]
